@@ -1,0 +1,474 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N = 1   one step = one batched decode-attention call (split-KV pass + merge pass) on the
+        Llama-3-8B-shaped workload: batch 16, 32 query / 8 kv heads, head_dim 128, KV length 4096,
+        fp16, inputs resident in HBM. Metric: algorithmic HBM GB/s of that call.
+N > 1   one step = one long-context decode with the KV sequence (131072 rows) sharded evenly over
+        the N GPUs: local split-KV decode -> NCCL all-gather of (O, LSE) records -> LSE merge.
+        Launched by torch.distributed.run, one process per GPU. Total work is fixed ("strong").
+
+Prints ONE JSON line (rank 0). `--impl reference` times the engine's own CPU attention
+(include/kernels_cpu.hpp, compiled under oracle/_ref, else the C restatement) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one split-pass launch on the N=1 workload, from the ncu
+# capture summarised in profiles/ (None until a capture has been taken for the current kernel).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def load_package():
+    name = "llm_infer_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    d = os.path.join(ROOT, "llm-infer_b200")
+    spec = importlib.util.spec_from_file_location(name, os.path.join(d, "__init__.py"),
+                                                  submodule_search_locations=[d])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 0.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML from a thread while the timed region runs."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, device_index: int):
+        self.samples = []
+        self.reason_bits = 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+
+    def _poll(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+            except Exception:
+                break
+            time.sleep(0.001)
+
+    def __enter__(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._poll, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": [name for bit, name in self.REASONS.items() if self.reason_bits & bit],
+                "samples": len(s)}
+
+
+# --------------------------------------------------------------------------- CPU baseline
+def cpu_reference_arm(wl, shape, steps: int, warmup: int, seconds_budget: float = 25.0):
+    """Times the engine's CPU attention on a bounded sample of `shape` (whole sequences, or the first rows of one
+    long sequence). Returns (GB/s, description dict)."""
+    import numpy as np
+    import oracle
+
+    chk = oracle.best()
+    kind = "reference" if chk.kind == "reference" else "port"
+    # sample: one sequence of the batch; long sequences are cut to 8192 rows so that one step stays well under 0.2 s
+    rows = min(shape.kv_len, 8192)
+    sample = wl.DecodeShape(shape.name + "-cpu-sample", shape.seed, 1, shape.n_heads, shape.n_kv_heads,
+                            shape.head_dim, rows, shape.q_dtype, shape.kv_dtype)
+    q, k, v = wl.decode_inputs(sample)
+    q32 = wl.widen(q, sample.q_dtype)
+    k16, v16 = wl.as_f16_for_oracle(k, sample.kv_dtype), wl.as_f16_for_oracle(v, sample.kv_dtype)
+    for _ in range(max(1, warmup)):
+        chk.attn_decode(q32, k16, v16)
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        chk.attn_decode(q32, k16, v16)
+        done += 1
+        if time.perf_counter() - t0 > seconds_budget:
+            break
+    dt = (time.perf_counter() - t0) / done
+    gbs = sample.algorithmic_bytes() / dt / 1e9
+    desc = {"value": gbs, "unit": "GB/s", "cores": chk.num_threads(), "kind": kind,
+            "sample": f"1 sequence x {rows} KV rows of the workload per step, {done} steps, "
+                      f"{dt * 1e3:.2f} ms/step; OpenMP over the {shape.n_heads} query heads as the engine does",
+            "ms_per_step": dt * 1e3}
+    return gbs, desc, done
+
+
+def run_reference(args, world: int, rank: int):
+    pkg = load_package()
+    wl = pkg.workloads
+    if rank != 0:
+        return
+    shape = wl.C2 if world == 1 else wl.C4
+    gbs, desc, done = cpu_reference_arm(wl, shape, args.steps, args.warmup, seconds_budget=120.0)
+    line = {
+        "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world,
+        "steps": done, "warmup": args.warmup, "ms_per_step": desc["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate",
+        "data": "synthetic", "config": workload_config(shape, world),
+        "cpu_baseline": {k: desc[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(shape, world: int):
+    cfg = {"workload": shape.name, "batch": shape.batch, "kv_len": shape.kv_len, "n_heads": shape.n_heads,
+           "n_kv_heads": shape.n_kv_heads, "head_dim": shape.head_dim, "q_dtype": shape.q_dtype,
+           "kv_dtype": shape.kv_dtype, "kv_layout": "[seq][kv_head][head_dim] per sequence"}
+    if world > 1:
+        cfg["parallelism"] = f"kv-sequence sharded over {world} GPUs, all-gather of (O, LSE), LSE merge"
+    return cfg
+
+
+# --------------------------------------------------------------------------- our arm, 1 GPU
+def time_steps(torch, fn, steps: int):
+    """CUDA-event time of `steps` calls of fn(i) on the current stream, in ms."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(steps):
+        fn(i)
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end)
+
+
+def run_single(args):
+    import torch
+
+    pkg = load_package()
+    from llm_infer_b200 import attention
+    wl = pkg.workloads
+    shape = wl.C2
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    hbm_peak, _, peak_kind = measured_peaks()
+    B, H, Hkv, D, T = shape.batch, shape.n_heads, shape.n_kv_heads, shape.head_dim, shape.kv_len
+
+    # Inputs: N(0,1) from a seeded generator, cast once to fp16. Three independent copies are rotated so that
+    # consecutive steps never re-read a cache line that could still sit in the 126 MB L2.
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(shape.seed)
+    n_sets = 3
+    qs = [torch.randn((B, H, D), generator=gen, device=dev, dtype=torch.float32).half() for _ in range(n_sets)]
+    ks = [torch.randn((B, T, Hkv, D), generator=gen, device=dev, dtype=torch.float32).half() for _ in range(n_sets)]
+    vs = [torch.randn((B, T, Hkv, D), generator=gen, device=dev, dtype=torch.float32).half() for _ in range(n_sets)]
+    out = torch.empty((B, H, D), dtype=torch.float32, device=dev)
+    ws = attention.DecodeWorkspace(B, H, Hkv, D, dev)
+
+    def step(i):
+        j = i % n_sets
+        attention.attn_decode(qs[j], ks[j], vs[j], out=out, workspace=ws)
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+
+    launches0 = attention.kernel_launch_count()
+    with ClockSampler(0) as clocks:
+        ms = time_steps(torch, step, args.steps)
+    launches = attention.kernel_launch_count() - launches0
+    ms_per_step = ms / args.steps
+    alg_bytes = shape.algorithmic_bytes(o_bytes=4)
+    gbs = alg_bytes / (ms_per_step * 1e-3) / 1e9
+    assert int(ws.status.item()) == 0, "device status word reports a timed-out wait"
+
+    # ---- end to end through the public API with host buffers: per decode step the engine moves the new token's
+    # q (and its K/V rows, appended to the resident cache) to the device and reads the attention output back.
+    q_host = qs[0].cpu().pin_memory()
+    knew_host = ks[0][:, T - 1:T].cpu().pin_memory()
+    vnew_host = vs[0][:, T - 1:T].cpu().pin_memory()
+    out_host = torch.empty((B, H, D), dtype=torch.float32).pin_memory()
+    q_dev = torch.empty_like(qs[0])
+
+    def e2e_step(i):
+        j = i % n_sets
+        q_dev.copy_(q_host, non_blocking=True)
+        ks[j][:, T - 1:T].copy_(knew_host, non_blocking=True)
+        vs[j][:, T - 1:T].copy_(vnew_host, non_blocking=True)
+        attention.attn_decode(q_dev, ks[j], vs[j], out=out, workspace=ws)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result before the next token
+
+    for i in range(3):
+        e2e_step(i)
+    e2e_steps = args.steps
+    e2e_ms = time_steps(torch, e2e_step, e2e_steps) / e2e_steps
+    h2d = q_host.numel() * 2 + knew_host.numel() * 2 + vnew_host.numel() * 2
+    d2h = out_host.numel() * 4
+    e2e = {"value": alg_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+           "what": "q + the new token's K/V rows copied from pinned host memory, attn_decode through the C ABI, "
+                   "output copied back and the stream synchronised every step; the KV cache itself stays resident "
+                   "in HBM, as the engine's per-layer cache does"}
+
+    extra = {}
+    # ---- the same call with NOTHING resident: whole KV cache copied from pinned host memory every step
+    try:
+        k_host = ks[0].cpu().pin_memory()
+        v_host = vs[0].cpu().pin_memory()
+
+        def cold_step(i):
+            q_dev.copy_(q_host, non_blocking=True)
+            ks[1].copy_(k_host, non_blocking=True)
+            vs[1].copy_(v_host, non_blocking=True)
+            attention.attn_decode(q_dev, ks[1], vs[1], out=out, workspace=ws)
+            out_host.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        cold_step(0)
+        n_cold = min(args.steps, 5)
+        cold_ms = time_steps(torch, cold_step, n_cold) / n_cold
+        extra["e2e_cold_cache"] = {"value": alg_bytes / (cold_ms * 1e-3) / 1e9, "unit": "GB/s",
+                                   "ms_per_step": cold_ms,
+                                   "h2d_bytes_per_step": h2d - 2 * knew_host.numel() * 2 + 2 * k_host.numel() * 2,
+                                   "what": "whole KV cache copied host->device every step (PCIe-bound)"}
+        del k_host, v_host
+    except Exception as e:  # host memory for pinning may be short on some boxes; the headline does not depend on it
+        extra["e2e_cold_cache"] = {"error": str(e)[:200]}
+
+    # ---- KV-length sweep of the metric (B = 1 and 16), 4K .. 128K
+    del ks, vs
+    torch.cuda.empty_cache()
+    sweep = []
+    Tmax = 131072
+    kbig = torch.randn((16, Tmax, Hkv, D), generator=gen, device=dev, dtype=torch.float16)
+    vbig = torch.randn((16, Tmax, Hkv, D), generator=gen, device=dev, dtype=torch.float16)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    for b in (1, 16):
+        ws_b = attention.DecodeWorkspace(b, H, Hkv, D, dev)
+        out_b = torch.empty((b, H, D), dtype=torch.float32, device=dev)
+        for t in (4096, 8192, 16384, 32768, 65536, 131072):
+            s = wl.DecodeShape("sweep", 1, b, H, Hkv, D, t, "f16", "f16")
+            kv_bytes = s.kv_bytes
+            reps = 5
+            best = None
+            starts = [torch.cuda.Event(enable_timing=True) for _ in range(reps)]
+            ends = [torch.cuda.Event(enable_timing=True) for _ in range(reps)]
+            for r in range(reps + 2):
+                if kv_bytes < 400e6:
+                    flush.zero_()  # working set smaller than ~3x L2: flush L2 between iterations
+                if r >= 2:
+                    starts[r - 2].record()
+                attention.attn_decode(qs[0][:b], kbig[:b], vbig[:b], t, out=out_b, workspace=ws_b)
+                if r >= 2:
+                    ends[r - 2].record()
+            torch.cuda.synchronize()
+            times = sorted(starts[i].elapsed_time(ends[i]) for i in range(reps))
+            med = times[reps // 2]
+            best = times[0]
+            sweep.append({"batch": b, "kv_len": t, "us": round(med * 1e3, 2), "us_best": round(best * 1e3, 2),
+                          "gbs": round(s.algorithmic_bytes() / (med * 1e-3) / 1e9, 1),
+                          "frac_of_peak": round(s.algorithmic_bytes() / (med * 1e-3) / 1e9 / hbm_peak, 3),
+                          "tok_per_s": round(b / (med * 1e-3), 1)})
+    extra["kv_sweep"] = {"timing": "median of 5 single calls, CUDA events, L2 flushed when KV < 400 MB",
+                         "points": sweep}
+    del kbig, vbig, flush
+
+    # ---- CPU baseline on the host cores of this box (bounded sample)
+    try:
+        _, cpu_desc, _ = cpu_reference_arm(wl, shape, steps=200, warmup=2, seconds_budget=15.0)
+        cpu_baseline = {k: cpu_desc[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    except Exception as e:
+        cpu_baseline = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"[:200]}
+
+    line = {
+        "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+        "config": {**workload_config(shape, 1),
+                   "l2": f"inputs {shape.kv_bytes >> 20} MiB per step > 126 MB L2, {n_sets} input copies rotated"},
+        "tok_per_s": B / (ms_per_step * 1e-3),
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"of {peak_kind}",
+                     "frac_of_nominal_8tbs": gbs / 8000.0, "algorithmic_bytes_per_launch": alg_bytes,
+                     "note": "duration = CUDA-event time of one step (split pass + merge pass) / steps"},
+        "cpu_baseline": cpu_baseline,
+        "e2e": e2e,
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+        "extra": extra,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- our arm, N GPUs
+def run_multi(args, world: int, rank: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+
+    pkg = load_package()
+    from llm_infer_b200 import attention
+    from llm_infer_b200.sharded import ShardedDecode, shard_rows
+    wl = pkg.workloads
+    shape = wl.C4
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    hbm_peak, _, peak_kind = measured_peaks()
+    H, Hkv, D, T = shape.n_heads, shape.n_kv_heads, shape.head_dim, shape.kv_len
+    r0, r1 = shard_rows(T, world, rank)
+    rows = r1 - r0
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(shape.seed)  # same seed on every rank: Q is replicated
+    q = torch.randn((1, H, D), generator=gen, device=dev, dtype=torch.float32).half()
+    gen.manual_seed(shape.seed * 1000 + rank + 1)
+    # rotate over enough copies of the shard that a step never finds its rows in L2
+    n_sets = max(2, min(8, int(400e6 // (2 * rows * Hkv * D * 2)) + 1))
+    ks = [torch.randn((1, rows, Hkv, D), generator=gen, device=dev, dtype=torch.float16) for _ in range(n_sets)]
+    vs = [torch.randn((1, rows, Hkv, D), generator=gen, device=dev, dtype=torch.float16) for _ in range(n_sets)]
+    op = ShardedDecode(H, D, device=dev)
+    op.use_workspace(attention.DecodeWorkspace(1, H, Hkv, D, dev))
+    out = torch.empty((H, D), dtype=torch.float32, device=dev)
+
+    def step(i):
+        j = i % n_sets
+        op(q, ks[j], vs[j], out=out)
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    launches0 = attention.kernel_launch_count()
+    with ClockSampler(local_rank) as clocks:
+        dist.barrier()
+        ms = time_steps(torch, step, args.steps)
+    launches = attention.kernel_launch_count() - launches0
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+
+    # itemised: local decode only / all-gather only / merge only (each timed alone, max over ranks)
+    def timed(fn, n=50):
+        for i in range(3):
+            fn(i)
+        dist.barrier()
+        x = torch.tensor([time_steps(torch, fn, n) / n], device=dev)
+        dist.all_reduce(x, op=dist.ReduceOp.MAX)
+        return float(x.item())
+
+    parts = {"local_decode_us": 1e3 * timed(lambda i: op.local_partial(q, ks[i % n_sets], vs[i % n_sets])),
+             "all_gather_us": 1e3 * timed(lambda i: op.gather()),
+             "merge_us": 1e3 * timed(lambda i: op.merge(out=out))}
+
+    # end to end with host buffers: q from pinned host memory, result read back, every step
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty((H, D), dtype=torch.float32).pin_memory()
+    q_dev = torch.empty_like(q)
+
+    def e2e_step(i):
+        j = i % n_sets
+        q_dev.copy_(q_host, non_blocking=True)
+        op(q_dev, ks[j], vs[j], out=out)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    dist.barrier()
+    x = torch.tensor([time_steps(torch, e2e_step, args.steps) / args.steps], device=dev)
+    dist.all_reduce(x, op=dist.ReduceOp.MAX)
+    e2e_ms = float(x.item())
+
+    alg_bytes = shape.algorithmic_bytes(o_bytes=4)
+    gbs = alg_bytes / (ms_per_step * 1e-3) / 1e9
+    if rank == 0:
+        line = {
+            "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+            "config": {**workload_config(shape, world),
+                       "l2": f"{rows * Hkv * D * 4 >> 20} MiB of KV per GPU per step, {n_sets} copies rotated"},
+            "tok_per_s": 1.0 / (ms_per_step * 1e-3),
+            "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": gbs / world / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "note": "per GPU: algorithmic bytes / N / step time (local decode + all-gather + merge)"},
+            "e2e": {"value": alg_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": q.numel() * 2,
+                    "d2h_bytes_per_step": H * D * 4, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+            "extra": {"breakdown": parts},
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, max(world, args.gpus), rank)
+        return
+    if world == 1 and args.gpus == 1:
+        run_single(args)
+    elif world > 1:
+        run_multi(args, world, rank, local_rank)
+    else:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
+
+
+if __name__ == "__main__":
+    main()

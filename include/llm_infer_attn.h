@@ -1,0 +1,127 @@
+/*
+ * C ABI of the B200 (sm_100a) attention path for the llm-infer engine.
+ *
+ * The engine's CUDA backend declares one attention entry point,
+ *
+ *     __global__ void attention(float* o, const float* q, const half* k,
+ *                               const half* v, uint32_t kv_tokens);
+ *                                                   (include/kernels.cuh:26)
+ *
+ * which no translation unit of the engine defines; its transformer block adds
+ * that symbol to a CUDA graph as a kernel node (src/model/block.cu:207-233,
+ * include/model/device.hpp:239-247). This library supplies that symbol (see
+ * include/kernels_b200.cuh) and, for everything a five-argument kernel cannot
+ * express (batches, dtypes, ragged lengths, causal prefill, KV sharded over
+ * several GPUs), the host functions below.
+ *
+ * Conventions of every function here:
+ *   - returns ATTN_OK (0) or a negative ATTN_ERR_* code; never throws;
+ *   - allocates nothing, frees nothing and never synchronises the device: work
+ *     is only enqueued on the stream that is passed in (a cudaStream_t, passed as
+ *     void* so that this header needs no CUDA include);
+ *   - the caller owns every buffer, as the engine's Tensor<T> does
+ *     (include/model/tensor.hpp:29-44);
+ *   - K/V caches keep the engine's layout: 16-bit elements,
+ *     [row][kv_head][head_dim], one cache per sequence
+ *     (include/model/block.hpp:66-67, src/model/block.cpp:71-74);
+ *   - results match the engine's CPU attention, attn() in
+ *     include/kernels_cpu.hpp:140-167 driven per head as in
+ *     src/model/block.cpp:157-164, to 2e-3 absolute / 1e-2 relative.
+ */
+#ifndef LLM_INFER_ATTN_H
+#define LLM_INFER_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    ATTN_OK = 0,
+    ATTN_ERR_INVALID_ARG = -1,  /* null pointer, zero dimension, n_heads % n_kv_heads != 0 ... */
+    ATTN_ERR_UNSUPPORTED = -2,  /* head_dim / group size / dtype combination with no kernel */
+    ATTN_ERR_ALIGNMENT = -3,    /* pointer or stride not 16-byte aligned */
+    ATTN_ERR_WORKSPACE = -4,    /* workspace missing or smaller than attn_*_workspace_bytes() */
+    ATTN_ERR_CUDA = -5,         /* a CUDA runtime call failed; see attn_last_cuda_error() */
+    ATTN_ERR_DEVICE = -6        /* not an sm_100 device */
+};
+
+enum { ATTN_DTYPE_F32 = 0, ATTN_DTYPE_F16 = 1, ATTN_DTYPE_BF16 = 2 };
+
+/* Bits of the optional device status word (AttnDecodeArgs.status etc.). A kernel
+ * ORs a bit in and returns early instead of spinning for ever or trapping. */
+enum {
+    ATTN_STATUS_OK = 0u,
+    ATTN_STATUS_WAIT_TIMEOUT = 1u, /* a bounded wait on a shared-memory barrier ran out */
+    ATTN_STATUS_BAD_SHAPE = 2u     /* device-side shape check failed */
+};
+
+/* Single-token (decode) attention over the KV cache. Replaces the per-head
+ * attn() loop of src/model/block.cpp:157-164 for a whole batch at once. */
+typedef struct AttnDecodeArgs {
+    void* o;       /* out: [batch][n_heads][head_dim], o_dtype */
+    const void* q; /* in : [batch][n_heads][head_dim], q_dtype (already RoPE'd) */
+    const void* k; /* in : kv_dtype, sequence b at k + b*kv_batch_stride, row t at + t*kv_row_stride */
+    const void* v; /* in : same geometry as k */
+    float* lse;    /* optional out: [batch][n_heads] natural-log sum-exp of the scaled scores
+                      (-inf for an empty sequence); NULL to skip */
+    int32_t o_dtype;  /* ATTN_DTYPE_F32 | F16 | BF16 */
+    int32_t q_dtype;  /* ATTN_DTYPE_F32 | F16 | BF16 */
+    int32_t kv_dtype; /* ATTN_DTYPE_F16 | BF16 */
+    uint32_t batch;
+    uint32_t n_heads;
+    uint32_t n_kv_heads;
+    uint32_t head_dim;       /* 64 or 128 */
+    const uint32_t* kv_len;  /* device pointer [batch], valid rows per sequence; NULL = kv_len_uniform for all */
+    uint32_t kv_len_uniform; /* used when kv_len == NULL */
+    uint64_t kv_row_stride;   /* elements between rows; 0 = n_kv_heads*head_dim */
+    uint64_t kv_batch_stride; /* elements between sequences; may be 0 only when batch == 1 */
+    float scale;              /* 0 = 1/sqrt(head_dim), as kernels_cpu.hpp:152 */
+    uint32_t max_ctas;        /* upper bound on the CTAs that share the KV rows; 0 = auto */
+    void* workspace;          /* device scratch, >= attn_decode_workspace_bytes(), 16-byte aligned */
+    size_t workspace_bytes;
+    uint32_t* status; /* optional device word, ATTN_STATUS_* bits are ORed in; NULL to skip */
+} AttnDecodeArgs;
+
+/* Scratch size for attn_decode with these dimensions on the current device. */
+size_t attn_decode_workspace_bytes(uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim);
+
+/* Enqueue: split-KV pass (per-CTA partial O and LSE) + merge pass. */
+int attn_decode(const AttnDecodeArgs* args, void* stream);
+
+/* Merge of n partial results with the engine's online-softmax state merge
+ * (src/attention.cu:41-65) in log-sum-exp form:
+ *   out[r] = sum_i w_i * part_o[i][r],  w_i = exp(lse_i[r] - LSE[r]),  LSE = logsumexp_i lse_i[r]
+ * for r over rows (= batch * n_heads). Used after an all-gather of per-GPU
+ * partials when the KV sequence is sharded across GPUs. A row whose partials
+ * are all empty (lse = -inf) yields zeros. */
+typedef struct AttnMergeArgs {
+    void* o;               /* out: [rows][head_dim], o_dtype */
+    float* lse;            /* optional out: [rows] */
+    const float* part_o;   /* partial i, row r at part_o + i*o_part_stride + r*head_dim; 16-byte aligned */
+    const float* part_lse; /* partial i, row r at part_lse + i*lse_part_stride + r */
+    uint64_t o_part_stride;   /* floats, multiple of 4 */
+    uint64_t lse_part_stride; /* floats */
+    uint32_t n_parts;
+    uint32_t rows;
+    uint32_t head_dim; /* 32, 64, 128 or 256 */
+    int32_t o_dtype;
+} AttnMergeArgs;
+
+int attn_merge(const AttnMergeArgs* args, void* stream);
+
+/* Human-readable text for an ATTN_ERR_* code. */
+const char* attn_status_string(int code);
+
+/* cudaError_t (as int) of the last failed CUDA call made by this library on the calling thread. */
+int attn_last_cuda_error(void);
+
+/* Number of kernels this library has launched from this process (for accounting in benchmarks). */
+uint64_t attn_kernel_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLM_INFER_ATTN_H */

@@ -1,0 +1,140 @@
+"""Host-side mirror of the engine's attention interface, over the C ABI.
+
+The engine calls ``attn(out, scores, q, k_cache, v_cache, group, head_dim,
+n_kv_heads, kv_len)`` once per query head (include/kernels_cpu.hpp:140-167,
+src/model/block.cpp:157-164). The functions here take the same operands — fp32 /
+fp16 / bf16 ``q``, 16-bit K/V caches laid out ``[row][kv_head][head_dim]``,
+``kv_len`` valid rows — for a whole batch and all heads at once, and run them on
+the GPU through ``libllm_infer_attn.so``. PyTorch is used only to hold device
+memory and streams; no computation falls back to it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import binding as _b
+
+_DTYPES = {torch.float32: _b.DTYPE_F32, torch.float16: _b.DTYPE_F16, torch.bfloat16: _b.DTYPE_BF16}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+def _stream_ptr(stream) -> int:
+    s = torch.cuda.current_stream() if stream is None else stream
+    return s.cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("attention operands must be CUDA tensors (there is no CPU path)")
+
+
+class DecodeWorkspace:
+    """Scratch for the split-KV pass (per-CTA partial O and LSE), reusable across calls of one shape."""
+
+    def __init__(self, batch: int, n_heads: int, n_kv_heads: int, head_dim: int, device=None):
+        lib = _b.load()
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        with torch.cuda.device(device):
+            nbytes = lib.attn_decode_workspace_bytes(batch, n_heads, n_kv_heads, head_dim)
+        if nbytes == 0:
+            raise _b.AttnError(-2, f"no decode kernel for batch={batch} heads={n_heads}/{n_kv_heads} dim={head_dim}")
+        self.key = (batch, n_heads, n_kv_heads, head_dim, device.index)
+        self.nbytes = int(nbytes)
+        self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len=None, *, out=None, lse=None,
+                out_dtype=torch.float32, scale: float = 0.0, workspace: DecodeWorkspace | None = None,
+                max_ctas: int = 0, stream=None) -> torch.Tensor:
+    """Single-token attention of every query head over its sequence's KV cache.
+
+    q        [B, H, D]        fp32 / fp16 / bf16, already rotated
+    k_cache  [B, T, Hkv, D]   fp16 / bf16; only the last dim must be dense, rows and sequences may be strided
+    v_cache  same geometry as k_cache
+    kv_len   None (all T rows valid), an int, or an int32/uint32 CUDA tensor [B]
+    returns  out [B, H, D] in out_dtype; fills ``lse`` [B, H] (fp32) when given
+    """
+    _require_cuda(q, k_cache, v_cache)
+    lib = _b.load()
+    B, H, D = q.shape
+    Bk, T, Hkv, Dk = k_cache.shape
+    if (Bk, Dk) != (B, D) or v_cache.shape != k_cache.shape:
+        raise ValueError("shape mismatch between q and the caches")
+    if k_cache.dtype != v_cache.dtype or k_cache.stride() != v_cache.stride():
+        raise ValueError("K and V caches must share dtype and strides")
+    if k_cache.stride(3) != 1 or k_cache.stride(2) != D:
+        raise ValueError("cache layout must be [row][kv_head][head_dim] with dense heads")
+    q = q.contiguous()
+    if out is None:
+        out = torch.empty((B, H, D), dtype=out_dtype, device=q.device)
+    elif out.shape != (B, H, D) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [B, H, D] tensor")
+    if workspace is None or workspace.key != (B, H, Hkv, D, q.device.index):
+        workspace = DecodeWorkspace(B, H, Hkv, D, q.device)
+
+    a = _b.AttnDecodeArgs()
+    a.o, a.q, a.k, a.v = out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.o_dtype, a.q_dtype, a.kv_dtype = _dtype_code(out), _dtype_code(q), _dtype_code(k_cache)
+    a.batch, a.n_heads, a.n_kv_heads, a.head_dim = B, H, Hkv, D
+    if kv_len is None:
+        a.kv_len, a.kv_len_uniform = None, T
+    elif isinstance(kv_len, int):
+        if kv_len > T:
+            raise ValueError("kv_len exceeds the cache")
+        a.kv_len, a.kv_len_uniform = None, kv_len
+    else:
+        if kv_len.dtype not in (torch.int32, torch.uint32) or kv_len.shape != (B,) or not kv_len.is_cuda:
+            raise ValueError("kv_len must be an int32 CUDA tensor of shape [B]")
+        a.kv_len, a.kv_len_uniform = kv_len.data_ptr(), 0
+    a.kv_row_stride = k_cache.stride(1)
+    a.kv_batch_stride = k_cache.stride(0) if B > 1 else max(k_cache.stride(0), 0)
+    a.scale = float(scale)
+    a.max_ctas = int(max_ctas)
+    a.workspace, a.workspace_bytes = workspace.buf.data_ptr(), workspace.nbytes
+    a.status = workspace.status.data_ptr()
+    with torch.cuda.device(q.device):
+        _b.check(lib.attn_decode(C.byref(a), _stream_ptr(stream)), "attn_decode")
+    return out
+
+
+def attn_merge(part_o: torch.Tensor, part_lse: torch.Tensor, *, out=None, lse=None, out_dtype=torch.float32,
+               stream=None) -> torch.Tensor:
+    """Online-softmax merge of partial results (src/attention.cu:41-65 in log-sum-exp form).
+
+    part_o   [n, rows, D] fp32 (partials may be strided in dim 0), part_lse [n, rows] fp32
+    returns  out [rows, D]
+    """
+    _require_cuda(part_o, part_lse)
+    lib = _b.load()
+    n, rows, D = part_o.shape
+    if part_lse.shape != (n, rows) or part_o.dtype != torch.float32 or part_lse.dtype != torch.float32:
+        raise ValueError("part_o must be fp32 [n, rows, D] and part_lse fp32 [n, rows]")
+    if part_o.stride(2) != 1 or part_o.stride(1) != D or part_lse.stride(1) != 1:
+        raise ValueError("rows of a partial must be dense")
+    if out is None:
+        out = torch.empty((rows, D), dtype=out_dtype, device=part_o.device)
+    a = _b.AttnMergeArgs()
+    a.o = out.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.part_o, a.part_lse = part_o.data_ptr(), part_lse.data_ptr()
+    a.o_part_stride = part_o.stride(0) if n > 1 else rows * D
+    a.lse_part_stride = part_lse.stride(0) if n > 1 else rows
+    a.n_parts, a.rows, a.head_dim, a.o_dtype = n, rows, D, _dtype_code(out)
+    with torch.cuda.device(part_o.device):
+        _b.check(lib.attn_merge(C.byref(a), _stream_ptr(stream)), "attn_merge")
+    return out
+
+
+def kernel_launch_count() -> int:
+    return int(_b.load().attn_kernel_launch_count())

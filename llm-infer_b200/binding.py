@@ -1,0 +1,138 @@
+"""ctypes binding of include/llm_infer_attn.h. No torch types cross this boundary:
+pointers are integers (``tensor.data_ptr()``), the stream is ``cudaStream_t`` as an integer.
+
+The library is mandatory: if it is missing or cannot be loaded this module raises;
+there is no CPU or PyTorch fallback anywhere in the package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libllm_infer_attn.so")
+
+ATTN_OK = 0
+DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
+STATUS_WAIT_TIMEOUT = 1
+STATUS_BAD_SHAPE = 2
+
+# every symbol include/llm_infer_attn.h declares
+EXPORTED_SYMBOLS = (
+    "attn_decode_workspace_bytes",
+    "attn_decode",
+    "attn_merge",
+    "attn_status_string",
+    "attn_last_cuda_error",
+    "attn_kernel_launch_count",
+)
+# include/kernels_b200.cuh
+SYMBOL_HELPERS = (
+    "attention_workspace_bytes",
+    "attention_configure",
+    "attention_launch_dims",
+    "attention_kernel_function",
+    "attention_graph_add_node",
+    "attention_graph_exec_update",
+    "attention_launch",
+)
+
+
+class AttnDecodeArgs(C.Structure):
+    _fields_ = [
+        ("o", C.c_void_p),
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("o_dtype", C.c_int32),
+        ("q_dtype", C.c_int32),
+        ("kv_dtype", C.c_int32),
+        ("batch", C.c_uint32),
+        ("n_heads", C.c_uint32),
+        ("n_kv_heads", C.c_uint32),
+        ("head_dim", C.c_uint32),
+        ("kv_len", C.c_void_p),
+        ("kv_len_uniform", C.c_uint32),
+        ("kv_row_stride", C.c_uint64),
+        ("kv_batch_stride", C.c_uint64),
+        ("scale", C.c_float),
+        ("max_ctas", C.c_uint32),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+        ("status", C.c_void_p),
+    ]
+
+
+class AttnMergeArgs(C.Structure):
+    _fields_ = [
+        ("o", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("part_o", C.c_void_p),
+        ("part_lse", C.c_void_p),
+        ("o_part_stride", C.c_uint64),
+        ("lse_part_stride", C.c_uint64),
+        ("n_parts", C.c_uint32),
+        ("rows", C.c_uint32),
+        ("head_dim", C.c_uint32),
+        ("o_dtype", C.c_int32),
+    ]
+
+
+class AttnError(RuntimeError):
+    def __init__(self, code: int, what: str, cuda_error: int = 0):
+        self.code = code
+        self.cuda_error = cuda_error
+        extra = f" (cudaError {cuda_error})" if cuda_error else ""
+        super().__init__(f"{what}: {code}{extra}")
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library (once). Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(
+            f"{LIB_PATH} is missing: build it with `python llm-infer_b200/build.py` "
+            "(this package has no fallback path)")
+    lib = C.CDLL(LIB_PATH)
+    lib.attn_decode_workspace_bytes.restype = C.c_size_t
+    lib.attn_decode_workspace_bytes.argtypes = [C.c_uint32] * 4
+    lib.attn_decode.restype = C.c_int
+    lib.attn_decode.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
+    lib.attn_merge.restype = C.c_int
+    lib.attn_merge.argtypes = [C.POINTER(AttnMergeArgs), C.c_void_p]
+    lib.attn_status_string.restype = C.c_char_p
+    lib.attn_status_string.argtypes = [C.c_int]
+    lib.attn_last_cuda_error.restype = C.c_int
+    lib.attn_kernel_launch_count.restype = C.c_uint64
+    # include/kernels_b200.cuh: the engine's kernel symbol and its helpers
+    lib.attention_workspace_bytes.restype = C.c_size_t
+    lib.attention_workspace_bytes.argtypes = [C.c_uint32] * 3
+    lib.attention_configure.restype = C.c_int
+    lib.attention_configure.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p, C.c_size_t,
+                                        C.c_void_p]
+    lib.attention_launch_dims.restype = C.c_int
+    lib.attention_launch_dims.argtypes = [C.POINTER(C.c_uint32)] * 3
+    lib.attention_kernel_function.restype = C.c_void_p
+    lib.attention_graph_add_node.restype = C.c_int
+    lib.attention_graph_add_node.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p,
+                                             C.c_void_p, C.c_void_p, C.c_uint32]
+    lib.attention_graph_exec_update.restype = C.c_int
+    lib.attention_graph_exec_update.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                C.c_void_p, C.c_uint32]
+    lib.attention_launch.restype = C.c_int
+    lib.attention_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str) -> None:
+    if code != ATTN_OK:
+        lib = load()
+        msg = lib.attn_status_string(code).decode()
+        raise AttnError(code, f"{what}: {msg}", lib.attn_last_cuda_error() if code == -5 else 0)

@@ -1,0 +1,98 @@
+// Launchers of the split-KV decode pass (kernel body: decode_body.cuh) and the
+// planning of its shared memory, grid and workspace.
+#include "decode_body.cuh"
+
+namespace b200 {
+
+namespace {
+
+using decode_detail::kConsumerWarps;
+using decode_detail::kThreads;
+
+template <int D, int HPC, bool QSPLIT, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const __grid_constant__ DecodeParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    decode_detail::decode_split_body<D, HPC, QSPLIT, BF16, false>(p, smem);
+}
+
+template <int D, int HPC, bool QSPLIT, bool BF16>
+int launch_one(const DecodeParams& p, uint32_t grid, size_t smem_bytes, cudaStream_t stream) {
+    auto kernel = decode_split_kernel<D, HPC, QSPLIT, BF16>;
+    B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem_bytes)));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return ATTN_OK;
+}
+
+template <int D, bool QSPLIT, bool BF16>
+int launch_hpc(const DecodeParams& p, uint32_t hpc, uint32_t grid, size_t smem_bytes, cudaStream_t stream) {
+    switch (hpc) {
+        case 8: return launch_one<D, 8, QSPLIT, BF16>(p, grid, smem_bytes, stream);
+        case 4: return launch_one<D, 4, QSPLIT, BF16>(p, grid, smem_bytes, stream);
+        case 2: return launch_one<D, 2, QSPLIT, BF16>(p, grid, smem_bytes, stream);
+        case 1: return launch_one<D, 1, QSPLIT, BF16>(p, grid, smem_bytes, stream);
+        default: return ATTN_ERR_UNSUPPORTED;
+    }
+}
+
+template <int D>
+int launch_d(const DecodeParams& p, uint32_t hpc, bool qsplit, bool kv_bf16, uint32_t grid, size_t smem_bytes,
+             cudaStream_t stream) {
+    if (kv_bf16) {
+        // bf16 MMA operands: Q and P always carry a residual term (8-bit significand otherwise)
+        return launch_hpc<D, true, true>(p, hpc, grid, smem_bytes, stream);
+    }
+    return qsplit ? launch_hpc<D, true, false>(p, hpc, grid, smem_bytes, stream)
+                  : launch_hpc<D, false, false>(p, hpc, grid, smem_bytes, stream);
+}
+
+}  // namespace
+
+int launch_decode_split(const DecodeParams& p, uint32_t head_dim, uint32_t hpc, bool qsplit, bool kv_bf16,
+                        uint32_t grid, size_t smem_bytes, cudaStream_t stream) {
+    switch (head_dim) {
+        case 128: return launch_d<128>(p, hpc, qsplit, kv_bf16, grid, smem_bytes, stream);
+        case 64: return launch_d<64>(p, hpc, qsplit, kv_bf16, grid, smem_bytes, stream);
+        default: return ATTN_ERR_UNSUPPORTED;
+    }
+}
+
+int make_decode_plan(uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, const DeviceInfo& dev,
+                     DecodePlan* plan) {
+    if (batch == 0 || n_heads == 0 || n_kv_heads == 0 || n_heads % n_kv_heads != 0) return ATTN_ERR_INVALID_ARG;
+    if (head_dim != 64 && head_dim != 128) return ATTN_ERR_UNSUPPORTED;
+    DecodePlan pl{};
+    pl.group = n_heads / n_kv_heads;
+    if (pl.group > 16) return ATTN_ERR_UNSUPPORTED;
+    pl.hpc = (n_kv_heads % 8 == 0) ? 8 : (n_kv_heads % 4 == 0) ? 4 : (n_kv_heads % 2 == 0) ? 2 : 1;
+    pl.ts = kConsumerWarps / pl.hpc;
+    pl.tile_rows = 16 * pl.ts;
+    pl.head_groups = n_kv_heads / pl.hpc;
+    uint64_t nseg = static_cast<uint64_t>(batch) * pl.head_groups;
+    if (nseg > 32768) return ATTN_ERR_UNSUPPORTED;
+    pl.nseg = static_cast<uint32_t>(nseg);
+    pl.grid = static_cast<uint32_t>(dev.sm_count);
+    const size_t tile_bytes = static_cast<size_t>(pl.tile_rows) * (static_cast<size_t>(pl.hpc) * head_dim * 2 + 16);
+    const size_t fixed = static_cast<size_t>(pl.nseg + 1) * 4 + 128;
+    size_t budget = static_cast<size_t>(dev.max_smem_optin);
+    if (budget < fixed + 2 * (2 * tile_bytes + 24)) return ATTN_ERR_UNSUPPORTED;
+    size_t nst = (budget - fixed) / (2 * tile_bytes + 24);
+    if (nst > 8) nst = 8;
+    pl.nstages = static_cast<uint32_t>(nst);
+    pl.smem_bytes = nst * (2 * tile_bytes + 24) + fixed;
+    const size_t slots = static_cast<size_t>(pl.grid) + pl.nseg;
+    const size_t rows = slots * pl.ts * pl.hpc * pl.group;
+    pl.part_o_floats = rows * head_dim;
+    pl.part_lse_floats = (rows + 3) & ~static_cast<size_t>(3);
+    pl.workspace_bytes = (pl.part_o_floats + pl.part_lse_floats) * 4 + ((static_cast<size_t>(pl.nseg) + 1 + 3) & ~3ull) * 4;
+    *plan = pl;
+    return ATTN_OK;
+}
+
+}  // namespace b200

@@ -1,0 +1,146 @@
+// Declarations shared by the translation units of libllm_infer_attn.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+
+#include "../../include/llm_infer_attn.h"
+
+namespace b200 {
+
+// ----------------------------------------------------------------------------
+// Split-KV decode: how the KV rows are divided.
+//
+// A "segment" is one (sequence, kv-head group) pair; a head group is HPC
+// consecutive kv heads that one CTA streams together (their slices of a cache
+// row are contiguous, so one bulk copy fetches them all). A segment is cut
+// into tiles of TT = 16 * (8 / HPC) rows. All tiles of all segments form one
+// flat list of NT tiles; CTA c of A active CTAs owns tiles
+// [c*NT/A, (c+1)*NT/A). For every segment it touches, each of its 8 warps
+// writes one partial (normalised O, LSE) into slot (c + s) * TS + ts, where s
+// is the segment index and ts the warp's row sub-tile. Because both c and s
+// only grow along the flat list, c + s is unique per (CTA, segment) pair and
+// the slots of one segment are consecutive, which is what the merge pass reads.
+// ----------------------------------------------------------------------------
+struct DecodeParams {
+    const void* q;
+    const uint16_t* k;
+    const uint16_t* v;
+    float* part_o;         // [slots*TS][HPC][G][D]
+    float* part_lse;       // [slots*TS][HPC][G]
+    uint32_t* seg_prefix;  // [nseg+1] tile prefix written by CTA 0 when lengths are ragged
+    const uint32_t* kv_len;
+    uint32_t kv_len_uniform;
+    uint32_t batch;
+    uint32_t n_heads;
+    uint32_t n_kv_heads;
+    uint32_t group;        // G = n_heads / n_kv_heads
+    uint32_t head_groups;  // n_kv_heads / HPC
+    uint64_t kv_row_stride;
+    uint64_t kv_batch_stride;
+    float scale_log2;  // softmax scale * log2(e)
+    int32_t q_dtype;
+    uint32_t max_ctas;
+    uint32_t min_tiles_per_cta;
+    uint32_t nstages;
+    uint32_t* status;
+    // single-launch (fused merge) mode only: final output and per-segment arrival counters
+    void* o;
+    float* lse;
+    int32_t o_dtype;
+    uint32_t* counters;  // [nseg], zero before the first launch; the kernel leaves them zero
+};
+
+struct MergeParams {
+    void* o;
+    float* lse;
+    const float* part_o;
+    const float* part_lse;
+    uint64_t o_part_stride;
+    uint64_t lse_part_stride;
+    uint32_t n_parts;
+    uint32_t rows;
+    uint32_t head_dim;
+    int32_t o_dtype;
+    // decode-internal mode (split_grid != 0): partial ranges are derived per row
+    uint32_t split_grid;
+    uint32_t hpc;
+    uint32_t ts;
+    uint32_t tile_rows;
+    uint32_t n_heads;
+    uint32_t group;
+    uint32_t head_groups;
+    uint32_t batch;
+    const uint32_t* kv_len;
+    uint32_t kv_len_uniform;
+    uint32_t max_ctas;
+    uint32_t min_tiles_per_cta;
+    const uint32_t* seg_prefix;
+};
+
+// Number of CTAs that actually take tiles, identical in the split and merge passes.
+__host__ __device__ inline uint32_t active_ctas(uint32_t grid, uint32_t max_ctas, uint32_t min_tiles, uint64_t nt) {
+    uint64_t a = grid;
+    if (max_ctas && max_ctas < a) a = max_ctas;
+    uint64_t by_work = nt / (min_tiles ? min_tiles : 1);
+    if (by_work < 1) by_work = 1;
+    if (by_work < a) a = by_work;
+    return static_cast<uint32_t>(a);
+}
+
+// CTA that owns flat tile t when nt tiles are dealt to a CTAs as [c*nt/a, (c+1)*nt/a).
+__host__ __device__ inline uint32_t cta_of_tile(uint64_t t, uint64_t nt, uint64_t a) {
+    return static_cast<uint32_t>(((t + 1) * a - 1) / nt);
+}
+
+// ----------------------------------------------------------------------------
+// host helpers (attn_api.cu)
+// ----------------------------------------------------------------------------
+extern thread_local int g_last_cuda_error;
+extern std::atomic<uint64_t> g_launch_count;
+
+inline int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = static_cast<int>(e);
+    return ATTN_ERR_CUDA;
+}
+
+#define B200_CUDA_TRY(expr)                                  \
+    do {                                                     \
+        cudaError_t e_ = (expr);                             \
+        if (e_ != cudaSuccess) return ::b200::cuda_fail(e_); \
+    } while (0)
+
+struct DeviceInfo {
+    int device;
+    int sm_count;
+    int cc_major;
+    int max_smem_optin;
+};
+// Properties of the current device (cached per device; no allocation).
+int current_device_info(DeviceInfo* out);
+
+int launch_decode_split(const DecodeParams& p, uint32_t head_dim, uint32_t hpc, bool qsplit, bool kv_bf16,
+                        uint32_t grid, size_t smem_bytes, cudaStream_t stream);
+int launch_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch);
+
+// Geometry of the decode split for given dimensions.
+struct DecodePlan {
+    uint32_t hpc;        // kv heads per CTA (8, 4, 2 or 1)
+    uint32_t ts;         // row sub-tiles per head = 8 / hpc
+    uint32_t tile_rows;  // 16 * ts
+    uint32_t group;
+    uint32_t head_groups;
+    uint32_t nseg;
+    uint32_t grid;
+    uint32_t nstages;
+    size_t smem_bytes;
+    size_t part_o_floats;
+    size_t part_lse_floats;
+    size_t workspace_bytes;
+};
+int make_decode_plan(uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, const DeviceInfo& dev,
+                     DecodePlan* plan);
+
+}  // namespace b200

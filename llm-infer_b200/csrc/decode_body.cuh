@@ -1,0 +1,449 @@
+// Split-KV single-token (decode) attention for sm_100a.
+//
+// What it replaces: the per-head attn() loop of the engine's CPU block
+// (include/kernels_cpu.hpp:140-167 called from src/model/block.cpp:157-164) and
+// the unfinished device kernel of src/attention.cu:284-370, whose idea of letting
+// all G query heads of one kv head share each K/V tile is kept. The KV cache
+// layout is the engine's: 16-bit elements, [row][kv_head][head_dim].
+//
+// Shape of the kernel (one persistent CTA per SM, 9 warps):
+//   * warp 8 is the producer. For every tile it issues one bulk asynchronous
+//     copy (TMA engine, untiled form) per cache row: HPC*D*2 contiguous bytes
+//     that hold HPC kv heads, landing in shared memory at a row pitch of
+//     HPC*D*2 + 16 bytes so that ldmatrix reads are bank-conflict free. K and V
+//     of a stage complete on separate mbarriers.
+//   * warps 0..7 are consumers. Warp w owns kv head w / TS of the CTA's head
+//     group and rows [16*(w % TS), +16) of every tile. The G query heads of that
+//     kv head are the (zero-padded) 16 rows of an m16n8k16 tensor-core MMA:
+//     S = Q K^T, online softmax in fp32 with quad shuffles, O += P V.
+//     Q given in fp32 is split into a 16-bit high part and a 16-bit residual so
+//     that the scores keep fp32-level accuracy.
+//   * when the CTA's tile range leaves a segment, every warp normalises its
+//     state and writes one partial (O, LSE); the merge pass (attn_merge.cu)
+//     combines the partials of each head with the online-softmax state merge of
+//     src/attention.cu:41-65.
+//
+// HBM traffic per launch: every K/V byte once (+ the clamped tail rows of the
+// last tile of a segment), Q once per (CTA, segment), partials once.
+#pragma once
+
+#include "attn_internal.cuh"
+#include "merge_device.cuh"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+namespace decode_detail {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+
+struct SegInfo {
+    uint32_t seg;       // segment index = b * head_groups + hg
+    uint32_t b;
+    uint32_t hg;
+    uint32_t len;       // valid rows of sequence b
+    uint32_t tile0;     // flat index of the segment's first tile
+    uint32_t tile_end;  // flat index one past its last tile
+};
+
+template <int TT>
+struct SegTable {
+    const DecodeParams& p;
+    const uint32_t* prefix;  // shared memory, [nseg+1]; unused when lengths are uniform
+    uint32_t tiles_uniform;
+
+    __device__ __forceinline__ SegInfo load(uint32_t seg) const {
+        SegInfo s;
+        s.seg = seg;
+        s.b = seg / p.head_groups;
+        s.hg = seg - s.b * p.head_groups;
+        if (p.kv_len) {
+            s.len = p.kv_len[s.b];
+            s.tile0 = prefix[seg];
+            s.tile_end = prefix[seg + 1];
+        } else {
+            s.len = p.kv_len_uniform;
+            s.tile0 = seg * tiles_uniform;
+            s.tile_end = s.tile0 + tiles_uniform;
+        }
+        return s;
+    }
+    // Segment that contains flat tile t (t < total tiles).
+    __device__ __forceinline__ uint32_t find(uint32_t t, uint32_t nseg) const {
+        if (!p.kv_len) return t / tiles_uniform;
+        uint32_t lo = 0, hi = nseg;  // largest s with prefix[s] <= t  (prefix[nseg] > t)
+        while (hi - lo > 1) {
+            uint32_t mid = (lo + hi) >> 1;
+            if (prefix[mid] <= t) lo = mid; else hi = mid;
+        }
+        return lo;
+    }
+};
+
+__device__ __forceinline__ float load_q(const void* q, int32_t dtype, size_t idx) {
+    if (dtype == ATTN_DTYPE_F32) return reinterpret_cast<const float*>(q)[idx];
+    if (dtype == ATTN_DTYPE_F16) return __half2float(reinterpret_cast<const __half*>(q)[idx]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(q)[idx]);
+}
+
+template <int D, int HPC, bool QSPLIT, bool BF16, bool FUSED>
+__device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigned char* smem) {
+    constexpr int TS = kConsumerWarps / HPC;     // row sub-tiles per kv head
+    constexpr int TT = 16 * TS;                  // rows per tile
+    constexpr int ROWB = HPC * D * 2;            // bytes of one cache row slice (HPC kv heads)
+    constexpr int PITCH = ROWB + 16;             // shared-memory row pitch
+    constexpr int TILEB = TT * PITCH;            // one K (or V) tile
+    constexpr int KC = D / 16;                   // k-chunks of the QK^T contraction
+    constexpr int DN = D / 8;                    // n-tiles of the PV product
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const uint32_t nst = p.nstages;
+    const uint32_t nseg = p.batch * p.head_groups;
+
+    unsigned char* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(nst) * 2 * TILEB);
+    uint32_t* prefix = reinterpret_cast<uint32_t*>(bars + 3 * nst);
+    // fused mode: lengths are uniform, so the prefix area is unused and its first word carries the ticket
+    volatile uint32_t* s_ticket = prefix;
+    const uint32_t bar_full_k = smem_u32(bars);
+    const uint32_t bar_full_v = bar_full_k + 8 * nst;
+    const uint32_t bar_empty = bar_full_v + 8 * nst;
+    const uint32_t tiles_u32 = smem_u32(tiles);
+
+    // The merge pass may be scheduled as soon as every CTA got here; it waits for
+    // this grid to finish before reading the partials.
+    grid_dep_launch_dependents();
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < nst; ++s) {
+            mbar_init(bar_full_k + 8 * s, 1);
+            mbar_init(bar_full_v + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, kConsumerWarps);
+        }
+        mbar_init_fence();
+    }
+
+    // ---- tile prefix over segments (ragged lengths only) --------------------
+    uint64_t nt;
+    uint32_t tiles_uniform = 0;
+    if (p.kv_len) {
+        for (uint32_t s = tid; s < nseg; s += kThreads) {
+            uint32_t len = p.kv_len[s / p.head_groups];
+            prefix[s + 1] = (len + TT - 1) / TT;
+        }
+        if (tid == 0) prefix[0] = 0;
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t carry = 0;
+            for (uint32_t base = 0; base < nseg; base += 32) {
+                uint32_t i = base + lane;
+                uint32_t x = (i < nseg) ? prefix[i + 1] : 0;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    uint32_t y = __shfl_up_sync(0xffffffffu, x, off);
+                    if (lane >= off) x += y;
+                }
+                x += carry;
+                if (i < nseg) prefix[i + 1] = x;
+                carry = __shfl_sync(0xffffffffu, x, 31);
+            }
+        }
+        __syncthreads();
+        nt = prefix[nseg];
+        if (blockIdx.x == 0 && p.seg_prefix) {
+            for (uint32_t s = tid; s <= nseg; s += kThreads) p.seg_prefix[s] = prefix[s];
+        }
+    } else {
+        tiles_uniform = (p.kv_len_uniform + TT - 1) / TT;
+        nt = static_cast<uint64_t>(tiles_uniform) * nseg;
+        __syncthreads();
+    }
+    if (nt == 0) return;
+
+    const uint32_t active = active_ctas(gridDim.x, p.max_ctas, p.min_tiles_per_cta, nt);
+    const uint32_t cta = blockIdx.x;
+    if (cta >= active) return;
+    const uint32_t t_begin = static_cast<uint32_t>(static_cast<uint64_t>(cta) * nt / active);
+    const uint32_t t_end = static_cast<uint32_t>(static_cast<uint64_t>(cta + 1) * nt / active);
+    const uint32_t n_my = t_end - t_begin;
+    if (n_my == 0) return;
+
+    SegTable<TT> table{p, prefix, tiles_uniform};
+    SegInfo seg = table.load(table.find(t_begin, nseg));
+
+    if (warp == kConsumerWarps) {
+        // ===================== producer warp =====================
+        const uint64_t policy = l2_policy_evict_first();
+        for (uint32_t i = 0; i < n_my; ++i) {
+            const uint32_t gt = t_begin + i;
+            while (gt >= seg.tile_end) seg = table.load(seg.seg + 1);
+            const uint32_t st = i % nst;
+            if (i >= nst) {
+                if (!mbar_wait(bar_empty + 8 * st, ((i / nst) - 1) & 1)) {
+                    if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+                    return;
+                }
+            }
+            const uint32_t tok0 = (gt - seg.tile0) * TT;
+            const size_t seq_off = static_cast<size_t>(seg.b) * p.kv_batch_stride + static_cast<size_t>(seg.hg) * (HPC * D);
+            const uint32_t kdst = tiles_u32 + st * 2 * TILEB;
+            const uint32_t vdst = kdst + TILEB;
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar_full_k + 8 * st, TT * ROWB);
+                mbar_arrive_expect_tx(bar_full_v + 8 * st, TT * ROWB);
+            }
+            __syncwarp();
+            // Rows past the end of the sequence re-read its last valid row: the
+            // tile is always full (constant byte count) and always finite; those
+            // rows are masked to probability zero by the consumers.
+#pragma unroll
+            for (int j = lane; j < TT; j += 32) {
+                uint32_t row = tok0 + j;
+                row = row < seg.len ? row : seg.len - 1;
+                const uint16_t* src = p.k + seq_off + static_cast<size_t>(row) * p.kv_row_stride;
+                bulk_g2s(kdst + j * PITCH, src, ROWB, bar_full_k + 8 * st, policy);
+            }
+#pragma unroll
+            for (int j = lane; j < TT; j += 32) {
+                uint32_t row = tok0 + j;
+                row = row < seg.len ? row : seg.len - 1;
+                const uint16_t* src = p.v + seq_off + static_cast<size_t>(row) * p.kv_row_stride;
+                bulk_g2s(vdst + j * PITCH, src, ROWB, bar_full_v + 8 * st, policy);
+            }
+        }
+        return;
+    }
+
+    // ===================== consumer warps =====================
+    const int hh = warp / TS;        // kv head within the head group
+    const int ts = warp - hh * TS;   // row sub-tile
+    const int gq = lane >> 2;        // MMA row owned by this lane (and gq + 8)
+    const int cq = lane & 3;
+    const uint32_t G = p.group;
+    const bool ghi = G > 8;          // rows 8..15 of the MMA hold real heads
+
+    // per-lane ldmatrix row addresses inside a tile (stage base added per tile)
+    const uint32_t k_lane_off = (ts * 16 + ((lane >> 4) << 3) + (lane & 7)) * PITCH + hh * (D * 2) + (((lane >> 3) & 1) << 4);
+    const uint32_t v_lane_off = (ts * 16 + (((lane >> 3) & 1) << 3) + (lane & 7)) * PITCH + hh * (D * 2) + ((lane >> 4) << 4);
+
+    uint32_t qhi[KC][4];
+    uint32_t qlo[QSPLIT ? KC : 1][4];
+    float o[DN][4];
+    float m0, m1, l0, l1;  // running max (scaled, log2 domain) and sum for rows gq, gq + 8
+
+    auto begin_segment = [&]() {
+        const size_t head0 = (static_cast<size_t>(seg.b) * p.n_heads + (static_cast<size_t>(seg.hg) * HPC + hh) * G);
+#pragma unroll
+        for (int kc = 0; kc < KC; ++kc) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                // a0:(gq, k) a1:(gq+8, k) a2:(gq, k+8) a3:(gq+8, k+8), k = kc*16 + cq*2 + {0,1}
+                const int row = gq + ((r & 1) << 3);
+                const int col = kc * 16 + cq * 2 + ((r >> 1) << 3);
+                float x0 = 0.f, x1 = 0.f;
+                if (row < static_cast<int>(G)) {
+                    const size_t idx = (head0 + row) * D + col;
+                    x0 = load_q(p.q, p.q_dtype, idx);
+                    x1 = load_q(p.q, p.q_dtype, idx + 1);
+                }
+                qhi[kc][r] = pack2<BF16>(x0, x1);
+                if constexpr (QSPLIT) {
+                    qlo[kc][r] = pack2<BF16>(x0 - round16<BF16>(x0), x1 - round16<BF16>(x1));
+                }
+            }
+        }
+#pragma unroll
+        for (int dn = 0; dn < DN; ++dn) {
+            o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.f;
+        }
+        m0 = m1 = -INFINITY;
+        l0 = l1 = 0.f;
+    };
+
+    auto end_segment = [&]() {
+        // quad-reduce the row sums, normalise, write this warp's partial
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f;
+        const float inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+        const size_t slot = (static_cast<size_t>(cta) + seg.seg) * TS + ts;
+        const size_t row0 = (slot * HPC + hh) * G;
+        constexpr float kLn2 = 0.6931471805599453f;
+        if (gq < static_cast<int>(G)) {
+            float* dst = p.part_o + (row0 + gq) * D + cq * 2;
+#pragma unroll
+            for (int dn = 0; dn < DN; ++dn) {
+                *reinterpret_cast<float2*>(dst + dn * 8) = make_float2(o[dn][0] * inv0, o[dn][1] * inv0);
+            }
+            if (cq == 0) p.part_lse[row0 + gq] = l0 > 0.f ? (m0 + log2f(l0)) * kLn2 : -INFINITY;
+        }
+        if (ghi && gq + 8 < static_cast<int>(G)) {
+            float* dst = p.part_o + (row0 + gq + 8) * D + cq * 2;
+#pragma unroll
+            for (int dn = 0; dn < DN; ++dn) {
+                *reinterpret_cast<float2*>(dst + dn * 8) = make_float2(o[dn][2] * inv1, o[dn][3] * inv1);
+            }
+            if (cq == 0) p.part_lse[row0 + gq + 8] = l1 > 0.f ? (m1 + log2f(l1)) * kLn2 : -INFINITY;
+        }
+    };
+
+    // Fused (single-launch) mode: the CTA that delivers the last partial of a segment merges it.
+    // No CTA ever waits for another: each one adds 1 to the segment's counter after its partials are
+    // visible, and whoever sees the final count does the merge and puts the counter back to zero.
+    auto fused_merge = [&]() {
+        if constexpr (FUSED) {
+            __threadfence();
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (tid == 0) *s_ticket = atomicAdd(p.counters + seg.seg, 1u);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const uint32_t c_first = cta_of_tile(seg.tile0, nt, active);
+            const uint32_t c_last = cta_of_tile(seg.tile_end - 1, nt, active);
+            if (*s_ticket == c_last - c_first) {
+                __threadfence();
+                const uint64_t first_slot = (static_cast<uint64_t>(c_first) + seg.seg) * TS;
+                const uint64_t l_stride = static_cast<uint64_t>(HPC) * G;
+                const uint32_t n = (c_last - c_first + 1) * TS;
+                for (uint32_t r = warp; r < HPC * G; r += kConsumerWarps) {
+                    const uint64_t row0 = first_slot * l_stride + r;  // r = hh * G + g
+                    const size_t out_row = static_cast<size_t>(seg.b) * p.n_heads + static_cast<size_t>(seg.hg) * HPC * G + r;
+                    warp_merge_row<D / 32, 1>(p.part_o + row0 * D, p.part_lse + row0, l_stride * D, l_stride, n, p.o,
+                                              p.o_dtype, p.lse, out_row, lane);
+                }
+                if (tid == 0) p.counters[seg.seg] = 0u;
+            }
+        }
+    };
+
+    begin_segment();
+
+    for (uint32_t i = 0; i < n_my; ++i) {
+        const uint32_t gt = t_begin + i;
+        if (gt >= seg.tile_end) {
+            end_segment();
+            fused_merge();
+            do { seg = table.load(seg.seg + 1); } while (gt >= seg.tile_end);
+            begin_segment();
+        }
+        const uint32_t st = i % nst;
+        const uint32_t par = (i / nst) & 1;
+        const uint32_t kbase = tiles_u32 + st * 2 * TILEB;
+        const uint32_t vbase = kbase + TILEB;
+
+        if (!mbar_wait(bar_full_k + 8 * st, par)) {
+            if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+            return;
+        }
+
+        // ---- S = Q K^T : 16 (heads) x 16 (rows of this sub-tile) ----
+        float s[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int kc = 0; kc < KC; ++kc) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(b0, b1, b2, b3, kbase + k_lane_off + kc * 32);
+            mma_16816<BF16>(s[0], qhi[kc], b0, b1);
+            mma_16816<BF16>(s[1], qhi[kc], b2, b3);
+            if constexpr (QSPLIT) {
+                mma_16816<BF16>(s[0], qlo[kc], b0, b1);
+                mma_16816<BF16>(s[1], qlo[kc], b2, b3);
+            }
+        }
+
+        // ---- scale, mask rows past the sequence end ----
+        const uint32_t tok = (gt - seg.tile0) * TT + ts * 16 + cq * 2;  // row of s[0][0]; s[1][*] is +8
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t r = tok + n * 8 + (e & 1);
+                s[n][e] = r < seg.len ? s[n][e] * p.scale_log2 : -INFINITY;
+            }
+        }
+
+        // ---- online softmax (rows gq and gq + 8) ----
+        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        const float mn0 = fmaxf(m0, mx0);
+        const float ref0 = mn0 == -INFINITY ? 0.f : mn0;
+        const float sc0 = exp2f(m0 - ref0);
+        m0 = mn0;
+        const float p00 = exp2f(s[0][0] - ref0), p01 = exp2f(s[0][1] - ref0);
+        const float p10 = exp2f(s[1][0] - ref0), p11 = exp2f(s[1][1] - ref0);
+        l0 = l0 * sc0 + (p00 + p01 + p10 + p11);
+
+        float sc1 = 1.f;
+        uint32_t pa[4];
+        uint32_t pb[4];  // residual of P when it is split (bf16 only)
+        pa[0] = pack2<BF16>(p00, p01);
+        pa[2] = pack2<BF16>(p10, p11);
+        if constexpr (BF16) {
+            pb[0] = pack2<BF16>(p00 - round16<BF16>(p00), p01 - round16<BF16>(p01));
+            pb[2] = pack2<BF16>(p10 - round16<BF16>(p10), p11 - round16<BF16>(p11));
+        }
+        if (ghi) {
+            float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn1 = fmaxf(m1, mx1);
+            const float ref1 = mn1 == -INFINITY ? 0.f : mn1;
+            sc1 = exp2f(m1 - ref1);
+            m1 = mn1;
+            const float q00 = exp2f(s[0][2] - ref1), q01 = exp2f(s[0][3] - ref1);
+            const float q10 = exp2f(s[1][2] - ref1), q11 = exp2f(s[1][3] - ref1);
+            l1 = l1 * sc1 + (q00 + q01 + q10 + q11);
+            pa[1] = pack2<BF16>(q00, q01);
+            pa[3] = pack2<BF16>(q10, q11);
+            if constexpr (BF16) {
+                pb[1] = pack2<BF16>(q00 - round16<BF16>(q00), q01 - round16<BF16>(q01));
+                pb[3] = pack2<BF16>(q10 - round16<BF16>(q10), q11 - round16<BF16>(q11));
+            }
+        } else {
+            pa[1] = pa[3] = 0u;
+            if constexpr (BF16) pb[1] = pb[3] = 0u;
+        }
+
+        // rescale the accumulator only when some row's maximum moved
+        if (__any_sync(0xffffffffu, sc0 != 1.f || sc1 != 1.f)) {
+#pragma unroll
+            for (int dn = 0; dn < DN; ++dn) {
+                o[dn][0] *= sc0;
+                o[dn][1] *= sc0;
+                o[dn][2] *= sc1;
+                o[dn][3] *= sc1;
+            }
+        }
+
+        if (!mbar_wait(bar_full_v + 8 * st, par)) {
+            if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+            return;
+        }
+
+        // ---- O += P V : 16 (heads) x D, contraction over this sub-tile's 16 rows ----
+#pragma unroll
+        for (int d2 = 0; d2 < DN / 2; ++d2) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, vbase + v_lane_off + d2 * 32);
+            mma_16816<BF16>(o[2 * d2], pa, b0, b1);
+            mma_16816<BF16>(o[2 * d2 + 1], pa, b2, b3);
+            if constexpr (BF16) {
+                mma_16816<BF16>(o[2 * d2], pb, b0, b1);
+                mma_16816<BF16>(o[2 * d2 + 1], pb, b2, b3);
+            }
+        }
+
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+    }
+    end_segment();
+    fused_merge();
+}
+
+}  // namespace decode_detail
+}  // namespace b200

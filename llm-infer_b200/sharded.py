@@ -1,0 +1,85 @@
+"""Long-context decode with the KV sequence sharded across the GPUs of one box.
+
+Softmax attention over a set of KV rows is a commutative, associative reduction
+under the engine's online-softmax state merge (src/attention.cu:41-65), so the
+rows of one sequence can live on different GPUs: rank r of N keeps rows
+[r*T/N, (r+1)*T/N) of every kv head in its own HBM, in the engine's unchanged
+[row][kv_head][head_dim] layout, and Q is replicated. Per step each rank
+
+  1. runs the same split-KV decode kernel over its rows  -> (O_r [H][D], LSE_r [H]),
+  2. all-gathers one packed fp32 record [H*D | H] per rank (NCCL over NVLink),
+  3. merges the N records with the same LSE merge kernel   -> O [H][D] on every rank.
+
+One process per GPU; ``torch.distributed`` carries the collective. The compute
+functions are injectable so the host logic (partitioning, record packing,
+gather, merge order) can be exercised with CPU ranks over gloo.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(total_rows: int, world: int, rank: int) -> tuple[int, int]:
+    """Row range [begin, end) of ``rank``: even split, the last rank takes the remainder."""
+    per = total_rows // world
+    begin = rank * per
+    end = total_rows if rank == world - 1 else begin + per
+    return begin, end
+
+
+class ShardedDecode:
+    """Decode attention for one sequence whose KV rows are spread over the ranks of ``group``."""
+
+    def __init__(self, n_heads: int, head_dim: int, *, device, group=None, decode_fn=None, merge_fn=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.H, self.D = n_heads, head_dim
+        n = n_heads * head_dim + n_heads
+        self.rec_len = (n + 3) // 4 * 4  # the merge kernel reads partials with 16-byte loads
+        self.record = torch.zeros(self.rec_len, dtype=torch.float32, device=device)
+        self.gathered = torch.zeros(self.world, self.rec_len, dtype=torch.float32, device=device)
+        if decode_fn is None or merge_fn is None:
+            from . import attention  # needs the CUDA library; raises if it is missing
+            decode_fn = decode_fn or attention.attn_decode
+            merge_fn = merge_fn or attention.attn_merge
+        self._decode, self._merge = decode_fn, merge_fn
+        self._workspace = None
+
+    # views into the packed record / gather buffer
+    def _o(self, buf):
+        return buf[..., : self.H * self.D]
+
+    def _lse(self, buf):
+        return buf[..., self.H * self.D: self.H * self.D + self.H]
+
+    def local_partial(self, q, k_shard, v_shard, kv_len_local=None):
+        """Step 1: this rank's (O, LSE) written straight into the record that will be gathered."""
+        o = self._o(self.record).view(1, self.H, self.D)
+        lse = self._lse(self.record).view(1, self.H)
+        kw = {}
+        if self._workspace is not None:
+            kw["workspace"] = self._workspace
+        self._decode(q, k_shard, v_shard, kv_len_local, out=o, lse=lse, **kw)
+        return o, lse
+
+    def gather(self):
+        """Step 2: one all-gather of rec_len floats per rank, on the current stream."""
+        dist.all_gather_into_tensor(self.gathered.view(-1), self.record, group=self.group)
+        return self.gathered
+
+    def merge(self, out=None, out_dtype=torch.float32):
+        """Step 3: LSE merge of the N gathered records."""
+        part_o = self._o(self.gathered).unflatten(-1, (self.H, self.D))  # [N, H, D], partial stride rec_len
+        part_lse = self._lse(self.gathered)  # [N, H]
+        return self._merge(part_o, part_lse, out=out, out_dtype=out_dtype)
+
+    def __call__(self, q, k_shard, v_shard, kv_len_local=None, out=None, out_dtype=torch.float32):
+        """q [1,H,D] (replicated); k_shard, v_shard [1,T_local,Hkv,D] (this rank's rows) -> out [H,D]."""
+        self.local_partial(q, k_shard, v_shard, kv_len_local)
+        self.gather()
+        return self.merge(out=out, out_dtype=out_dtype)
+
+    def use_workspace(self, workspace) -> None:
+        self._workspace = workspace

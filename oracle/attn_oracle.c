@@ -1,0 +1,369 @@
+/*
+ * Test infrastructure only (checker / CPU baseline), never part of the product
+ * path: only the test-suite, the smoke check and the benchmark's CPU-baseline
+ * leg may load this library.
+ *
+ * Plain-C restatement of the reference's CPU attention and of its online-softmax
+ * state merge, written from the reference's behaviour (no reference code is
+ * included or linked here):
+ *
+ *   include/kernels_cpu.hpp:14-17    f16 <-> f32 (F16C, round-to-nearest-even)
+ *   include/kernels_cpu.hpp:122-138  softmax(): max from -FLT_MAX, expf(v - max), divide by the sum
+ *   include/kernels_cpu.hpp:140-167  attn(): scores = (q . K[t]) / sqrtf(head_dim), softmax,
+ *                                    out[i] = sum_t p[t] * V[t][i], all in fp32, sequential order
+ *   src/model/block.cpp:157-164      head loop: group = head / (n_heads / n_kv_heads)
+ *   src/model/model.cpp:65-68        kv_len = pos + 1  => causal prefill row t sees rows 0..t
+ *   src/attention.cu:41-65           AttentionState::merge: (m, z, o) with o already normalised
+ *
+ * Parity pin: the reference ships no tests or golden vectors for this path, so
+ * this restatement is pinned against the reference's own header compiled into
+ * oracle/_ref/libref_attn.so (tests compare the two bit for bit where both are
+ * present) and against fixtures in tests/golden/ that were produced by that
+ * compiled reference.
+ *
+ * KV layout everywhere: fp16 bit patterns, [row][kv_head][head_dim], row stride
+ * given in elements (default n_kv_heads * head_dim) — include/model/block.hpp:66-67.
+ */
+#include <float.h>
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* ---------------------------------------------------------------- conversions */
+
+static inline uint32_t f32_bits(float x) {
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    return u;
+}
+static inline float bits_f32(uint32_t u) {
+    float x;
+    memcpy(&x, &u, 4);
+    return x;
+}
+
+/* IEEE binary16 -> binary32, exact (what _cvtsh_ss does, kernels_cpu.hpp:16). */
+float oracle_f16_to_f32(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1Fu;
+    uint32_t man = h & 0x3FFu;
+    if (exp == 0) {
+        if (man == 0) return bits_f32(sign);
+        /* subnormal: value = man * 2^-24 */
+        float v = (float)man * 5.9604644775390625e-8f;
+        return (sign ? -v : v);
+    }
+    if (exp == 31) return bits_f32(sign | 0x7F800000u | (man << 13));
+    return bits_f32(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+/* binary32 -> binary16 with round-to-nearest-even (what _cvtss_sh(x, 0) does,
+ * kernels_cpu.hpp:17). NaN keeps its top payload bits and is made quiet. */
+uint16_t oracle_f32_to_f16(float x) {
+    uint32_t u = f32_bits(x);
+    uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+    uint32_t a = u & 0x7FFFFFFFu;
+    if (a >= 0x7F800000u) { /* inf / nan */
+        if (a == 0x7F800000u) return (uint16_t)(sign | 0x7C00u);
+        return (uint16_t)(sign | 0x7E00u | ((a >> 13) & 0x3FFu));
+    }
+    if (a >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u); /* rounds to >= 65520 -> inf */
+    if (a < 0x33000001u) return sign;                        /* <= 2^-25 -> +-0 (ties to even) */
+    int32_t e = (int32_t)(a >> 23) - 127;
+    uint32_t m = (a & 0x7FFFFFu) | 0x800000u;
+    uint32_t shift, half_exp;
+    if (e < -14) { /* subnormal half */
+        shift = (uint32_t)(13 + (-14 - e));
+        half_exp = 0;
+    } else {
+        shift = 13;
+        half_exp = (uint32_t)(e + 15);
+    }
+    uint32_t q = m >> shift;
+    uint32_t rem = m & ((1u << shift) - 1u);
+    uint32_t halfway = 1u << (shift - 1);
+    if (rem > halfway || (rem == halfway && (q & 1u))) q += 1;
+    uint32_t out;
+    if (half_exp == 0) {
+        out = q; /* may carry into exponent 1: still correct encoding */
+    } else {
+        out = ((half_exp - 1) << 10) + q; /* q carries the implicit bit (0x400) */
+    }
+    return (uint16_t)(sign | out);
+}
+
+float oracle_bf16_to_f32(uint16_t b) { return bits_f32((uint32_t)b << 16); }
+
+uint16_t oracle_f32_to_bf16(float x) {
+    uint32_t u = f32_bits(x);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x0040u);
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7FFFu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+void oracle_f32_to_f16_array(const float* src, uint16_t* dst, size_t n) {
+    for (size_t i = 0; i < n; ++i) dst[i] = oracle_f32_to_f16(src[i]);
+}
+void oracle_f16_to_f32_array(const uint16_t* src, float* dst, size_t n) {
+    for (size_t i = 0; i < n; ++i) dst[i] = oracle_f16_to_f32(src[i]);
+}
+
+int oracle_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* -------------------------------------------------------------------- softmax */
+
+/* kernels_cpu.hpp:122-138 */
+void oracle_softmax(float* v, uint32_t size) {
+    float max_val = -FLT_MAX;
+    for (uint32_t i = 0; i < size; ++i) {
+        if (v[i] > max_val) max_val = v[i];
+    }
+    float sum = 0.0f;
+    for (uint32_t i = 0; i < size; ++i) {
+        float ev = expf(v[i] - max_val);
+        v[i] = ev;
+        sum += ev;
+    }
+    for (uint32_t i = 0; i < size; ++i) v[i] /= sum;
+}
+
+/* ------------------------------------------------------------- one query head */
+
+/* kernels_cpu.hpp:140-167. scores is scratch of >= kv_len floats. row_stride in
+ * elements. kv_head selects the [head_dim] slice of every row. */
+void oracle_attn_head(float* out, float* scores, const float* q, const uint16_t* k_cache, const uint16_t* v_cache,
+                      uint32_t kv_head, uint32_t head_dim, size_t row_stride, uint32_t kv_len) {
+    const uint16_t* k0 = k_cache + (size_t)head_dim * kv_head;
+    const uint16_t* v0 = v_cache + (size_t)head_dim * kv_head;
+    float denom = sqrtf((float)head_dim);
+    for (uint32_t t = 0; t < kv_len; ++t) {
+        const uint16_t* kt = k0 + row_stride * t;
+        float score = 0.0f;
+        for (uint32_t i = 0; i < head_dim; ++i) score += q[i] * oracle_f16_to_f32(kt[i]);
+        scores[t] = score / denom;
+    }
+    oracle_softmax(scores, kv_len);
+    for (uint32_t i = 0; i < head_dim; ++i) {
+        float acc = 0.0f;
+        for (uint32_t t = 0; t < kv_len; ++t) acc += scores[t] * oracle_f16_to_f32(v0[row_stride * t + i]);
+        out[i] = acc;
+    }
+}
+
+/* ------------------------------------------------------------------- decode */
+
+/* Batched single-token decode; sequences run one after another and heads in an
+ * OpenMP parallel-for, as src/model/block.cpp:157-164 does for its one sequence.
+ *   q, out : fp32 [batch][n_heads][head_dim]
+ *   k, v   : fp16 bits, sequence b starts at b * batch_stride elements, rows of
+ *            row_stride elements
+ *   kv_len : [batch]
+ * Returns 0, -1 on allocation failure, -2 on bad arguments. */
+int oracle_attn_decode(float* out, const float* q, const uint16_t* k, const uint16_t* v, const uint32_t* kv_len,
+                       uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, size_t row_stride,
+                       size_t batch_stride) {
+    if (n_kv_heads == 0 || n_heads % n_kv_heads != 0) return -2;
+    uint32_t max_len = 1;
+    for (uint32_t b = 0; b < batch; ++b)
+        if (kv_len[b] > max_len) max_len = kv_len[b];
+    float* scores = (float*)malloc(sizeof(float) * (size_t)n_heads * max_len);
+    if (!scores) return -1;
+    uint32_t g = n_heads / n_kv_heads;
+    for (uint32_t b = 0; b < batch; ++b) {
+        const float* qb = q + (size_t)b * n_heads * head_dim;
+        float* ob = out + (size_t)b * n_heads * head_dim;
+        const uint16_t* kb = k + batch_stride * b;
+        const uint16_t* vb = v + batch_stride * b;
+        uint32_t len = kv_len[b];
+#pragma omp parallel for
+        for (uint32_t h = 0; h < n_heads; ++h) {
+            oracle_attn_head(ob + (size_t)h * head_dim, scores + (size_t)h * max_len, qb + (size_t)h * head_dim, kb,
+                             vb, h / g, head_dim, row_stride, len);
+        }
+    }
+    free(scores);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ prefill */
+
+/* Causal prefill of one sequence: row t of head h is oracle_attn_head with
+ * kv_len = t + 1 (src/model/model.cpp:68, tools/infer.cpp:271-274).
+ *   q, out : fp32 [seq][n_heads][head_dim];  k, v : fp16 bits [seq][n_kv_heads][head_dim]
+ * Visits rows row_begin, row_begin + row_step, ... < row_end; other rows of out
+ * are left untouched. */
+int oracle_attn_prefill_causal(float* out, const float* q, const uint16_t* k, const uint16_t* v, uint32_t seq,
+                               uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t row_begin,
+                               uint32_t row_end, uint32_t row_step) {
+    if (n_kv_heads == 0 || n_heads % n_kv_heads != 0) return -2;
+    if (row_step == 0) row_step = 1;
+    if (row_end > seq) row_end = seq;
+    int nthreads = oracle_num_threads();
+    float* scores = (float*)malloc(sizeof(float) * (size_t)nthreads * (seq ? seq : 1));
+    if (!scores) return -1;
+    uint32_t g = n_heads / n_kv_heads;
+    size_t row_stride = (size_t)n_kv_heads * head_dim;
+    int64_t n_rows = row_end > row_begin ? (int64_t)(row_end - row_begin + row_step - 1) / row_step : 0;
+    int64_t n_items = n_rows * n_heads;
+#pragma omp parallel for schedule(dynamic, 8)
+    for (int64_t item = 0; item < n_items; ++item) {
+        uint32_t t = row_begin + (uint32_t)(item / n_heads) * row_step;
+        uint32_t h = (uint32_t)(item % n_heads);
+#ifdef _OPENMP
+        int tid = omp_get_thread_num();
+#else
+        int tid = 0;
+#endif
+        size_t qo = ((size_t)t * n_heads + h) * head_dim;
+        oracle_attn_head(out + qo, scores + (size_t)tid * seq, q + qo, k, v, h / g, head_dim, row_stride, t + 1);
+    }
+    free(scores);
+    return 0;
+}
+
+/* ------------------------------------------------- online-softmax state + merge */
+
+/* State of src/attention.cu:41-45: m = running max of the scaled scores
+ * (-inf when empty), z = sum exp(score - m) (0 when empty), o = NORMALISED partial
+ * output sum_t (e_t / z) V[t] (0 when empty). Computed for rows
+ * [row_begin, row_end) of one head; scores is scratch of >= row_end - row_begin. */
+void oracle_state_from_rows(float* m_out, float* z_out, float* o, float* scores, const float* q,
+                            const uint16_t* k_cache, const uint16_t* v_cache, uint32_t kv_head, uint32_t head_dim,
+                            size_t row_stride, uint32_t row_begin, uint32_t row_end) {
+    uint32_t n = row_end > row_begin ? row_end - row_begin : 0;
+    for (uint32_t i = 0; i < head_dim; ++i) o[i] = 0.0f;
+    if (n == 0) {
+        *m_out = -INFINITY;
+        *z_out = 0.0f;
+        return;
+    }
+    const uint16_t* k0 = k_cache + (size_t)head_dim * kv_head;
+    const uint16_t* v0 = v_cache + (size_t)head_dim * kv_head;
+    float denom = sqrtf((float)head_dim);
+    float m = -INFINITY;
+    for (uint32_t t = 0; t < n; ++t) {
+        const uint16_t* kt = k0 + row_stride * (row_begin + t);
+        float score = 0.0f;
+        for (uint32_t i = 0; i < head_dim; ++i) score += q[i] * oracle_f16_to_f32(kt[i]);
+        score /= denom;
+        scores[t] = score;
+        if (score > m) m = score;
+    }
+    float z = 0.0f;
+    for (uint32_t t = 0; t < n; ++t) {
+        scores[t] = expf(scores[t] - m);
+        z += scores[t];
+    }
+    for (uint32_t t = 0; t < n; ++t) {
+        float s = scores[t] / z;
+        const uint16_t* vt = v0 + row_stride * (row_begin + t);
+        for (uint32_t i = 0; i < head_dim; ++i) o[i] += s * oracle_f16_to_f32(vt[i]);
+    }
+    *m_out = m;
+    *z_out = z;
+}
+
+/* a <- merge(a, b), src/attention.cu:47-64, with one addition the reference
+ * lacks: when both sides are empty (z_c == 0) the result stays the empty state
+ * instead of 0/0. */
+void oracle_state_merge(float* m_a, float* z_a, float* o_a, float m_b, float z_b, const float* o_b,
+                        uint32_t head_dim) {
+    float m_c = fmaxf(*m_a, m_b);
+    float eac = (*m_a == m_c) ? 1.0f : expf(*m_a - m_c);
+    float ebc = (m_b == m_c) ? 1.0f : expf(m_b - m_c);
+    float z_c = (*z_a * eac) + (z_b * ebc);
+    if (!(z_c > 0.0f)) {
+        for (uint32_t i = 0; i < head_dim; ++i) o_a[i] = 0.0f;
+        *m_a = -INFINITY;
+        *z_a = 0.0f;
+        return;
+    }
+    float oas = (*z_a / z_c) * eac;
+    float obs = (z_b / z_c) * ebc;
+    for (uint32_t i = 0; i < head_dim; ++i) o_a[i] = o_a[i] * oas + o_b[i] * obs;
+    *m_a = m_c;
+    *z_a = z_c;
+}
+
+/* The same merge in log-sum-exp form over n partials of one head:
+ * lse_i = m_i + ln z_i (-inf when empty); out = sum_i w_i o_i,
+ * w_i = exp(lse_i - lse_max) / sum_j exp(lse_j - lse_max); lse_out = lse_max + ln(sum).
+ * o_parts: [n][o_stride] (first head_dim entries used). All-empty input gives
+ * out = 0 and lse_out = -inf. */
+void oracle_lse_merge(float* out, float* lse_out, const float* o_parts, size_t o_stride, const float* lse_parts,
+                      uint32_t n, uint32_t head_dim) {
+    float mx = -INFINITY;
+    for (uint32_t i = 0; i < n; ++i)
+        if (lse_parts[i] > mx) mx = lse_parts[i];
+    for (uint32_t d = 0; d < head_dim; ++d) out[d] = 0.0f;
+    if (mx == -INFINITY) {
+        if (lse_out) *lse_out = -INFINITY;
+        return;
+    }
+    float sum = 0.0f;
+    for (uint32_t i = 0; i < n; ++i) sum += expf(lse_parts[i] - mx);
+    for (uint32_t i = 0; i < n; ++i) {
+        float w = expf(lse_parts[i] - mx) / sum;
+        if (w == 0.0f) continue;
+        const float* oi = o_parts + o_stride * i;
+        for (uint32_t d = 0; d < head_dim; ++d) out[d] += w * oi[d];
+    }
+    if (lse_out) *lse_out = mx + logf(sum);
+}
+
+/* Sequence-sharded decode as the multi-GPU path computes it, on the CPU: split
+ * rows [0, kv_len) of one sequence into n_shards contiguous even shards (the
+ * last one takes the remainder), compute the (m, z, o) state of every shard per
+ * head, write them as (o, lse) partials, and also the merged result.
+ *   q, out     : fp32 [n_heads][head_dim]
+ *   part_o     : fp32 [n_shards][n_heads][head_dim]   (may be NULL)
+ *   part_lse   : fp32 [n_shards][n_heads]             (may be NULL)
+ */
+int oracle_attn_decode_sharded(float* out, float* part_o, float* part_lse, const float* q, const uint16_t* k,
+                               const uint16_t* v, uint32_t kv_len, uint32_t n_shards, uint32_t n_heads,
+                               uint32_t n_kv_heads, uint32_t head_dim, size_t row_stride) {
+    if (n_kv_heads == 0 || n_heads % n_kv_heads != 0 || n_shards == 0) return -2;
+    uint32_t g = n_heads / n_kv_heads;
+    uint32_t per = kv_len / n_shards;
+    int fail = 0;
+#pragma omp parallel for
+    for (uint32_t h = 0; h < n_heads; ++h) {
+        float* scores = (float*)malloc(sizeof(float) * (size_t)(kv_len ? kv_len : 1));
+        float* o_tmp = (float*)malloc(sizeof(float) * (size_t)head_dim * n_shards);
+        float* lse_tmp = (float*)malloc(sizeof(float) * n_shards);
+        if (!scores || !o_tmp || !lse_tmp) {
+            fail = 1;
+        } else {
+            for (uint32_t s = 0; s < n_shards; ++s) {
+                uint32_t r0 = s * per;
+                uint32_t r1 = (s + 1 == n_shards) ? kv_len : r0 + per;
+                float m, z;
+                oracle_state_from_rows(&m, &z, o_tmp + (size_t)s * head_dim, scores, q + (size_t)h * head_dim, k, v,
+                                       h / g, head_dim, row_stride, r0, r1);
+                lse_tmp[s] = (z > 0.0f) ? m + logf(z) : -INFINITY;
+                if (part_o)
+                    memcpy(part_o + ((size_t)s * n_heads + h) * head_dim, o_tmp + (size_t)s * head_dim,
+                           sizeof(float) * head_dim);
+                if (part_lse) part_lse[(size_t)s * n_heads + h] = lse_tmp[s];
+            }
+            oracle_lse_merge(out + (size_t)h * head_dim, NULL, o_tmp, head_dim, lse_tmp, n_shards, head_dim);
+        }
+        free(scores);
+        free(o_tmp);
+        free(lse_tmp);
+    }
+    return fail ? -1 : 0;
+}

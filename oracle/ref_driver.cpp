@@ -1,0 +1,114 @@
+// Test infrastructure only (checker / CPU baseline), never part of the product path.
+//
+// C-ABI driver around the reference's own CPU attention. It includes the
+// reference header include/kernels_cpu.hpp unmodified (found through -I at
+// build time; no reference source is copied) and calls attn() (lines 140-167)
+// the way the reference's transformer block does: an OpenMP parallel-for over
+// query heads with group = head / (n_heads / n_kv_heads)
+// (src/model/block.cpp:157-164). The reference has no batch dimension, so
+// sequences of a batch are run one after another. Causal prefill is defined by
+// the reference as "row t attends to rows 0..t" because its prefill is the
+// decode step run once per prompt token with kv_len = pos + 1
+// (tools/infer.cpp:271-274, src/model/model.cpp:68).
+#include <kernels_cpu.hpp>
+
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+extern "C" {
+
+int ref_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+uint16_t ref_f32_to_f16(float x) { return f32_to_f16(x); }
+float ref_f16_to_f32(uint16_t x) { return f16_to_f32(x); }
+
+void ref_f32_to_f16_array(const float* src, uint16_t* dst, size_t n) {
+    for (size_t i = 0; i < n; ++i) dst[i] = f32_to_f16(src[i]);
+}
+
+void ref_softmax(float* v, uint32_t size) { softmax(v, size); }
+
+// One sequence. q: fp32 [n_heads][head_dim]; k_cache/v_cache: fp16 bit patterns
+// [kv_len][n_kv_heads][head_dim]; out: fp32 [n_heads][head_dim];
+// scores: fp32 scratch [n_heads][scores_stride], scores_stride >= kv_len.
+void ref_attn_decode_seq(float* out, float* scores, size_t scores_stride, const float* q, const uint16_t* k_cache,
+                         const uint16_t* v_cache, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                         uint32_t kv_len) {
+    uint32_t heads_per_group = n_heads / n_kv_heads;
+#pragma omp parallel for
+    for (uint32_t head_i = 0; head_i < n_heads; ++head_i) {
+        uint32_t group_i = head_i / heads_per_group;
+        attn(out + static_cast<size_t>(head_i) * head_dim, scores + static_cast<size_t>(head_i) * scores_stride,
+             q + static_cast<size_t>(head_i) * head_dim, k_cache, v_cache, group_i, head_dim, n_kv_heads, kv_len);
+    }
+}
+
+// Batch of independent sequences, each with its own contiguous cache of
+// kv_capacity rows and its own kv_len[b]. Returns 0, or -1 on allocation failure.
+int ref_attn_decode_batch(float* out, const float* q, const uint16_t* k_cache, const uint16_t* v_cache,
+                          const uint32_t* kv_len, uint32_t batch, uint32_t kv_capacity, uint32_t n_heads,
+                          uint32_t n_kv_heads, uint32_t head_dim) {
+    std::vector<float> scores;
+    try {
+        scores.resize(static_cast<size_t>(n_heads) * (kv_capacity ? kv_capacity : 1));
+    } catch (...) {
+        return -1;
+    }
+    size_t seq_elems = static_cast<size_t>(kv_capacity) * n_kv_heads * head_dim;
+    size_t qo_elems = static_cast<size_t>(n_heads) * head_dim;
+    for (uint32_t b = 0; b < batch; ++b) {
+        ref_attn_decode_seq(out + b * qo_elems, scores.data(), kv_capacity ? kv_capacity : 1, q + b * qo_elems,
+                            k_cache + b * seq_elems, v_cache + b * seq_elems, n_heads, n_kv_heads, head_dim,
+                            kv_len[b]);
+    }
+    return 0;
+}
+
+// Causal prefill of one sequence, rows [row_begin, row_end) with a row step:
+// q: fp32 [seq][n_heads][head_dim]; k/v: fp16 bits [seq][n_kv_heads][head_dim];
+// out: fp32 [seq][n_heads][head_dim] (only the visited rows are written).
+// Parallel over (row, head) pairs; each pair is exactly one attn() call with
+// kv_len = row + 1.
+int ref_attn_prefill_causal_seq(float* out, const float* q, const uint16_t* k, const uint16_t* v, uint32_t seq,
+                                uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t row_begin,
+                                uint32_t row_end, uint32_t row_step) {
+    if (row_step == 0) row_step = 1;
+    if (row_end > seq) row_end = seq;
+    uint32_t heads_per_group = n_heads / n_kv_heads;
+    int nthreads = ref_num_threads();
+    std::vector<float> scores;
+    try {
+        scores.resize(static_cast<size_t>(nthreads) * (seq ? seq : 1));
+    } catch (...) {
+        return -1;
+    }
+    int64_t n_rows = row_end > row_begin ? (row_end - row_begin + row_step - 1) / row_step : 0;
+    int64_t n_items = n_rows * n_heads;
+#pragma omp parallel for schedule(dynamic, 8)
+    for (int64_t item = 0; item < n_items; ++item) {
+        uint32_t t = row_begin + static_cast<uint32_t>(item / n_heads) * row_step;
+        uint32_t head_i = static_cast<uint32_t>(item % n_heads);
+#ifdef _OPENMP
+        int tid = omp_get_thread_num();
+#else
+        int tid = 0;
+#endif
+        size_t qo = (static_cast<size_t>(t) * n_heads + head_i) * head_dim;
+        attn(out + qo, scores.data() + static_cast<size_t>(tid) * seq, q + qo, k, v, head_i / heads_per_group,
+             head_dim, n_kv_heads, t + 1);
+    }
+    return 0;
+}
+
+}  // extern "C"

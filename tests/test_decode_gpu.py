@@ -1,0 +1,178 @@
+"""GPU parity of the split-KV decode path, called through the C ABI, against the
+CPU checker (the engine's attn(), include/kernels_cpu.hpp:140-167) on identical
+seeded inputs. Tolerance: max abs 2e-3, max rel 1e-2 (relative error measured
+against max(|ref|, 1% of the RMS of ref))."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def attention(built_lib, pkg):
+    import torch
+    assert torch.cuda.is_available()
+    from llm_infer_b200 import attention as a
+    return a
+
+
+@pytest.fixture(scope="module")
+def wl(pkg):
+    return pkg.workloads
+
+
+def _rand(wl, seed, B, H, Hkv, D, T, q_dtype="f32", kv_dtype="f16"):
+    shape = wl.DecodeShape("t", seed, B, H, Hkv, D, T, q_dtype, kv_dtype)
+    return wl.decode_inputs(shape)
+
+
+def _oracle(wl, checker, q, k, v, q_dtype, kv_dtype, kv_len=None):
+    return checker.attn_decode(wl.widen(q, q_dtype), wl.as_f16_for_oracle(k, kv_dtype),
+                               wl.as_f16_for_oracle(v, kv_dtype),
+                               None if kv_len is None else np.asarray(kv_len, np.uint32))
+
+
+def test_golden_vectors(attention, wl):
+    from gpu_util import check_close, run_decode
+    g = np.load(os.path.join(GOLDEN, "decode_golden.npz"))
+    for name in sorted({k.split(".")[0] for k in g.files}):
+        lens = g[f"{name}.kv_len"]
+        got = run_decode(attention, g[f"{name}.q"], g[f"{name}.k"], g[f"{name}.v"], kv_len=lens)
+        check_close(wl, got, g[f"{name}.o"], name)
+
+
+def test_c1_tinyllama_shape(attention, wl, checker):
+    from gpu_util import check_close, run_decode
+    q, k, v = wl.decode_inputs(wl.C1)
+    got = run_decode(attention, q, k, v)
+    check_close(wl, got, checker.attn_decode(q, k, v), "C1")
+
+
+def test_c2_llama3_batched_full_size(attention, wl, checker):
+    from gpu_util import check_close, run_decode
+    q, k, v = wl.decode_inputs(wl.C2)
+    got = run_decode(attention, q, k, v, q_dtype="f16")
+    want = checker.attn_decode(q.astype(np.float32), k, v)
+    max_abs, max_rel = check_close(wl, got, want, "C2")
+    print(f"C2 max_abs={max_abs:.3e} max_rel={max_rel:.3e}")
+
+
+def test_c4_long_context_single_gpu(attention, wl, checker):
+    from gpu_util import check_close, run_decode
+    q, k, v = wl.decode_inputs(wl.C4)
+    got, lse = run_decode(attention, q, k, v, q_dtype="f16", lse=True)
+    want = checker.attn_decode(q.astype(np.float32), k, v)
+    max_abs, max_rel = check_close(wl, got, want, "C4")
+    print(f"C4 max_abs={max_abs:.3e} max_rel={max_rel:.3e}")
+    assert np.isfinite(lse).all()
+
+
+@pytest.mark.parametrize("kv_len", [1, 2, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 257, 1000, 4095, 4097])
+def test_edge_lengths(attention, wl, checker, kv_len):
+    from gpu_util import check_close, run_decode
+    q, k, v = _rand(wl, 100 + kv_len, 2, 32, 8, 128, kv_len)
+    got = run_decode(attention, q, k, v)
+    check_close(wl, got, _oracle(wl, checker, q, k, v, "f32", "f16"), f"kv_len={kv_len}")
+
+
+@pytest.mark.parametrize("H,Hkv,D", [(4, 4, 64), (8, 1, 128), (8, 2, 64), (16, 4, 128), (32, 4, 64), (64, 8, 128),
+                                     (32, 2, 128), (16, 16, 64), (48, 24, 128), (12, 6, 64), (5, 5, 128)])
+def test_head_configurations(attention, wl, checker, H, Hkv, D):
+    from gpu_util import check_close, run_decode
+    q, k, v = _rand(wl, H * 1000 + Hkv * 10 + D, 3, H, Hkv, D, 333)
+    got = run_decode(attention, q, k, v)
+    check_close(wl, got, _oracle(wl, checker, q, k, v, "f32", "f16"), f"H={H} Hkv={Hkv} D={D}")
+
+
+def test_ragged_batch_including_empty_sequence(attention, wl, checker):
+    from gpu_util import check_close, run_decode
+    lens = [1, 700, 0, 64, 699, 5, 333, 128]
+    q, k, v = _rand(wl, 7, len(lens), 32, 8, 128, 700)
+    got, lse = run_decode(attention, q, k, v, kv_len=lens, lse=True)
+    want = _oracle(wl, checker, q, k, v, "f32", "f16", lens)
+    check_close(wl, got, want, "ragged")
+    assert np.array_equal(got[2], np.zeros_like(got[2]))  # empty sequence -> zeros, as the CPU loop gives
+    assert np.isneginf(lse[2]).all() and np.isfinite(np.delete(lse, 2, axis=0)).all()
+
+
+@pytest.mark.parametrize("q_dtype,kv_dtype,out_dtype", [("f16", "f16", "f32"), ("bf16", "f16", "f32"),
+                                                         ("f32", "bf16", "f32"), ("bf16", "bf16", "bf16"),
+                                                         ("f16", "f16", "f16")])
+def test_dtypes(attention, wl, checker, q_dtype, kv_dtype, out_dtype):
+    from gpu_util import run_decode
+    q, k, v = _rand(wl, 11, 2, 32, 8, 128, 777, q_dtype, kv_dtype)
+    got = run_decode(attention, q, k, v, q_dtype=q_dtype, kv_dtype=kv_dtype, out_dtype=out_dtype)
+    want = _oracle(wl, checker, q, k, v, q_dtype, kv_dtype)
+    max_abs, max_rel = wl.error_metrics(got, want)
+    # 16-bit outputs carry their own rounding (bf16: 2^-9 relative)
+    rel_tol = {"f32": wl.REL_TOL, "f16": wl.REL_TOL, "bf16": 1.5e-2}[out_dtype]
+    assert max_abs <= wl.ABS_TOL and max_rel <= rel_tol, (max_abs, max_rel)
+
+
+def test_lse_output(attention, wl, port):
+    from gpu_util import run_decode
+    q, k, v = _rand(wl, 12, 1, 8, 2, 64, 200)
+    _, lse = run_decode(attention, q, k, v, lse=True)
+    for h in (0, 3, 7):
+        m, z, _ = port.state_from_rows(q[0, h], k[0], v[0], h // 4, 0, 200)
+        assert abs(lse[0, h] - (m + np.log(z))) < 1e-4
+
+
+def test_strided_cache_with_spare_capacity(attention, wl, checker):
+    """Cache rows wider than n_kv_heads*head_dim and longer than kv_len, as a preallocated cache has."""
+    import torch
+    from gpu_util import check_close, to_device
+    B, H, Hkv, D, T, cap = 2, 32, 8, 128, 300, 512
+    q, k, v = _rand(wl, 13, B, H, Hkv, D, T)
+    kbig = torch.zeros((B, cap, Hkv + 1, D), dtype=torch.float16, device="cuda")
+    vbig = torch.full((B, cap, Hkv + 1, D), float("nan"), dtype=torch.float16, device="cuda")
+    kbig[:, :T, :Hkv] = to_device(k, "f16")
+    vbig[:, :T, :Hkv] = to_device(v, "f16")
+    out = attention.attn_decode(to_device(q, "f32"), kbig[:, :, :Hkv], vbig[:, :, :Hkv], T)
+    torch.cuda.synchronize()
+    check_close(wl, out.cpu().numpy(), checker.attn_decode(q, k, v), "strided")
+
+
+def test_bitwise_deterministic_and_canaries(attention, wl):
+    import torch
+    from gpu_util import to_device
+    q, k, v = _rand(wl, 14, 4, 32, 8, 128, 1500)
+    qd, kd, vd = to_device(q, "f32"), to_device(k, "f16"), to_device(v, "f16")
+    ws = attention.DecodeWorkspace(4, 32, 8, 128)
+    padded = torch.full((4 * 32 * 128 + 512,), float("nan"), dtype=torch.float32, device="cuda")
+    out = padded[256:256 + 4 * 32 * 128].view(4, 32, 128)
+    attention.attn_decode(qd, kd, vd, out=out, workspace=ws)
+    first = out.clone()
+    for _ in range(3):
+        attention.attn_decode(qd, kd, vd, out=out, workspace=ws)
+        assert torch.equal(out, first)
+    torch.cuda.synchronize()
+    assert torch.isnan(padded[:256]).all() and torch.isnan(padded[-256:]).all()  # nothing written outside o
+    assert int(ws.status.item()) == 0
+
+
+def test_max_ctas_limits_split_without_changing_result(attention, wl, checker):
+    from gpu_util import check_close, run_decode
+    q, k, v = _rand(wl, 15, 1, 32, 8, 128, 5000)
+    want = checker.attn_decode(q, k, v)
+    for cap in (1, 2, 7, 148, 0):
+        check_close(wl, run_decode(attention, q, k, v, max_ctas=cap), want, f"max_ctas={cap}")
+
+
+def test_merge_entry_point(attention, wl, port):
+    import torch
+    q, k, v = wl.decode_inputs(wl.C4, kv_len=999)
+    want, part_o, part_lse = port.attn_decode_sharded(q.astype(np.float32)[0], k[0], v[0], 5)
+    part_lse[3] = -np.inf  # an empty shard
+    want = np.stack([port.lse_merge(part_o[:, h], part_lse[:, h])[0] for h in range(32)])
+    lse = torch.empty(32, dtype=torch.float32, device="cuda")
+    got = attention.attn_merge(torch.from_numpy(part_o).cuda(), torch.from_numpy(part_lse).cuda(), lse=lse)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=0, atol=1e-5)
+    all_empty = torch.full((3, 8), float("-inf"), device="cuda")
+    z = attention.attn_merge(torch.randn(3, 8, 128, device="cuda"), all_empty)
+    assert torch.equal(z, torch.zeros_like(z))

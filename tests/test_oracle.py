@@ -1,0 +1,163 @@
+"""CPU tests of the checker itself: the C restatement against golden vectors made
+by the reference's own code, against the compiled reference when it is present,
+and the algebra of the online-softmax merge."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from conftest import GOLDEN
+
+
+def _cases(npz):
+    return sorted({k.split(".")[0] for k in npz.files})
+
+
+@pytest.fixture(scope="module")
+def decode_golden():
+    return np.load(os.path.join(GOLDEN, "decode_golden.npz"))
+
+
+@pytest.fixture(scope="module")
+def prefill_golden():
+    return np.load(os.path.join(GOLDEN, "prefill_golden.npz"))
+
+
+def test_f16_rounding_matches_reference_vectors(port):
+    g = np.load(os.path.join(GOLDEN, "scalar_golden.npz"))
+    got = port.f32_to_f16_array(g["f32"])
+    assert np.array_equal(got, g["f16_bits"])
+    # numpy's cast is the rounding the input generators use: it must agree as well
+    with np.errstate(over="ignore"):
+        assert np.array_equal(g["f32"].astype(np.float16).view(np.uint16), g["f16_bits"])
+
+
+def test_f16_to_f32_exhaustive(port):
+    bits = np.arange(65536, dtype=np.uint16)
+    want = bits.view(np.float16).astype(np.float32)
+    got = np.array([port.f16_to_f32(int(b)) for b in bits], dtype=np.float32)
+    assert np.array_equal(got.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)])
+    assert np.isnan(got[np.isnan(want)]).all()
+
+
+def test_bf16_round_trip(port, pkg):
+    wl = pkg.workloads
+    x = np.random.default_rng(5).standard_normal(4096).astype(np.float32)
+    bits = wl.f32_to_bf16_bits(x)
+    assert all(port.lib.oracle_f32_to_bf16(float(a)) == int(b) for a, b in zip(x[:512], bits[:512]))
+    assert np.array_equal(wl.f32_to_bf16_bits(wl.bf16_bits_to_f32(bits)), bits)
+
+
+def test_softmax_golden(port):
+    g = np.load(os.path.join(GOLDEN, "scalar_golden.npz"))
+    got = port.softmax(g["softmax_in"])
+    np.testing.assert_allclose(got, g["softmax_out"], rtol=0, atol=1e-7)
+    assert abs(float(got.sum()) - 1.0) < 1e-5
+
+
+def test_decode_port_matches_golden(port, decode_golden):
+    for name in _cases(decode_golden):
+        g = decode_golden
+        got = port.attn_decode(g[f"{name}.q"], g[f"{name}.k"], g[f"{name}.v"], g[f"{name}.kv_len"])
+        np.testing.assert_allclose(got, g[f"{name}.o"], rtol=0, atol=2e-6, err_msg=name)
+
+
+def test_prefill_port_matches_golden(port, prefill_golden):
+    for name in _cases(prefill_golden):
+        g = prefill_golden
+        got = port.attn_prefill_causal(g[f"{name}.q"].astype(np.float32), g[f"{name}.k"], g[f"{name}.v"])
+        np.testing.assert_allclose(got, g[f"{name}.o"], rtol=0, atol=2e-6, err_msg=name)
+
+
+def test_prefill_row_is_decode_with_kv_len(port, prefill_golden):
+    """Row t of causal prefill is the decode call with kv_len = t + 1 (src/model/model.cpp:68)."""
+    g = prefill_golden
+    name = _cases(g)[0]
+    q, k, v = g[f"{name}.q"].astype(np.float32), g[f"{name}.k"], g[f"{name}.v"]
+    full = port.attn_prefill_causal(q, k, v)
+    for t in (0, 1, 17, q.shape[1] - 1):
+        row = port.attn_decode(q[:, t], k, v, np.full(q.shape[0], t + 1, np.uint32))
+        assert np.array_equal(row, full[:, t])
+
+
+@pytest.mark.skipif(not oracle.have_reference(), reason="compiled reference not present")
+def test_port_matches_compiled_reference(port, pkg):
+    ref = oracle.Oracle("reference")
+    wl = pkg.workloads
+    q, k, v = wl.decode_inputs(wl.C1)
+    np.testing.assert_allclose(port.attn_decode(q, k, v), ref.attn_decode(q, k, v), rtol=0, atol=2e-6)
+    q, k, v = wl.decode_inputs(wl.C2, kv_len=300, batch=2)
+    lens = np.array([300, 123], np.uint32)
+    np.testing.assert_allclose(port.attn_decode(q, k, v, lens), ref.attn_decode(q, k, v, lens), rtol=0, atol=2e-6)
+    x = np.random.default_rng(1).standard_normal(100000).astype(np.float32) * 10
+    assert np.array_equal(port.f32_to_f16_array(x), ref.f32_to_f16_array(x))
+
+
+def test_state_merge_equals_unsplit(port, pkg):
+    """(m, z, o) of two row ranges merged by the rule of src/attention.cu:47-64 equals the state of the union."""
+    wl = pkg.workloads
+    q, k, v = wl.decode_inputs(wl.C1)
+    q, k, v = q[0], k[0], v[0]
+    for head, kvh in ((0, 0), (13, 1), (31, 3)):
+        whole = port.state_from_rows(q[head], k, v, kvh, 0, 512)
+        for cut in (1, 100, 511):
+            a = port.state_from_rows(q[head], k, v, kvh, 0, cut)
+            b = port.state_from_rows(q[head], k, v, kvh, cut, 512)
+            for x, y in ((a, b), (b, a)):  # commutative
+                m, z, o = port.state_merge(x, y)
+                assert m == whole[0]
+                assert abs(z - whole[1]) <= 1e-5 * whole[1]
+                np.testing.assert_allclose(o, whole[2], rtol=0, atol=1e-6)
+
+
+def test_state_merge_empty_sides(port):
+    empty = (-np.inf, 0.0, np.zeros(8, np.float32))
+    full = (0.5, 2.0, np.arange(8, dtype=np.float32))
+    for x, y in ((empty, full), (full, empty)):
+        m, z, o = port.state_merge(x, y)
+        assert (m, z) == (0.5, 2.0) and np.array_equal(o, full[2])
+    m, z, o = port.state_merge(empty, empty)
+    assert m == -np.inf and z == 0.0 and not np.isnan(o).any()
+
+
+def test_lse_merge_matches_pairwise_state_merge(port):
+    rng = np.random.default_rng(3)
+    n, D = 7, 16
+    ms = rng.standard_normal(n).astype(np.float32) * 4
+    zs = (rng.random(n).astype(np.float32) + 0.1) * 50
+    os_ = rng.standard_normal((n, D)).astype(np.float32)
+    acc = (float(ms[0]), float(zs[0]), os_[0])
+    for i in range(1, n):
+        acc = port.state_merge(acc, (float(ms[i]), float(zs[i]), os_[i]))
+    out, lse = port.lse_merge(os_, ms + np.log(zs))
+    np.testing.assert_allclose(out, acc[2], rtol=0, atol=2e-6)
+    assert abs(lse - (acc[0] + np.log(acc[1]))) < 1e-5
+    # all partials empty -> zeros, not NaN
+    out, lse = port.lse_merge(os_, np.full(n, -np.inf, np.float32))
+    assert np.array_equal(out, np.zeros(D, np.float32)) and lse == -np.inf
+
+
+@pytest.mark.parametrize("n_shards", [1, 2, 3, 8])
+def test_sharded_decode_equals_unsharded(port, pkg, n_shards):
+    wl = pkg.workloads
+    q, k, v = wl.decode_inputs(wl.C4, kv_len=1000)
+    want = port.attn_decode(q, k, v)[0]
+    got, part_o, part_lse = port.attn_decode_sharded(q[0], k[0], v[0], n_shards)
+    np.testing.assert_allclose(got, want, rtol=0, atol=2e-6)
+    assert part_o.shape == (n_shards, 32, 128) and np.isfinite(part_lse).all()
+
+
+def test_sharded_decode_with_empty_shards(port, pkg):
+    wl = pkg.workloads
+    q, k, v = wl.decode_inputs(wl.C1, kv_len=3)
+    got, _, part_lse = port.attn_decode_sharded(q[0], k[0], v[0], 8)  # 3 rows over 8 shards: 7 shards empty
+    np.testing.assert_allclose(got, port.attn_decode(q, k, v)[0], rtol=0, atol=2e-6)
+    assert np.isinf(part_lse).sum() == 7 * 32
+
+
+def test_kv_len_zero_gives_zeros(port, pkg):
+    wl = pkg.workloads
+    q, k, v = wl.decode_inputs(wl.C1, kv_len=4)
+    out = port.attn_decode(q, k, v, np.zeros(1, np.uint32))
+    assert np.array_equal(out, np.zeros_like(out))
