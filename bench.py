@@ -29,7 +29,7 @@ if ROOT not in sys.path:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one split-pass launch on the N=1 workload, from the ncu
 # capture summarised in profiles/ (None until a capture has been taken for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 272_322_304  # 268.65 MB read + 3.67 MB write, profiles/decode_split_c2_b16_kv4096.md
 
 
 def load_package():
@@ -203,7 +203,7 @@ def run_single(args):
     # consecutive steps never re-read a cache line that could still sit in the 126 MB L2.
     gen = torch.Generator(device=dev)
     gen.manual_seed(shape.seed)
-    n_sets = 3
+    n_sets = 1 if args.kernel_only else 3
     qs = [torch.randn((B, H, D), generator=gen, device=dev, dtype=torch.float32).half() for _ in range(n_sets)]
     ks = [torch.randn((B, T, Hkv, D), generator=gen, device=dev, dtype=torch.float32).half() for _ in range(n_sets)]
     vs = [torch.randn((B, T, Hkv, D), generator=gen, device=dev, dtype=torch.float32).half() for _ in range(n_sets)]
@@ -226,6 +226,12 @@ def run_single(args):
     alg_bytes = shape.algorithmic_bytes(o_bytes=4)
     gbs = alg_bytes / (ms_per_step * 1e-3) / 1e9
     assert int(ws.status.item()) == 0, "device status word reports a timed-out wait"
+    if args.kernel_only:
+        # small-footprint mode for profiler captures: one input copy (256 MiB > L2), no host copies, no sweep
+        print(json.dumps({"metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms_per_step,
+                          "steps": args.steps, "config": workload_config(shape, 1), "kernel_only": True,
+                          "gpu_launches": int(launches)}), flush=True)
+        return
 
     # ---- end to end through the public API with host buffers: per decode step the engine moves the new token's
     # q (and its K/V rows, appended to the resident cache) to the device and reads the attention output back.
@@ -455,6 +461,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="time only the resident-input steps of the 1-GPU workload (used for profiler captures)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

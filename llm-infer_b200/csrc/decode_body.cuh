@@ -16,8 +16,9 @@
 //     group and rows [16*(w % TS), +16) of every tile. The G query heads of that
 //     kv head are the (zero-padded) 16 rows of an m16n8k16 tensor-core MMA:
 //     S = Q K^T, online softmax in fp32 with quad shuffles, O += P V.
-//     Q given in fp32 is split into a 16-bit high part and a 16-bit residual so
-//     that the scores keep fp32-level accuracy.
+//     Q given in fp32 and the probabilities P are each split into a 16-bit high
+//     part and a 16-bit residual (two MMAs) so that scores and outputs keep
+//     near-fp32 accuracy; K and V enter the tensor cores exactly.
 //   * when the CTA's tile range leaves a segment, every warp normalises its
 //     state and writes one partial (O, LSE); the merge pass (attn_merge.cu)
 //     combines the partials of each head with the online-softmax state merge of
@@ -380,13 +381,14 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
 
         float sc1 = 1.f;
         uint32_t pa[4];
-        uint32_t pb[4];  // residual of P when it is split (bf16 only)
+        // P goes to the tensor cores as a 16-bit value plus a 16-bit residual (two MMAs per tile), so the
+        // PV product keeps ~2^-22 (fp16) / 2^-17 (bf16) relative accuracy instead of the 2^-11 / 2^-8 of one
+        // rounded operand.
+        uint32_t pb[4];
         pa[0] = pack2<BF16>(p00, p01);
         pa[2] = pack2<BF16>(p10, p11);
-        if constexpr (BF16) {
-            pb[0] = pack2<BF16>(p00 - round16<BF16>(p00), p01 - round16<BF16>(p01));
-            pb[2] = pack2<BF16>(p10 - round16<BF16>(p10), p11 - round16<BF16>(p11));
-        }
+        pb[0] = pack2<BF16>(p00 - round16<BF16>(p00), p01 - round16<BF16>(p01));
+        pb[2] = pack2<BF16>(p10 - round16<BF16>(p10), p11 - round16<BF16>(p11));
         if (ghi) {
             float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
@@ -400,13 +402,11 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
             l1 = l1 * sc1 + (q00 + q01 + q10 + q11);
             pa[1] = pack2<BF16>(q00, q01);
             pa[3] = pack2<BF16>(q10, q11);
-            if constexpr (BF16) {
-                pb[1] = pack2<BF16>(q00 - round16<BF16>(q00), q01 - round16<BF16>(q01));
-                pb[3] = pack2<BF16>(q10 - round16<BF16>(q10), q11 - round16<BF16>(q11));
-            }
+            pb[1] = pack2<BF16>(q00 - round16<BF16>(q00), q01 - round16<BF16>(q01));
+            pb[3] = pack2<BF16>(q10 - round16<BF16>(q10), q11 - round16<BF16>(q11));
         } else {
             pa[1] = pa[3] = 0u;
-            if constexpr (BF16) pb[1] = pb[3] = 0u;
+            pb[1] = pb[3] = 0u;
         }
 
         // rescale the accumulator only when some row's maximum moved
@@ -432,10 +432,8 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
             ldmatrix_x4_trans(b0, b1, b2, b3, vbase + v_lane_off + d2 * 32);
             mma_16816<BF16>(o[2 * d2], pa, b0, b1);
             mma_16816<BF16>(o[2 * d2 + 1], pa, b2, b3);
-            if constexpr (BF16) {
-                mma_16816<BF16>(o[2 * d2], pb, b0, b1);
-                mma_16816<BF16>(o[2 * d2 + 1], pb, b2, b3);
-            }
+            mma_16816<BF16>(o[2 * d2], pb, b0, b1);
+            mma_16816<BF16>(o[2 * d2 + 1], pb, b2, b3);
         }
 
         __syncwarp();
