@@ -91,6 +91,26 @@ size_t attn_decode_workspace_bytes(uint32_t batch, uint32_t n_heads, uint32_t n_
 /* Enqueue: split-KV pass (per-CTA partial O and LSE) + merge pass. */
 int attn_decode(const AttnDecodeArgs* args, void* stream);
 
+/* Size of the built-in scratch array used by attn_decode_static_scratch(). */
+#define ATTN_STATIC_SCRATCH_BYTES (8u << 20)
+
+/* attn_decode() for callers that may not allocate device memory (no counterpart in the
+ * reference, which never got as far as needing scratch: src/attention.cu:369 stops before the
+ * cross-CTA reduction). Think of a server that gave all free HBM to its KV-cache pool at start-up,
+ * where a later cudaMalloc can fail and stalls the GPU while it runs, or of a host application that
+ * lets nobody but its own allocator touch the device heap. args->workspace and
+ * args->workspace_bytes are ignored; the partials go into a fixed ATTN_STATIC_SCRATCH_BYTES array
+ * that ships inside this library and occupies that much memory on every GPU that loads it, for the
+ * life of the process. Inputs and outputs are still the caller's. The function itself calls no
+ * cudaMalloc, cudaFree or other allocating routine.
+ *   - Shapes that need more scratch than the array holds return ATTN_ERR_WORKSPACE.
+ *   - One array per GPU is shared by every call: calls that overlap on the GPU (two streams) race
+ *     on it and corrupt each other; run them on one stream or use attn_decode() with a workspace.
+ *   - Nothing in the array has to be zero on entry; each call overwrites what it later reads.
+ *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress with
+ *     that device current); make that first call before any stream capture begins. */
+int attn_decode_static_scratch(const AttnDecodeArgs* args, void* stream);
+
 /* Merge of n partial results with the engine's online-softmax state merge
  * (src/attention.cu:41-65) in log-sum-exp form:
  *   out[r] = sum_i w_i * part_o[i][r],  w_i = exp(lse_i[r] - LSE[r]),  LSE = logsumexp_i lse_i[r]

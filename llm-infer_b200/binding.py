@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libllm_infer_attn.so")
 
 ATTN_OK = 0
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
+STATIC_SCRATCH_BYTES = 8 << 20
 STATUS_WAIT_TIMEOUT = 1
 STATUS_BAD_SHAPE = 2
 
@@ -21,6 +22,7 @@ STATUS_BAD_SHAPE = 2
 EXPORTED_SYMBOLS = (
     "attn_decode_workspace_bytes",
     "attn_decode",
+    "attn_decode_static_scratch",
     "attn_merge",
     "attn_status_string",
     "attn_last_cuda_error",
@@ -104,6 +106,8 @@ def load() -> C.CDLL:
     lib.attn_decode_workspace_bytes.argtypes = [C.c_uint32] * 4
     lib.attn_decode.restype = C.c_int
     lib.attn_decode.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
+    lib.attn_decode_static_scratch.restype = C.c_int
+    lib.attn_decode_static_scratch.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
     lib.attn_merge.restype = C.c_int
     lib.attn_merge.argtypes = [C.POINTER(AttnMergeArgs), C.c_void_p]
     lib.attn_status_string.restype = C.c_char_p
