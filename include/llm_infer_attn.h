@@ -91,6 +91,33 @@ size_t attn_decode_workspace_bytes(uint32_t batch, uint32_t n_heads, uint32_t n_
 /* Enqueue: split-KV pass (per-CTA partial O and LSE) + merge pass. */
 int attn_decode(const AttnDecodeArgs* args, void* stream);
 
+/* Causal prefill attention of whole prompts. The engine has no such kernel: its prefill is the decode step
+ * run once per prompt token with kv_len = pos + 1 (tools/infer.cpp:271-274, src/model/model.cpp:68), so row t
+ * of the result is attn() (include/kernels_cpu.hpp:140-167) over rows 0..t. Dense layouts, 16-bit inputs:
+ *   q, o : [batch][seq_len][n_heads][head_dim]      k, v : [batch][seq_len][n_kv_heads][head_dim]
+ * (k, v are the engine's cache layout [row][kv_head][head_dim] per sequence). head_dim must be 128. */
+typedef struct AttnPrefillArgs {
+    void* o;          /* out, o_dtype */
+    const void* q;    /* in, dtype */
+    const void* k;    /* in, dtype */
+    const void* v;    /* in, dtype */
+    int32_t o_dtype;  /* ATTN_DTYPE_F32 or the input dtype */
+    int32_t dtype;    /* ATTN_DTYPE_F16 | ATTN_DTYPE_BF16 */
+    uint32_t batch;
+    uint32_t seq_len;
+    uint32_t n_heads;
+    uint32_t n_kv_heads;
+    uint32_t head_dim;
+    float scale;      /* 0 = 1/sqrt(head_dim) */
+    uint32_t fast;    /* 0: probabilities enter the tensor cores as a 16-bit value plus a 16-bit residual
+                         (two MMAs; fp32-level accuracy). 1: one rounded 16-bit value (one MMA). */
+    uint32_t* status; /* optional device word for ATTN_STATUS_* bits */
+    float* debug_s_tile; /* optional device buffer [128][128]: raw Q.K^T of the first tile of the last rows of
+                            head 0 / sequence 0, for bring-up checks; NULL in normal use */
+} AttnPrefillArgs;
+
+int attn_prefill_causal(const AttnPrefillArgs* args, void* stream);
+
 /* Size of the built-in scratch array used by attn_decode_static_scratch(). */
 #define ATTN_STATIC_SCRATCH_BYTES (8u << 20)
 

@@ -108,6 +108,38 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, k
     return out
 
 
+def attn_prefill_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, out=None, out_dtype=None,
+                        scale: float = 0.0, fast: bool = False, status=None, debug_s_tile=None,
+                        stream=None) -> torch.Tensor:
+    """Causal attention of whole prompts: row t attends rows 0..t (the engine's token-at-a-time prefill,
+    tools/infer.cpp:271-274, as one kernel).
+
+    q [B, S, H, D], k / v [B, S, Hkv, D], fp16 or bf16, dense; D = 128. Returns out [B, S, H, D] in ``out_dtype``
+    (fp32 or the input dtype; default the input dtype).
+    """
+    _require_cuda(q, k, v)
+    lib = _b.load()
+    B, S, H, D = q.shape
+    Hkv = k.shape[2]
+    if k.shape != (B, S, Hkv, D) or v.shape != k.shape or not (q.dtype == k.dtype == v.dtype):
+        raise ValueError("q, k, v must share batch, length, head_dim and dtype")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if out is None:
+        out = torch.empty((B, S, H, D), dtype=out_dtype or q.dtype, device=q.device)
+    elif out.shape != (B, S, H, D) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [B, S, H, D] tensor")
+    a = _b.AttnPrefillArgs()
+    a.o, a.q, a.k, a.v = out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.o_dtype, a.dtype = _dtype_code(out), _dtype_code(q)
+    a.batch, a.seq_len, a.n_heads, a.n_kv_heads, a.head_dim = B, S, H, Hkv, D
+    a.scale, a.fast = float(scale), int(bool(fast))
+    a.status = status.data_ptr() if status is not None else None
+    a.debug_s_tile = debug_s_tile.data_ptr() if debug_s_tile is not None else None
+    with torch.cuda.device(q.device):
+        _b.check(lib.attn_prefill_causal(C.byref(a), _stream_ptr(stream)), "attn_prefill_causal")
+    return out
+
+
 def attn_merge(part_o: torch.Tensor, part_lse: torch.Tensor, *, out=None, lse=None, out_dtype=torch.float32,
                stream=None) -> torch.Tensor:
     """Online-softmax merge of partial results (src/attention.cu:41-65 in log-sum-exp form).

@@ -24,6 +24,7 @@ EXPORTED_SYMBOLS = (
     "attn_decode",
     "attn_decode_static_scratch",
     "attn_merge",
+    "attn_prefill_causal",
     "attn_status_string",
     "attn_last_cuda_error",
     "attn_kernel_launch_count",
@@ -63,6 +64,26 @@ class AttnDecodeArgs(C.Structure):
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
+    ]
+
+
+class AttnPrefillArgs(C.Structure):
+    _fields_ = [
+        ("o", C.c_void_p),
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("o_dtype", C.c_int32),
+        ("dtype", C.c_int32),
+        ("batch", C.c_uint32),
+        ("seq_len", C.c_uint32),
+        ("n_heads", C.c_uint32),
+        ("n_kv_heads", C.c_uint32),
+        ("head_dim", C.c_uint32),
+        ("scale", C.c_float),
+        ("fast", C.c_uint32),
+        ("status", C.c_void_p),
+        ("debug_s_tile", C.c_void_p),
     ]
 
 
@@ -108,6 +129,8 @@ def load() -> C.CDLL:
     lib.attn_decode.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
     lib.attn_decode_static_scratch.restype = C.c_int
     lib.attn_decode_static_scratch.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
+    lib.attn_prefill_causal.restype = C.c_int
+    lib.attn_prefill_causal.argtypes = [C.POINTER(AttnPrefillArgs), C.c_void_p]
     lib.attn_merge.restype = C.c_int
     lib.attn_merge.argtypes = [C.POINTER(AttnMergeArgs), C.c_void_p]
     lib.attn_status_string.restype = C.c_char_p

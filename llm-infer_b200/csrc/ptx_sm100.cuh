@@ -15,7 +15,7 @@ namespace b200 {
 // A wait that has not succeeded after this many polls gives up; the caller then
 // records ATTN_STATUS_WAIT_TIMEOUT and leaves the kernel. Each poll may itself
 // block for a hardware-defined interval, so this is on the order of seconds.
-constexpr uint32_t kWaitPollLimit = 1u << 22;
+constexpr uint32_t kWaitPollLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
