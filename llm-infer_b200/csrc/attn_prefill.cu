@@ -143,6 +143,19 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&u)[32
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Packed 16-bit pair -> two floats (exact).
+template <bool BF16>
+__device__ __forceinline__ void unpack2(uint32_t u, float& a, float& b) {
+    if constexpr (BF16) {
+        a = __uint_as_float(u << 16);
+        b = __uint_as_float(u & 0xffff0000u);
+    } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u));
+        a = f.x;
+        b = f.y;
+    }
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -262,9 +275,15 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (j * BN + c > q_row) s[c] = -INFINITY;
                 }
             }
-            float mx = s[0];
+            // eight independent chains, then a tree: a single chain of 127 dependent max operations would
+            // leave this warp's scheduler idle most of the time (only two softmax warps share a scheduler)
+            float mx8[8];
 #pragma unroll
-            for (int c = 1; c < 128; ++c) mx = fmaxf(mx, s[c]);
+            for (int i = 0; i < 8; ++i) mx8[i] = s[i];
+#pragma unroll
+            for (int c = 8; c < 128; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], s[c]);
+            float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             mx *= p.scale_log2;
             // Rescale only when the maximum grew by more than 8 (probabilities stay below 2^8).
             float factor = 1.f;
@@ -288,7 +307,7 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
             l *= factor;
             // probabilities; P overwrites S in place (every S value of this row is already in registers)
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t hi[16], lo[16];
@@ -296,9 +315,13 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 for (int i = 0; i < 16; ++i) {
                     const float p0 = fast_exp2(fmaf(s[c * 32 + 2 * i], p.scale_log2, -m_used));
                     const float p1 = fast_exp2(fmaf(s[c * 32 + 2 * i + 1], p.scale_log2, -m_used));
-                    sum += p0 + p1;
+                    sum4[i & 3] += p0 + p1;
+                    // Rounded pair by one packed convert; its fp32 value is recovered with integer / half-add
+                    // operations so that no scalar convert (special-function pipe, already busy with exp2) is used.
                     hi[i] = pack2<BF16>(p0, p1);
-                    lo[i] = pack2<BF16>(p0 - round16<BF16>(p0), p1 - round16<BF16>(p1));
+                    float h0, h1;
+                    unpack2<BF16>(hi[i], h0, h1);
+                    lo[i] = pack2<BF16>(p0 - h0, p1 - h1);
                 }
                 // 32 keys -> 16 packed columns: rounded part at column 16c, residual at 64 + 16c
                 asm volatile(
@@ -316,7 +339,7 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         : "memory");
                 }
             }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(BAR_P_FULL + t));
