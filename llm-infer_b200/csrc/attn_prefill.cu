@@ -195,17 +195,19 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int lane = tid & 31;
 
     // ---- which two tiles does this CTA own ----
-    const uint32_t b = blockIdx.z;
+    // The row-tile index is the slowest-varying grid dimension and counts down, so every CTA with the longest
+    // causal span is dispatched before any shorter one and the kernel's tail is made of one-block CTAs.
+    const uint32_t b = blockIdx.y;
     uint32_t head[2], m0[2];
     if (p.pair_heads) {
-        const uint32_t mt = p.m_tiles - 1 - blockIdx.x;  // longest rows first
-        head[0] = 2 * blockIdx.y;
-        head[1] = 2 * blockIdx.y + 1;
+        const uint32_t mt = p.m_tiles - 1 - blockIdx.z;
+        head[0] = 2 * blockIdx.x;
+        head[1] = 2 * blockIdx.x + 1;
         m0[0] = m0[1] = mt * BM;
     } else {
         const uint32_t pairs = (p.m_tiles + 1) / 2;
-        const uint32_t mp = pairs - 1 - blockIdx.x;
-        head[0] = head[1] = blockIdx.y;
+        const uint32_t mp = pairs - 1 - blockIdx.z;
+        head[0] = head[1] = blockIdx.x;
         m0[0] = (2 * mp) * BM;
         m0[1] = (2 * mp + 1) * BM;
     }
@@ -264,7 +266,7 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tmem_ld32(tmem_s(t) + lane_addr + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
             }
             tmem_wait_ld();
-            if (p.debug && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0 && t == 0 && j == 0) {
+            if (p.debug && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == gridDim.z - 1 && t == 0 && j == 0) {
 #pragma unroll
                 for (int c = 0; c < 128; ++c) p.debug[r * 128 + c] = s[c];
             }
@@ -581,8 +583,9 @@ extern "C" int attn_prefill_causal(const AttnPrefillArgs* a, void* stream_v) {
     p.debug = a->debug_s_tile;
 
     dim3 grid;
-    if (p.pair_heads) grid = dim3(p.m_tiles, a->n_heads / 2, a->batch);
-    else grid = dim3((p.m_tiles + 1) / 2, a->n_heads, a->batch);
+    if (p.pair_heads) grid = dim3(a->n_heads / 2, a->batch, p.m_tiles);
+    else grid = dim3(a->n_heads, a->batch, (p.m_tiles + 1) / 2);
+    if (grid.y > 65535u || grid.z > 65535u) return ATTN_ERR_UNSUPPORTED;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     auto launch = [&](auto kernel) -> int {
         B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemAlloc)));
