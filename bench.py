@@ -236,8 +236,9 @@ def run_single(args):
     B, H, Hkv, D, T = shape.batch, shape.n_heads, shape.n_kv_heads, shape.head_dim, shape.kv_len
     if args.prefill_only:
         # small-footprint mode for profiler captures of the prefill kernel
-        print(json.dumps({"prefill": prefill_measure(torch, attention, wl, args.steps, args.warmup, tflops_peak,
-                                                     peak_kind)}), flush=True)
+        with ClockSampler(0) as clocks:
+            res = prefill_measure(torch, attention, wl, args.steps, args.warmup, tflops_peak, peak_kind)
+        print(json.dumps({"prefill": res, "clocks": clocks.summary()}), flush=True)
         return
 
     # Inputs: N(0,1) from a seeded generator, cast once to fp16. Three independent copies are rotated so that
@@ -435,11 +436,33 @@ def run_multi(args, world: int, rank: int, local_rank: int):
         step(i)
     torch.cuda.synchronize()
     dist.barrier()
-    launches0 = attention.kernel_launch_count()
+    # The step is replayed from CUDA graphs (one per input copy), as the engine replays its decode graph; the
+    # eager path is timed next to it. If capture is refused on some rank every rank falls back to eager launches.
+    launch_mode = "cuda-graph"
+    eager_step = step
+    try:
+        graphs = [op.capture(q, ks[j], vs[j], out) for j in range(n_sets)]
+        flag = torch.ones(1, device=dev)
+    except Exception:
+        graphs, flag = None, torch.zeros(1, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if flag.item() < 1:
+        launch_mode, graphs = "eager", None
+    if graphs is not None:
+        def step(i):
+            graphs[i % n_sets].replay()
+        for i in range(3):
+            step(i)
+        torch.cuda.synchronize()
+    dist.barrier()
     with ClockSampler(local_rank) as clocks:
         dist.barrier()
         ms = time_steps(torch, step, args.steps)
-    launches = attention.kernel_launch_count() - launches0
+    launches = 3 * args.steps  # split pass + its merge + the cross-GPU merge, per step
+    dist.barrier()
+    t_e = torch.tensor([time_steps(torch, eager_step, args.steps)], device=dev)
+    dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
+    eager_ms_per_step = float(t_e.item()) / args.steps
     t = torch.tensor([ms], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = float(t.item()) / args.steps
@@ -460,12 +483,11 @@ def run_multi(args, world: int, rank: int, local_rank: int):
     # end to end with host buffers: q from pinned host memory, result read back, every step
     q_host = q.cpu().pin_memory()
     out_host = torch.empty((H, D), dtype=torch.float32).pin_memory()
-    q_dev = torch.empty_like(q)
 
     def e2e_step(i):
         j = i % n_sets
-        q_dev.copy_(q_host, non_blocking=True)
-        op(q_dev, ks[j], vs[j], out=out)
+        q.copy_(q_host, non_blocking=True)
+        step(i)
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -493,7 +515,7 @@ def run_multi(args, world: int, rank: int, local_rank: int):
                     "d2h_bytes_per_step": H * D * 4, "ms_per_step": e2e_ms},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
-            "extra": {"breakdown": parts},
+            "extra": {"breakdown": parts, "launch": launch_mode, "eager_ms_per_step": eager_ms_per_step},
         }
         print(json.dumps(line), flush=True)
     dist.barrier()

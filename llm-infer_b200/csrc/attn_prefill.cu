@@ -75,7 +75,9 @@ enum {
 constexpr uint32_t kSmemQ = 0;
 constexpr uint32_t kSmemK = kSmemQ + 2 * kTileBytes;
 constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
-constexpr uint32_t kSmemBars = kSmemV + kStages * kTileBytes;
+constexpr uint32_t kSmemStage = kSmemV + kStages * kTileBytes;   // per tile: [128 rows][128 B] output staging
+constexpr uint32_t kStageTileBytes = 128 * 128;
+constexpr uint32_t kSmemBars = kSmemStage + 2 * kStageTileBytes;
 constexpr uint32_t kSmemTmemPtr = kSmemBars + BAR_COUNT * 8;
 constexpr uint32_t kSmemTotal = kSmemTmemPtr + 16;
 constexpr uint32_t kSmemAlloc = kSmemTotal + 1024;  // slack to align the base to 1024 bytes
@@ -88,6 +90,22 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// Tile store shared -> global through the TMA engine (asynchronous; rows outside the tensor are clipped).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the shared-memory source of every committed store has been read
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// every committed store is complete
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
 }
@@ -181,7 +199,8 @@ __device__ __forceinline__ void report_timeout(uint32_t* status) {
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ PrefillParams p) {
+                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                      const __grid_constant__ PrefillParams p) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -353,40 +372,60 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             } else {
                 tc_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                const bool row_ok = q_row < p.seq;
-                const size_t out_off = ((static_cast<size_t>(b) * p.seq + q_row) * p.n_heads + head[t]) * HD;
+                // The tile leaves through shared memory and the TMA engine, 128 bytes of every row per pass: each
+                // thread writes its row's 16-byte chunks XOR-swizzled by the row (the 128-byte swizzle the tensor
+                // map expects; no bank conflicts), the four warps of the tile meet, and one thread issues the bulk
+                // store, which also clips rows past the end of the sequence. Plain per-thread global stores (rows
+                // are 8 KB apart) would sit in the load/store queue that this SM's MMA and TMA instructions also
+                // pass through and stall them while they drain.
+                const uint32_t stage = base + kSmemStage + t * kStageTileBytes;
+                const bool f32_out = p.o_dtype == ATTN_DTYPE_F32;
+                const int passes = f32_out ? 4 : 2;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float o[32];
-                    tmem_ld32(tmem_o(t) + lane_addr + c * 32, o);
-                    tmem_wait_ld();
-                    if (row_ok) {
-                        if (p.o_dtype == ATTN_DTYPE_F32) {
-                            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.o) + out_off + c * 32);
+                for (int pass = 0; pass < 4; ++pass) {
+                    if (pass < passes) {
+                        // 32 accumulator columns at a time (fp32 out: one pass; 16-bit out: half a pass)
+                        const int n_ld = f32_out ? 1 : 2;
 #pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
-                        } else {
-                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.o) + out_off + c * 32);
+                        for (int h = 0; h < 2; ++h) {
+                            if (h < n_ld) {
+                                float o[32];
+                                tmem_ld32(tmem_o(t) + lane_addr + (f32_out ? pass * 32 : pass * 64 + h * 32), o);
+                                tmem_wait_ld();
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                uint4 w;
-                                if (p.o_dtype == ATTN_DTYPE_BF16) {
-                                    w.x = pack2<true>(o[8 * i] * inv, o[8 * i + 1] * inv);
-                                    w.y = pack2<true>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-                                    w.z = pack2<true>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
-                                    w.w = pack2<true>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
-                                } else {
-                                    w.x = pack2<false>(o[8 * i] * inv, o[8 * i + 1] * inv);
-                                    w.y = pack2<false>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-                                    w.z = pack2<false>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
-                                    w.w = pack2<false>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+                                for (int c = 0; c < (8 >> 1) * 2; ++c) {
+                                    if (f32_out) {
+                                        const uint4 v = make_uint4(__float_as_uint(o[c * 4] * inv), __float_as_uint(o[c * 4 + 1] * inv),
+                                                                   __float_as_uint(o[c * 4 + 2] * inv), __float_as_uint(o[c * 4 + 3] * inv));
+                                        const uint32_t addr = stage + r * 128 + ((c ^ (r & 7)) << 4);
+                                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                                    } else if (c < 4) {
+                                        uint4 v;
+                                        if (p.o_dtype == ATTN_DTYPE_BF16) {
+                                            v = make_uint4(pack2<true>(o[c * 8] * inv, o[c * 8 + 1] * inv), pack2<true>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
+                                                           pack2<true>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack2<true>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
+                                        } else {
+                                            v = make_uint4(pack2<false>(o[c * 8] * inv, o[c * 8 + 1] * inv), pack2<false>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
+                                                           pack2<false>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack2<false>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
+                                        }
+                                        const int chunk = h * 4 + c;
+                                        const uint32_t addr = stage + r * 128 + ((chunk ^ (r & 7)) << 4);
+                                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                                    }
                                 }
-                                dst[i] = w;
                             }
                         }
+                        fence_async_smem();
+                        named_bar_sync(1 + t, 128);
+                        if ((warp & 3) == 0 && lane == 0) {
+                            tma_store_4d(&tm_o, stage, pass * (f32_out ? 32 : 64), m0[t], head[t], b);
+                            tma_store_commit();
+                            tma_store_wait_read();  // the staging tile may be overwritten after this
+                        }
+                        named_bar_sync(1 + t, 128);
                     }
                 }
+                if ((warp & 3) == 0 && lane == 0) tma_store_wait_all();
             }
         }
     } else {
@@ -521,16 +560,20 @@ EncodeTiledFn encode_tiled_fn() {
     return reinterpret_cast<EncodeTiledFn>(fn);
 }
 
-// [B][S][heads][128] 16-bit tensor viewed as (dim, row, head, batch); box = 64 dims x 128 rows, 128-byte swizzle.
+// [B][S][heads][128] tensor viewed as (dim, row, head, batch); box = 128 bytes of 128 rows, 128-byte swizzle.
 int make_map(CUtensorMap* map, const void* ptr, int32_t dtype, uint32_t batch, uint32_t seq, uint32_t heads) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return ATTN_ERR_CUDA;
+    const cuuint64_t esz = dtype == ATTN_DTYPE_F32 ? 4 : 2;
     const cuuint64_t dims[4] = {HD, seq, heads, batch};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(heads) * HD * 2, static_cast<cuuint64_t>(HD) * 2,
-                                   static_cast<cuuint64_t>(seq) * heads * HD * 2};
-    const cuuint32_t box[4] = {64, BM, 1, 1};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(heads) * HD * esz, static_cast<cuuint64_t>(HD) * esz,
+                                   static_cast<cuuint64_t>(seq) * heads * HD * esz};
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / esz), BM, 1, 1};  // 128-byte rows
     const cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = enc(map, dtype == ATTN_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+    const CUtensorMapDataType dt = dtype == ATTN_DTYPE_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : dtype == ATTN_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = enc(map, dt,
                      4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -560,7 +603,8 @@ extern "C" int attn_prefill_causal(const AttnPrefillArgs* a, void* stream_v) {
     if (rc != ATTN_OK) return rc;
     if (dev.cc_major != 10) return ATTN_ERR_DEVICE;
 
-    CUtensorMap tm_q, tm_k, tm_v;
+    CUtensorMap tm_q, tm_k, tm_v, tm_o;
+    if ((rc = make_map(&tm_o, a->o, a->o_dtype, a->batch, a->seq_len, a->n_heads)) != ATTN_OK) return rc;
     if ((rc = make_map(&tm_q, a->q, a->dtype, a->batch, a->seq_len, a->n_heads)) != ATTN_OK) return rc;
     if ((rc = make_map(&tm_k, a->k, a->dtype, a->batch, a->seq_len, a->n_kv_heads)) != ATTN_OK) return rc;
     if ((rc = make_map(&tm_v, a->v, a->dtype, a->batch, a->seq_len, a->n_kv_heads)) != ATTN_OK) return rc;
@@ -594,7 +638,7 @@ extern "C" int attn_prefill_causal(const AttnPrefillArgs* a, void* stream_v) {
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = kSmemAlloc;
         cfg.stream = stream;
-        B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tm_q, tm_k, tm_v, p));
+        B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tm_q, tm_k, tm_v, tm_o, p));
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
         return ATTN_OK;
     };

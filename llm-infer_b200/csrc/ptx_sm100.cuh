@@ -56,6 +56,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t it = 0; it < kWaitPollLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+#ifdef ATTN_WAIT_BACKOFF_NS
+        __nanosleep(ATTN_WAIT_BACKOFF_NS);
+#endif
     }
     return false;
 }

@@ -83,3 +83,17 @@ class ShardedDecode:
 
     def use_workspace(self, workspace) -> None:
         self._workspace = workspace
+
+    def capture(self, q, k_shard, v_shard, out, kv_len_local=None):
+        """Record one step (local decode, all-gather, merge) into a CUDA graph and return it.
+
+        A decode step is three small launches and one small collective, so at long-context shard sizes the host's
+        launch cost is comparable to the GPU time; replaying a captured graph removes it, which is also how the
+        engine drives its decode step (include/model/device.hpp:161-262). The tensors passed here are the ones the
+        graph will read and write on every ``replay()``; run at least one eager step first so that NCCL and the
+        kernels have done their lazy set-up outside the capture.
+        """
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self(q, k_shard, v_shard, kv_len_local, out=out)
+        return graph
