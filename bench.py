@@ -436,18 +436,20 @@ def run_multi(args, world: int, rank: int, local_rank: int):
         step(i)
     torch.cuda.synchronize()
     dist.barrier()
-    # The step is replayed from CUDA graphs (one per input copy), as the engine replays its decode graph; the
-    # eager path is timed next to it. If capture is refused on some rank every rank falls back to eager launches.
-    launch_mode = "cuda-graph"
+    # With --cuda-graph the step is replayed from CUDA graphs (one per input copy), as the engine replays its decode
+    # graph; the eager path is timed next to it. If capture is refused on some rank every rank falls back to eager.
+    launch_mode = "cuda-graph" if args.cuda_graph else "eager"
     eager_step = step
-    try:
-        graphs = [op.capture(q, ks[j], vs[j], out) for j in range(n_sets)]
-        flag = torch.ones(1, device=dev)
-    except Exception:
-        graphs, flag = None, torch.zeros(1, device=dev)
-    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    if flag.item() < 1:
-        launch_mode, graphs = "eager", None
+    graphs = None
+    if args.cuda_graph:
+        try:
+            graphs = [op.capture(q, ks[j], vs[j], out) for j in range(n_sets)]
+            flag = torch.ones(1, device=dev)
+        except Exception:
+            graphs, flag = None, torch.zeros(1, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if flag.item() < 1:
+            launch_mode, graphs = "eager", None
     if graphs is not None:
         def step(i):
             graphs[i % n_sets].replay()
@@ -519,6 +521,12 @@ def run_multi(args, world: int, rank: int, local_rank: int):
         }
         print(json.dumps(line), flush=True)
     dist.barrier()
+    torch.cuda.synchronize()
+    if graphs is not None:
+        # Tearing the communicator down while captured graphs still hold its kernels blocks in
+        # destroy_process_group(); the line is printed, so leave without the teardown.
+        sys.stdout.flush()
+        os._exit(0)
     dist.destroy_process_group()
 
 
@@ -528,6 +536,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="N > 1: replay the sharded decode step from CUDA graphs instead of launching it eagerly")
     ap.add_argument("--prefill-only", action="store_true",
                     help="time only the causal-prefill workload (used for profiler captures)")
     ap.add_argument("--kernel-only", action="store_true",
