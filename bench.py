@@ -7,7 +7,9 @@ N = 1   one step = one batched decode-attention call (split-KV pass + merge pass
         Llama-3-8B-shaped workload: batch 16, 32 query / 8 kv heads, head_dim 128, KV length 4096,
         fp16, inputs resident in HBM. Metric: algorithmic HBM GB/s of that call.
 N > 1   one step = one long-context decode with the KV sequence (131072 rows) sharded evenly over
-        the N GPUs: local split-KV decode -> NCCL all-gather of (O, LSE) records -> LSE merge.
+        the N GPUs: local split-KV pass, then one kernel that merges the local partials, exchanges the
+        per-GPU (O, LSE) rows through peer memory over NVLink and finishes the LSE merge (replayed from a
+        CUDA graph). The NCCL all-gather variant of the same step is timed next to it.
         Launched by torch.distributed.run, one process per GPU. Total work is fixed ("strong").
 
 Prints ONE JSON line (rank 0). `--impl reference` times the engine's own CPU attention
@@ -170,7 +172,7 @@ def workload_config(shape, world: int):
            "n_kv_heads": shape.n_kv_heads, "head_dim": shape.head_dim, "q_dtype": shape.q_dtype,
            "kv_dtype": shape.kv_dtype, "kv_layout": "[seq][kv_head][head_dim] per sequence"}
     if world > 1:
-        cfg["parallelism"] = f"kv-sequence sharded over {world} GPUs, all-gather of (O, LSE), LSE merge"
+        cfg["parallelism"] = f"kv-sequence sharded over {world} GPUs, exchange of per-GPU (O, LSE), LSE merge"
     return cfg
 
 
@@ -405,7 +407,7 @@ def run_multi(args, world: int, rank: int, local_rank: int):
 
     pkg = load_package()
     from llm_infer_b200 import attention
-    from llm_infer_b200.sharded import ShardedDecode, shard_rows
+    from llm_infer_b200.sharded import FusedShardedDecode, ShardedDecode, shard_rows
     wl = pkg.workloads
     shape = wl.C4
     torch.cuda.set_device(local_rank)
@@ -424,81 +426,94 @@ def run_multi(args, world: int, rank: int, local_rank: int):
     n_sets = max(2, min(8, int(400e6 // (2 * rows * Hkv * D * 2)) + 1))
     ks = [torch.randn((1, rows, Hkv, D), generator=gen, device=dev, dtype=torch.float16) for _ in range(n_sets)]
     vs = [torch.randn((1, rows, Hkv, D), generator=gen, device=dev, dtype=torch.float16) for _ in range(n_sets)]
-    op = ShardedDecode(H, D, device=dev)
-    op.use_workspace(attention.DecodeWorkspace(1, H, Hkv, D, dev))
-    out = torch.empty((H, D), dtype=torch.float32, device=dev)
+    out = torch.empty((1, H, D), dtype=torch.float32, device=dev)
 
-    def step(i):
-        j = i % n_sets
-        op(q, ks[j], vs[j], out=out)
-
-    for i in range(max(3, args.warmup)):
-        step(i)
-    torch.cuda.synchronize()
-    dist.barrier()
-    # With --cuda-graph the step is replayed from CUDA graphs (one per input copy), as the engine replays its decode
-    # graph; the eager path is timed next to it. If capture is refused on some rank every rank falls back to eager.
-    launch_mode = "cuda-graph" if args.cuda_graph else "eager"
-    eager_step = step
-    graphs = None
-    if args.cuda_graph:
-        try:
-            graphs = [op.capture(q, ks[j], vs[j], out) for j in range(n_sets)]
-            flag = torch.ones(1, device=dev)
-        except Exception:
-            graphs, flag = None, torch.zeros(1, device=dev)
+    def agree(ok: bool) -> bool:
+        flag = torch.tensor([1.0 if ok else 0.0], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if flag.item() < 1:
-            launch_mode, graphs = "eager", None
-    if graphs is not None:
-        def step(i):
-            graphs[i % n_sets].replay()
-        for i in range(3):
-            step(i)
-        torch.cuda.synchronize()
-    dist.barrier()
-    with ClockSampler(local_rank) as clocks:
-        dist.barrier()
-        ms = time_steps(torch, step, args.steps)
-    launches = 3 * args.steps  # split pass + its merge + the cross-GPU merge, per step
-    dist.barrier()
-    t_e = torch.tensor([time_steps(torch, eager_step, args.steps)], device=dev)
-    dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
-    eager_ms_per_step = float(t_e.item()) / args.steps
-    t = torch.tensor([ms], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / args.steps
+        return flag.item() >= 1
 
-    # itemised: local decode only / all-gather only / merge only (each timed alone, max over ranks)
-    def timed(fn, n=50):
+    def timed(fn, n):
+        """CUDA-event time per call in ms, max over ranks."""
         for i in range(3):
             fn(i)
+        torch.cuda.synchronize()
         dist.barrier()
         x = torch.tensor([time_steps(torch, fn, n) / n], device=dev)
         dist.all_reduce(x, op=dist.ReduceOp.MAX)
         return float(x.item())
 
-    parts = {"local_decode_us": 1e3 * timed(lambda i: op.local_partial(q, ks[i % n_sets], vs[i % n_sets])),
-             "all_gather_us": 1e3 * timed(lambda i: op.gather()),
-             "merge_us": 1e3 * timed(lambda i: op.merge(out=out))}
+    # ---- path A: NCCL all-gather between the local decode and the merge (three launches + one collective)
+    nccl = ShardedDecode(H, D, device=dev)
+    nccl.use_workspace(attention.DecodeWorkspace(1, H, Hkv, D, dev))
+    out_a = out.view(H, D)
+    for i in range(max(3, args.warmup)):
+        nccl(q, ks[i % n_sets], vs[i % n_sets], out=out_a)
+    torch.cuda.synchronize()
+    paths = {"nccl_allgather_eager_ms": timed(lambda i: nccl(q, ks[i % n_sets], vs[i % n_sets], out=out_a), args.steps)}
+    parts = {"local_decode_us": 1e3 * timed(lambda i: nccl.local_partial(q, ks[i % n_sets], vs[i % n_sets]), 50),
+             "all_gather_us": 1e3 * timed(lambda i: nccl.gather(), 50),
+             "merge_us": 1e3 * timed(lambda i: nccl.merge(out=out_a), 50)}
+
+    # ---- path B (the product path): exchange fused into the merge kernel over peer memory, two launches per step,
+    #      replayed from CUDA graphs (one per input copy) the way the engine replays its decode graph
+    step, launch_mode, graphs = None, "nccl-allgather, eager", None
+    try:
+        fused = FusedShardedDecode(1, H, Hkv, D, device=dev)
+        ok = True
+    except Exception as e:  # no peer-mapped memory on this box: stay on path A
+        fused, ok = None, False
+        paths["fused_error"] = str(e)[:200]
+    if agree(ok):
+        def fused_step(i):
+            fused(q, ks[i % n_sets], vs[i % n_sets], out=out)
+        for i in range(max(3, args.warmup)):
+            fused_step(i)
+        torch.cuda.synchronize()
+        paths["fused_peer_store_eager_ms"] = timed(fused_step, args.steps)
+        step, launch_mode = fused_step, "fused peer-store exchange, eager"
+        try:
+            graphs = [fused.capture(q, ks[j], vs[j], out) for j in range(n_sets)]
+            ok = True
+        except Exception:
+            graphs, ok = None, False
+        if agree(ok):
+            def graph_step(i):
+                graphs[i % n_sets].replay()
+            step, launch_mode = graph_step, "fused peer-store exchange, CUDA-graph replay"
+        else:
+            graphs = None
+    if step is None:
+        def step(i):
+            nccl(q, ks[i % n_sets], vs[i % n_sets], out=out_a)
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    launches0 = attention.kernel_launch_count()
+    with ClockSampler(local_rank) as clocks:
+        dist.barrier()
+        ms = time_steps(torch, step, args.steps)
+    launches = attention.kernel_launch_count() - launches0
+    if graphs is not None:
+        launches = 2 * args.steps  # split pass + merge/exchange pass per replay (replays bypass the host-side counter)
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    status_ok = fused is None or int(fused.workspace.status.item()) == 0
 
     # end to end with host buffers: q from pinned host memory, result read back, every step
     q_host = q.cpu().pin_memory()
-    out_host = torch.empty((H, D), dtype=torch.float32).pin_memory()
+    out_host = torch.empty((1, H, D), dtype=torch.float32).pin_memory()
 
     def e2e_step(i):
-        j = i % n_sets
         q.copy_(q_host, non_blocking=True)
         step(i)
-        out_host.copy_(out, non_blocking=True)
+        out_host.copy_(out if fused is not None else out_a.view(1, H, D), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for i in range(3):
-        e2e_step(i)
-    dist.barrier()
-    x = torch.tensor([time_steps(torch, e2e_step, args.steps) / args.steps], device=dev)
-    dist.all_reduce(x, op=dist.ReduceOp.MAX)
-    e2e_ms = float(x.item())
+    e2e_ms = timed(e2e_step, args.steps)
 
     alg_bytes = shape.algorithmic_bytes(o_bytes=4)
     gbs = alg_bytes / (ms_per_step * 1e-3) / 1e9
@@ -507,27 +522,25 @@ def run_multi(args, world: int, rank: int, local_rank: int):
             "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
-            "config": {**workload_config(shape, world),
+            "config": {**workload_config(shape, world), "exchange": launch_mode,
                        "l2": f"{rows * Hkv * D * 4 >> 20} MiB of KV per GPU per step, {n_sets} copies rotated"},
             "tok_per_s": 1.0 / (ms_per_step * 1e-3),
             "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": hbm_peak, "unit": "GB/s",
                          "frac": gbs / world / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                         "note": "per GPU: algorithmic bytes / N / step time (local decode + all-gather + merge)"},
+                         "note": "per GPU: algorithmic bytes / N / step time (local decode + exchange + merge)"},
             "e2e": {"value": alg_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": q.numel() * 2,
                     "d2h_bytes_per_step": H * D * 4, "ms_per_step": e2e_ms},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
-            "extra": {"breakdown": parts, "launch": launch_mode, "eager_ms_per_step": eager_ms_per_step},
+            "extra": {"paths_ms_per_step": paths, "nccl_path_breakdown": parts, "status_ok": status_ok},
         }
         print(json.dumps(line), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
-    if graphs is not None:
-        # Tearing the communicator down while captured graphs still hold its kernels blocks in
-        # destroy_process_group(); the line is printed, so leave without the teardown.
-        sys.stdout.flush()
-        os._exit(0)
-    dist.destroy_process_group()
+    # Tearing the process group down while captured graphs or symmetric-memory handles are alive can block;
+    # the line is printed, so leave directly.
+    sys.stdout.flush()
+    os._exit(0)
 
 
 def main():
@@ -536,8 +549,6 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cuda-graph", action="store_true",
-                    help="N > 1: replay the sharded decode step from CUDA graphs instead of launching it eagerly")
     ap.add_argument("--prefill-only", action="store_true",
                     help="time only the causal-prefill workload (used for profiler captures)")
     ap.add_argument("--kernel-only", action="store_true",

@@ -138,6 +138,36 @@ int attn_prefill_causal(const AttnPrefillArgs* args, void* stream);
  *     that device current); make that first call before any stream capture begins. */
 int attn_decode_static_scratch(const AttnDecodeArgs* args, void* stream);
 
+/* Decode with the KV sequence of every sequence sharded across the GPUs of one NVLink box, exchange fused into the
+ * merge pass (no counterpart in the reference, which is single-GPU: include/model/device.hpp:54,127-128). Each rank
+ * calls this with its own rows in `decode` (same q on every rank). Two launches: the split pass over the local rows,
+ * then one kernel that merges the local partials per row, stores the row's (O, LSE) into every rank's exchange
+ * buffer with plain peer stores, raises a per-row flag on every rank, waits (bounded) for the other ranks' flags
+ * for that row and merges the world_size records that arrived. decode.o / decode.lse receive the final result on
+ * every rank.
+ *   peer_buffers[r]: device pointer, valid on THIS GPU, to rank r's exchange buffer (peer-mapped memory, e.g. a
+ *                    symmetric allocation); peer_buffers[rank] is this rank's own buffer. Every buffer has
+ *                    attn_decode_sharded_exchange_bytes() bytes and is zero before the first step.
+ *   step           : 0 = the kernel counts steps itself in the exchange buffer (every rank must then make the same
+ *                    sequence of calls on its buffer; the launch arguments stay constant, so the call can be
+ *                    replayed from a CUDA graph). Otherwise 1, 2, 3, ...: the same value on every rank for the
+ *                    same call, consecutive calls using consecutive values (records are double-buffered by the
+ *                    parity of the step).
+ *   poll_limit     : flag polls before a row gives up with ATTN_STATUS_WAIT_TIMEOUT in decode.status
+ *                    (0 = a default of about a second). The context stays usable after a timeout. */
+#define ATTN_MAX_PEERS 8
+typedef struct AttnDecodeShardedArgs {
+    AttnDecodeArgs decode;
+    uint32_t world_size; /* 1 .. ATTN_MAX_PEERS */
+    uint32_t rank;
+    void* peer_buffers[ATTN_MAX_PEERS];
+    uint32_t step;
+    uint32_t poll_limit;
+} AttnDecodeShardedArgs;
+
+size_t attn_decode_sharded_exchange_bytes(uint32_t batch, uint32_t n_heads, uint32_t head_dim, uint32_t world_size);
+int attn_decode_sharded(const AttnDecodeShardedArgs* args, void* stream);
+
 /* Merge of n partial results with the engine's online-softmax state merge
  * (src/attention.cu:41-65) in log-sum-exp form:
  *   out[r] = sum_i w_i * part_o[i][r],  w_i = exp(lse_i[r] - LSE[r]),  LSE = logsumexp_i lse_i[r]

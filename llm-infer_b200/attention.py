@@ -53,19 +53,9 @@ class DecodeWorkspace:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
 
-def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len=None, *, out=None, lse=None,
-                out_dtype=torch.float32, scale: float = 0.0, workspace: DecodeWorkspace | None = None,
-                max_ctas: int = 0, stream=None) -> torch.Tensor:
-    """Single-token attention of every query head over its sequence's KV cache.
-
-    q        [B, H, D]        fp32 / fp16 / bf16, already rotated
-    k_cache  [B, T, Hkv, D]   fp16 / bf16; only the last dim must be dense, rows and sequences may be strided
-    v_cache  same geometry as k_cache
-    kv_len   None (all T rows valid), an int, or an int32/uint32 CUDA tensor [B]
-    returns  out [B, H, D] in out_dtype; fills ``lse`` [B, H] (fp32) when given
-    """
+def _decode_args(q, k_cache, v_cache, kv_len, out, lse, out_dtype, scale, workspace, max_ctas):
+    """Validates the operands of a decode call and fills the C struct. Returns (args, out, workspace)."""
     _require_cuda(q, k_cache, v_cache)
-    lib = _b.load()
     B, H, D = q.shape
     Bk, T, Hkv, Dk = k_cache.shape
     if (Bk, Dk) != (B, D) or v_cache.shape != k_cache.shape:
@@ -103,9 +93,45 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, k
     a.max_ctas = int(max_ctas)
     a.workspace, a.workspace_bytes = workspace.buf.data_ptr(), workspace.nbytes
     a.status = workspace.status.data_ptr()
-    with torch.cuda.device(q.device):
-        _b.check(lib.attn_decode(C.byref(a), _stream_ptr(stream)), "attn_decode")
+    return a, out, workspace, q
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len=None, *, out=None, lse=None,
+                out_dtype=torch.float32, scale: float = 0.0, workspace: DecodeWorkspace | None = None,
+                max_ctas: int = 0, stream=None) -> torch.Tensor:
+    """Single-token attention of every query head over its sequence's KV cache.
+
+    q        [B, H, D]        fp32 / fp16 / bf16, already rotated
+    k_cache  [B, T, Hkv, D]   fp16 / bf16; only the last dim must be dense, rows and sequences may be strided
+    v_cache  same geometry as k_cache
+    kv_len   None (all T rows valid), an int, or an int32/uint32 CUDA tensor [B]
+    returns  out [B, H, D] in out_dtype; fills ``lse`` [B, H] (fp32) when given
+    """
+    a, out, _, _q = _decode_args(q, k_cache, v_cache, kv_len, out, lse, out_dtype, scale, workspace, max_ctas)
+    with torch.cuda.device(out.device):
+        _b.check(_b.load().attn_decode(C.byref(a), _stream_ptr(stream)), "attn_decode")
     return out
+
+
+def attn_decode_sharded(q, k_shard, v_shard, kv_len_local=None, *, peer_buffers, world_size: int, rank: int,
+                        step: int = 0, poll_limit: int = 0, out=None, lse=None, out_dtype=torch.float32,
+                        scale: float = 0.0, workspace: DecodeWorkspace | None = None, stream=None) -> torch.Tensor:
+    """Decode over this rank's KV rows with the cross-GPU exchange fused into the merge pass (C ABI
+    ``attn_decode_sharded``). ``peer_buffers`` holds one device pointer per rank (as int) to that rank's exchange
+    buffer, valid on this GPU; ``step = 0`` lets the kernel count steps itself. Returns the final out [B, H, D]."""
+    a, out, _, _q = _decode_args(q, k_shard, v_shard, kv_len_local, out, lse, out_dtype, scale, workspace, 0)
+    s = _b.AttnDecodeShardedArgs()
+    s.decode = a
+    s.world_size, s.rank, s.step, s.poll_limit = world_size, rank, step, poll_limit
+    for r in range(world_size):
+        s.peer_buffers[r] = int(peer_buffers[r])
+    with torch.cuda.device(out.device):
+        _b.check(_b.load().attn_decode_sharded(C.byref(s), _stream_ptr(stream)), "attn_decode_sharded")
+    return out
+
+
+def exchange_bytes(batch: int, n_heads: int, head_dim: int, world_size: int) -> int:
+    return int(_b.load().attn_decode_sharded_exchange_bytes(batch, n_heads, head_dim, world_size))
 
 
 def attn_prefill_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, out=None, out_dtype=None,

@@ -23,6 +23,8 @@ EXPORTED_SYMBOLS = (
     "attn_decode_workspace_bytes",
     "attn_decode",
     "attn_decode_static_scratch",
+    "attn_decode_sharded_exchange_bytes",
+    "attn_decode_sharded",
     "attn_merge",
     "attn_prefill_causal",
     "attn_status_string",
@@ -64,6 +66,20 @@ class AttnDecodeArgs(C.Structure):
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
+    ]
+
+
+MAX_PEERS = 8
+
+
+class AttnDecodeShardedArgs(C.Structure):
+    _fields_ = [
+        ("decode", AttnDecodeArgs),
+        ("world_size", C.c_uint32),
+        ("rank", C.c_uint32),
+        ("peer_buffers", C.c_void_p * MAX_PEERS),
+        ("step", C.c_uint32),
+        ("poll_limit", C.c_uint32),
     ]
 
 
@@ -129,6 +145,10 @@ def load() -> C.CDLL:
     lib.attn_decode.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
     lib.attn_decode_static_scratch.restype = C.c_int
     lib.attn_decode_static_scratch.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
+    lib.attn_decode_sharded_exchange_bytes.restype = C.c_size_t
+    lib.attn_decode_sharded_exchange_bytes.argtypes = [C.c_uint32] * 4
+    lib.attn_decode_sharded.restype = C.c_int
+    lib.attn_decode_sharded.argtypes = [C.POINTER(AttnDecodeShardedArgs), C.c_void_p]
     lib.attn_prefill_causal.restype = C.c_int
     lib.attn_prefill_causal.argtypes = [C.POINTER(AttnPrefillArgs), C.c_void_p]
     lib.attn_merge.restype = C.c_int

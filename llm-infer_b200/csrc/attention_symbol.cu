@@ -120,7 +120,7 @@ extern "C" {
 size_t attention_workspace_bytes(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim) {
     DecodePlan plan{};
     if (plan_for(n_heads, n_kv_heads, head_dim, &plan) != ATTN_OK) return 0;
-    return plan.workspace_bytes + static_cast<size_t>(plan.nseg) * 4 + 16;
+    return plan.workspace_bytes;
 }
 
 int attention_configure(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, float scale, void* workspace,
@@ -151,7 +151,7 @@ int attention_configure(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim
     float* ws = static_cast<float*>(workspace);
     c.part_o = ws;
     c.part_lse = ws + plan.part_o_floats;
-    c.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + plan.workspace_bytes);
+    c.counters = reinterpret_cast<uint32_t*>(ws + plan.part_o_floats + plan.part_lse_floats) + plan.prefix_words;
     B200_CUDA_TRY(cudaMemsetAsync(c.counters, 0, static_cast<size_t>(plan.nseg) * 4, stream));
     B200_CUDA_TRY(cudaMemcpyToSymbolAsync(g_cfg, &c, sizeof(c), 0, cudaMemcpyHostToDevice, stream));
     B200_CUDA_TRY(cudaStreamSynchronize(stream));  // c lives on this stack frame

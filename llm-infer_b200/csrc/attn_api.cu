@@ -55,6 +55,9 @@ bool valid_dtype(int32_t d) { return d == ATTN_DTYPE_F32 || d == ATTN_DTYPE_F16 
 // extra memory parallelism.
 constexpr uint32_t kMinRowsPerCta = 64;
 
+// Largest number of partials per segment for which the last-arriving CTA merges them itself.
+constexpr uint32_t kFusedMaxParts = 0;
+
 }  // namespace
 }  // namespace b200
 
@@ -70,7 +73,14 @@ size_t attn_decode_workspace_bytes(uint32_t batch, uint32_t n_heads, uint32_t n_
     return plan.workspace_bytes;
 }
 
-int attn_decode(const AttnDecodeArgs* a, void* stream_v) {
+}  // extern "C"
+
+namespace {
+struct Exchange {
+    const AttnDecodeShardedArgs* s;
+};
+
+int decode_impl(const AttnDecodeArgs* a, void* stream_v, const Exchange* xchg) {
     if (!a || !a->o || !a->q || !a->k || !a->v) return ATTN_ERR_INVALID_ARG;
     if (!valid_dtype(a->o_dtype) || !valid_dtype(a->q_dtype)) return ATTN_ERR_INVALID_ARG;
     if (a->kv_dtype != ATTN_DTYPE_F16 && a->kv_dtype != ATTN_DTYPE_BF16) return ATTN_ERR_UNSUPPORTED;
@@ -123,8 +133,20 @@ int attn_decode(const AttnDecodeArgs* a, void* stream_v) {
 
     const bool kv_bf16 = a->kv_dtype == ATTN_DTYPE_BF16;
     const bool qsplit = a->q_dtype != ATTN_DTYPE_F16;
-    rc = launch_decode_split(p, a->head_dim, plan.hpc, qsplit, kv_bf16, plan.grid, plan.smem_bytes, stream);
-    if (rc != ATTN_OK) return rc;
+    // Single-launch mode: when every segment is shared by only a few CTAs (batched decode), the CTA that delivers a
+    // segment's last partial merges it and there is no merge pass. With many partials per segment (one long
+    // sequence) that one CTA would be slow, and the parallel merge pass is used instead.
+    const uint32_t parts_per_segment = (plan.grid + plan.nseg - 1) / plan.nseg + 1;
+    const bool fused = !xchg && !kv_bf16 && a->kv_len == nullptr && parts_per_segment <= kFusedMaxParts;
+    if (fused) {
+        p.o = a->o;
+        p.lse = a->lse;
+        p.o_dtype = a->o_dtype;
+        p.counters = p.seg_prefix + plan.prefix_words;
+        B200_CUDA_TRY(cudaMemsetAsync(p.counters, 0, static_cast<size_t>(plan.nseg) * 4, stream));
+    }
+    rc = launch_decode_split(p, a->head_dim, plan.hpc, qsplit, kv_bf16, fused, plan.grid, plan.smem_bytes, stream);
+    if (rc != ATTN_OK || fused) return rc;
 
     MergeParams m{};
     m.o = a->o;
@@ -147,7 +169,39 @@ int attn_decode(const AttnDecodeArgs* a, void* stream_v) {
     m.max_ctas = p.max_ctas;
     m.min_tiles_per_cta = p.min_tiles_per_cta;
     m.seg_prefix = p.seg_prefix;
+    m.status = a->status;
+    if (xchg) {
+        const AttnDecodeShardedArgs* s = xchg->s;
+        m.xchg_world = s->world_size;
+        m.xchg_rank = s->rank;
+        m.xchg_step = s->step;
+        m.xchg_poll_limit = s->poll_limit ? s->poll_limit : (1u << 23);
+        for (uint32_t r = 0; r < s->world_size; ++r) m.xchg_peers[r] = static_cast<float*>(s->peer_buffers[r]);
+    }
     return launch_merge(m, stream, /*dependent_launch=*/true);
+}
+}  // namespace
+
+extern "C" {
+
+int attn_decode(const AttnDecodeArgs* a, void* stream_v) { return decode_impl(a, stream_v, nullptr); }
+
+size_t attn_decode_sharded_exchange_bytes(uint32_t batch, uint32_t n_heads, uint32_t head_dim, uint32_t world_size) {
+    if (world_size == 0 || world_size > ATTN_MAX_PEERS) return 0;
+    const size_t rows = static_cast<size_t>(batch) * n_heads;
+    const size_t rec_floats = rows * (static_cast<size_t>(head_dim) + 1);
+    return (2 * world_size * rec_floats + static_cast<size_t>(world_size) * rows + 4) * 4;  // records, flags, 2 control words
+}
+
+int attn_decode_sharded(const AttnDecodeShardedArgs* s, void* stream_v) {
+    if (!s) return ATTN_ERR_INVALID_ARG;
+    if (s->world_size == 0 || s->world_size > ATTN_MAX_PEERS || s->rank >= s->world_size) return ATTN_ERR_INVALID_ARG;
+    for (uint32_t r = 0; r < s->world_size; ++r) {
+        if (!s->peer_buffers[r]) return ATTN_ERR_INVALID_ARG;
+        if (reinterpret_cast<uintptr_t>(s->peer_buffers[r]) & 15u) return ATTN_ERR_ALIGNMENT;
+    }
+    Exchange x{s};
+    return decode_impl(&s->decode, stream_v, &x);
 }
 
 int attn_merge(const AttnMergeArgs* a, void* stream_v) {

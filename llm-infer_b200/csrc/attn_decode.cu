@@ -9,15 +9,16 @@ namespace {
 using decode_detail::kConsumerWarps;
 using decode_detail::kThreads;
 
-template <int D, int HPC, bool QSPLIT, bool BF16>
+// FUSED = the CTA that delivers a segment's last partial also merges it (single launch, no merge pass).
+template <int D, int HPC, bool QSPLIT, bool BF16, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const __grid_constant__ DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    decode_detail::decode_split_body<D, HPC, QSPLIT, BF16, false>(p, smem);
+    decode_detail::decode_split_body<D, HPC, QSPLIT, BF16, FUSED>(p, smem);
 }
 
-template <int D, int HPC, bool QSPLIT, bool BF16>
+template <int D, int HPC, bool QSPLIT, bool BF16, bool FUSED>
 int launch_one(const DecodeParams& p, uint32_t grid, size_t smem_bytes, cudaStream_t stream) {
-    auto kernel = decode_split_kernel<D, HPC, QSPLIT, BF16>;
+    auto kernel = decode_split_kernel<D, HPC, QSPLIT, BF16, FUSED>;
     B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem_bytes)));
     cudaLaunchConfig_t cfg{};
@@ -30,35 +31,39 @@ int launch_one(const DecodeParams& p, uint32_t grid, size_t smem_bytes, cudaStre
     return ATTN_OK;
 }
 
-template <int D, bool QSPLIT, bool BF16>
+template <int D, bool QSPLIT, bool BF16, bool FUSED>
 int launch_hpc(const DecodeParams& p, uint32_t hpc, uint32_t grid, size_t smem_bytes, cudaStream_t stream) {
     switch (hpc) {
-        case 8: return launch_one<D, 8, QSPLIT, BF16>(p, grid, smem_bytes, stream);
-        case 4: return launch_one<D, 4, QSPLIT, BF16>(p, grid, smem_bytes, stream);
-        case 2: return launch_one<D, 2, QSPLIT, BF16>(p, grid, smem_bytes, stream);
-        case 1: return launch_one<D, 1, QSPLIT, BF16>(p, grid, smem_bytes, stream);
+        case 8: return launch_one<D, 8, QSPLIT, BF16, FUSED>(p, grid, smem_bytes, stream);
+        case 4: return launch_one<D, 4, QSPLIT, BF16, FUSED>(p, grid, smem_bytes, stream);
+        case 2: return launch_one<D, 2, QSPLIT, BF16, FUSED>(p, grid, smem_bytes, stream);
+        case 1: return launch_one<D, 1, QSPLIT, BF16, FUSED>(p, grid, smem_bytes, stream);
         default: return ATTN_ERR_UNSUPPORTED;
     }
 }
 
 template <int D>
-int launch_d(const DecodeParams& p, uint32_t hpc, bool qsplit, bool kv_bf16, uint32_t grid, size_t smem_bytes,
-             cudaStream_t stream) {
+int launch_d(const DecodeParams& p, uint32_t hpc, bool qsplit, bool kv_bf16, bool fused, uint32_t grid,
+             size_t smem_bytes, cudaStream_t stream) {
     if (kv_bf16) {
-        // bf16 MMA operands: Q and P always carry a residual term (8-bit significand otherwise)
-        return launch_hpc<D, true, true>(p, hpc, grid, smem_bytes, stream);
+        // bf16 MMA operands: Q and P always carry a residual term (8-bit significand otherwise); two-pass only
+        return launch_hpc<D, true, true, false>(p, hpc, grid, smem_bytes, stream);
     }
-    return qsplit ? launch_hpc<D, true, false>(p, hpc, grid, smem_bytes, stream)
-                  : launch_hpc<D, false, false>(p, hpc, grid, smem_bytes, stream);
+    if (fused) {
+        return qsplit ? launch_hpc<D, true, false, true>(p, hpc, grid, smem_bytes, stream)
+                      : launch_hpc<D, false, false, true>(p, hpc, grid, smem_bytes, stream);
+    }
+    return qsplit ? launch_hpc<D, true, false, false>(p, hpc, grid, smem_bytes, stream)
+                  : launch_hpc<D, false, false, false>(p, hpc, grid, smem_bytes, stream);
 }
 
 }  // namespace
 
-int launch_decode_split(const DecodeParams& p, uint32_t head_dim, uint32_t hpc, bool qsplit, bool kv_bf16,
+int launch_decode_split(const DecodeParams& p, uint32_t head_dim, uint32_t hpc, bool qsplit, bool kv_bf16, bool fused,
                         uint32_t grid, size_t smem_bytes, cudaStream_t stream) {
     switch (head_dim) {
-        case 128: return launch_d<128>(p, hpc, qsplit, kv_bf16, grid, smem_bytes, stream);
-        case 64: return launch_d<64>(p, hpc, qsplit, kv_bf16, grid, smem_bytes, stream);
+        case 128: return launch_d<128>(p, hpc, qsplit, kv_bf16, fused, grid, smem_bytes, stream);
+        case 64: return launch_d<64>(p, hpc, qsplit, kv_bf16, fused, grid, smem_bytes, stream);
         default: return ATTN_ERR_UNSUPPORTED;
     }
 }
@@ -90,7 +95,9 @@ int make_decode_plan(uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint
     const size_t rows = slots * pl.ts * pl.hpc * pl.group;
     pl.part_o_floats = rows * head_dim;
     pl.part_lse_floats = (rows + 3) & ~static_cast<size_t>(3);
-    pl.workspace_bytes = (pl.part_o_floats + pl.part_lse_floats) * 4 + ((static_cast<size_t>(pl.nseg) + 1 + 3) & ~3ull) * 4;
+    // partials, LSEs, tile prefix [nseg+1], arrival counters [nseg] of the single-launch mode
+    pl.prefix_words = (static_cast<size_t>(pl.nseg) + 1 + 3) & ~3ull;
+    pl.workspace_bytes = (pl.part_o_floats + pl.part_lse_floats + pl.prefix_words + ((static_cast<size_t>(pl.nseg) + 3) & ~3ull)) * 4;
     *plan = pl;
     return ATTN_OK;
 }

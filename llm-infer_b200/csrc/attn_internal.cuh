@@ -78,6 +78,16 @@ struct MergeParams {
     uint32_t max_ctas;
     uint32_t min_tiles_per_cta;
     const uint32_t* seg_prefix;
+    // cross-GPU exchange (xchg_world > 0): the locally merged row is stored into every rank's exchange buffer over
+    // NVLink, a per-row flag is raised on each of them, and the row is finished by merging the xchg_world records
+    // that arrived in this GPU's own buffer. Buffer layout, in floats: rec[2 (step parity)][world][rows*(D+1)]
+    // (O rows, then LSE), followed by uint32 flags[world][rows].
+    float* xchg_peers[ATTN_MAX_PEERS];
+    uint32_t xchg_world;
+    uint32_t xchg_rank;
+    uint32_t xchg_step;
+    uint32_t xchg_poll_limit;
+    uint32_t* status;
 };
 
 // Number of CTAs that actually take tiles, identical in the split and merge passes.
@@ -121,7 +131,7 @@ struct DeviceInfo {
 // Properties of the current device (cached per device; no allocation).
 int current_device_info(DeviceInfo* out);
 
-int launch_decode_split(const DecodeParams& p, uint32_t head_dim, uint32_t hpc, bool qsplit, bool kv_bf16,
+int launch_decode_split(const DecodeParams& p, uint32_t head_dim, uint32_t hpc, bool qsplit, bool kv_bf16, bool fused,
                         uint32_t grid, size_t smem_bytes, cudaStream_t stream);
 int launch_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch);
 
@@ -138,6 +148,7 @@ struct DecodePlan {
     size_t smem_bytes;
     size_t part_o_floats;
     size_t part_lse_floats;
+    size_t prefix_words;
     size_t workspace_bytes;
 };
 int make_decode_plan(uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, const DeviceInfo& dev,

@@ -11,6 +11,8 @@
 //   * the decode split pass (partials of consecutive slots, located per row),
 //   * attn_merge(): partials stacked with a constant stride, e.g. the all-gather
 //     buffer of the KV-sharded multi-GPU decode.
+// With an exchange descriptor (attn_decode_sharded) the same kernel also carries the collective of the multi-GPU
+// path: peer stores of the merged row, per-row flags, bounded wait, merge of the arrived records.
 #include "attn_internal.cuh"
 #include "merge_device.cuh"
 #include "ptx_sm100.cuh"
@@ -19,10 +21,10 @@ namespace b200 {
 
 namespace {
 
-constexpr int kMergeWarps = 4;
+constexpr int kMergeWarps = 8;
 constexpr int kMergeThreads = kMergeWarps * 32;
 
-// One CTA per output row. The four warps take every fourth partial each (so that up to a few hundred
+// One CTA per output row. The eight warps take every eighth partial each (so that up to a few hundred
 // partials of a long single sequence are fetched with many loads in flight) and combine through shared memory.
 template <int VEC, int CHUNKS>
 __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_constant__ MergeParams p) {
@@ -95,7 +97,9 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
     for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     if (lane == 0) s_red[0][warp] = mx;
     __syncthreads();
-    mx = fmaxf(fmaxf(s_red[0][0], s_red[0][1]), fmaxf(s_red[0][2], s_red[0][3]));
+    mx = s_red[0][0];
+#pragma unroll
+    for (int w = 1; w < kMergeWarps; ++w) mx = fmaxf(mx, s_red[0][w]);
     float z = 0.f;
     if (mx != -INFINITY) {
         for (uint32_t i = tid; i < n; i += kMergeThreads) z += __expf(__ldcg(pl + i * l_stride) - mx);
@@ -104,10 +108,12 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
     for (int off = 16; off; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
     if (lane == 0) s_red[1][warp] = z;
     __syncthreads();
-    z = s_red[1][0] + s_red[1][1] + s_red[1][2] + s_red[1][3];
+    z = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMergeWarps; ++w) z += s_red[1][w];
     const float inv_z = z > 0.f ? 1.f / z : 0.f;
 
-    // pass 2: warp w accumulates partials w, w + 4, ...
+    // pass 2: warp w accumulates partials w, w + 8, ...
     float acc[CHUNKS][VEC];
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c)
@@ -132,11 +138,103 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
 #pragma unroll
         for (int e = 0; e < VEC; ++e) s_acc[warp][c * 32 * VEC + lane * VEC + e] = acc[c][e];
     __syncthreads();
-    for (int d = tid; d < HEAD_DIM; d += kMergeThreads) {
-        const float x = (s_acc[0][d] + s_acc[1][d]) + (s_acc[2][d] + s_acc[3][d]);
-        store_out(p.o, p.o_dtype, static_cast<size_t>(row) * HEAD_DIM + d, x);
+    const float lse_local = z > 0.f ? mx + logf(z) : -INFINITY;
+    if (p.xchg_world == 0) {
+        for (int d = tid; d < HEAD_DIM; d += kMergeThreads) {
+            float x = 0.f;
+#pragma unroll
+            for (int w = 0; w < kMergeWarps; ++w) x += s_acc[w][d];
+            store_out(p.o, p.o_dtype, static_cast<size_t>(row) * HEAD_DIM + d, x);
+        }
+        if (p.lse && tid == 0) p.lse[row] = lse_local;
+        return;
     }
-    if (p.lse && tid == 0) p.lse[row] = z > 0.f ? mx + logf(z) : -INFINITY;
+
+    // ---- cross-GPU part: compute step followed by its collective, in the same kernel -------------------------
+    // 1. store this rank's merged row into every rank's exchange buffer (plain stores to peer memory over NVLink),
+    // 2. system-scope fence, then raise this (rank, row)'s flag on every rank with a release store,
+    // 3. wait (bounded) until every rank's flag for this row shows the current step in the local buffer,
+    // 4. merge the records that arrived locally. Rows are independent, so a CTA waits for its own row only.
+    __shared__ uint32_t s_fail;
+    __shared__ uint32_t s_step;
+    const uint32_t world = p.xchg_world, me = p.xchg_rank, rows = p.rows;
+    const size_t rec_floats = static_cast<size_t>(rows) * (HEAD_DIM + 1);
+    const size_t flags_off = 2 * static_cast<size_t>(world) * rec_floats;
+    // control words behind the flags of the local buffer: [0] = steps completed so far, [1] = rows finished in this step
+    uint32_t* ctl = reinterpret_cast<uint32_t*>(p.xchg_peers[me] + flags_off) + static_cast<size_t>(world) * rows;
+    if (tid == 0) {
+        s_fail = 0;
+        // step 0 in the arguments = count steps on the device (keeps the launch arguments constant, e.g. for graph replay)
+        s_step = p.xchg_step ? p.xchg_step : *reinterpret_cast<volatile uint32_t*>(ctl) + 1u;
+    }
+    __syncthreads();
+    const uint32_t step = s_step;
+    const size_t rec_me = ((step & 1u) * world + me) * rec_floats;
+    // Every CTA of this launch has read the step by now or will before it finishes its own row, and the counter only
+    // advances after all rows have finished, so all rows of one launch agree on the step.
+    auto finish_row = [&]() {
+        if (p.xchg_step == 0 && tid == 0) {
+            __threadfence();
+            if (atomicAdd(ctl + 1, 1u) == rows - 1) {
+                ctl[1] = 0;
+                __threadfence();
+                atomicAdd(ctl, 1u);
+            }
+        }
+    };
+    for (int d = tid; d < HEAD_DIM; d += kMergeThreads) {
+        float x = 0.f;
+#pragma unroll
+            for (int w = 0; w < kMergeWarps; ++w) x += s_acc[w][d];
+        for (uint32_t r = 0; r < world; ++r) p.xchg_peers[r][rec_me + static_cast<size_t>(row) * HEAD_DIM + d] = x;
+    }
+    if (tid == 0) {
+        for (uint32_t r = 0; r < world; ++r) p.xchg_peers[r][rec_me + static_cast<size_t>(rows) * HEAD_DIM + row] = lse_local;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < static_cast<int>(world)) {
+        uint32_t* remote = reinterpret_cast<uint32_t*>(p.xchg_peers[tid] + flags_off) + static_cast<size_t>(me) * rows + row;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(step) : "memory");
+        const uint32_t* local = reinterpret_cast<const uint32_t*>(p.xchg_peers[me] + flags_off) + static_cast<size_t>(tid) * rows + row;
+        bool seen = false;
+        for (uint32_t it = 0; it < p.xchg_poll_limit; ++it) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
+            if (v == step) { seen = true; break; }
+            __nanosleep(64);
+        }
+        if (!seen) {
+            // a peer never delivered this row: report it and leave the output row untouched
+            if (p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+            atomicExch(&s_fail, 1u);
+        }
+    }
+    __syncthreads();
+    if (s_fail) {
+        finish_row();
+        return;
+    }
+    const float* mine = p.xchg_peers[me] + (step & 1u) * world * rec_floats;
+    float gmx = -INFINITY;
+    for (uint32_t r = 0; r < world; ++r) gmx = fmaxf(gmx, __ldcg(mine + r * rec_floats + static_cast<size_t>(rows) * HEAD_DIM + row));
+    float gz = 0.f;
+    if (gmx != -INFINITY) {
+        for (uint32_t r = 0; r < world; ++r) gz += __expf(__ldcg(mine + r * rec_floats + static_cast<size_t>(rows) * HEAD_DIM + row) - gmx);
+    }
+    const float inv_gz = gz > 0.f ? 1.f / gz : 0.f;
+    for (int d = tid; d < HEAD_DIM; d += kMergeThreads) {
+        float acc_d = 0.f;
+        if (gmx != -INFINITY) {
+            for (uint32_t r = 0; r < world; ++r) {
+                const float w = __expf(__ldcg(mine + r * rec_floats + static_cast<size_t>(rows) * HEAD_DIM + row) - gmx) * inv_gz;
+                acc_d = fmaf(w, __ldcg(mine + r * rec_floats + static_cast<size_t>(row) * HEAD_DIM + d), acc_d);
+            }
+        }
+        store_out(p.o, p.o_dtype, static_cast<size_t>(row) * HEAD_DIM + d, acc_d);
+    }
+    if (p.lse && tid == 0) p.lse[row] = gz > 0.f ? gmx + logf(gz) : -INFINITY;
+    finish_row();
 }
 
 template <int VEC, int CHUNKS>

@@ -107,8 +107,8 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     unsigned char* tiles = smem;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(nst) * 2 * TILEB);
     uint32_t* prefix = reinterpret_cast<uint32_t*>(bars + 3 * nst);
-    // fused mode: lengths are uniform, so the prefix area is unused and its first word carries the ticket
-    volatile uint32_t* s_ticket = prefix;
+    // fused mode: one word behind the prefix area carries the arrival ticket from thread 0 to the other warps
+    volatile uint32_t* s_ticket = prefix + nseg + 1;
     const uint32_t bar_full_k = smem_u32(bars);
     const uint32_t bar_full_v = bar_full_k + 8 * nst;
     const uint32_t bar_empty = bar_full_v + 8 * nst;

@@ -97,3 +97,43 @@ class ShardedDecode:
         with torch.cuda.graph(graph):
             self(q, k_shard, v_shard, kv_len_local, out=out)
         return graph
+
+
+class FusedShardedDecode:
+    """The same sharded decode with the collective carried by the merge kernel itself instead of NCCL.
+
+    Every rank owns an exchange buffer in symmetric (peer-mapped) memory. The merge pass of ``attn_decode_sharded``
+    stores each merged row straight into all ranks' buffers over NVLink, raises a per-row flag there, waits (bounded)
+    for the other ranks' flags of that row and finishes the row: two launches per step, no separate collective and
+    no third kernel. ``torch.distributed`` is only used to allocate and exchange the buffer handles.
+    """
+
+    def __init__(self, batch: int, n_heads: int, n_kv_heads: int, head_dim: int, *, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import attention
+        self._attention = attention
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        nbytes = attention.exchange_bytes(batch, n_heads, head_dim, self.world)
+        self.buffer = symm_mem.empty((nbytes + 3) // 4, dtype=torch.float32, device=device)
+        self.buffer.zero_()
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self.peer_buffers = [int(p) for p in self.handle.buffer_ptrs]
+        self.workspace = attention.DecodeWorkspace(batch, n_heads, n_kv_heads, head_dim, device)
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)  # every buffer is zero before anybody's first step
+
+    def __call__(self, q, k_shard, v_shard, kv_len_local=None, out=None, lse=None, out_dtype=torch.float32):
+        """q [B,H,D] (replicated); k_shard, v_shard [B,T_local,Hkv,D] (this rank's rows) -> out [B,H,D]."""
+        return self._attention.attn_decode_sharded(
+            q, k_shard, v_shard, kv_len_local, peer_buffers=self.peer_buffers, world_size=self.world, rank=self.rank,
+            step=0, out=out, lse=lse, out_dtype=out_dtype, workspace=self.workspace)
+
+    def capture(self, q, k_shard, v_shard, out, kv_len_local=None):
+        """One step as a CUDA graph (the kernel counts steps on the device, so the arguments never change)."""
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self(q, k_shard, v_shard, kv_len_local, out=out)
+        return graph

@@ -176,3 +176,55 @@ def test_merge_entry_point(attention, wl, port):
     all_empty = torch.full((3, 8), float("-inf"), device="cuda")
     z = attention.attn_merge(torch.randn(3, 8, 128, device="cuda"), all_empty)
     assert torch.equal(z, torch.zeros_like(z))
+
+
+def _sharded_single_gpu(attention, q, k, v, world, rank, bufs, out, status_ws, step=0, poll_limit=0):
+    import torch
+    return attention.attn_decode_sharded(q, k, v, peer_buffers=[b.data_ptr() for b in bufs], world_size=world,
+                                         rank=rank, step=step, poll_limit=poll_limit, out=out, workspace=status_ws)
+
+
+def test_fused_exchange_with_one_rank_equals_plain_decode(attention, wl, checker):
+    """World size 1: the exchange path (peer stores, flags, wait, cross merge) runs against the rank's own buffer."""
+    import torch
+    from gpu_util import check_close, to_device
+    q, k, v = _rand(wl, 41, 2, 32, 8, 128, 3000, "f16", "f16")
+    qd, kd, vd = to_device(q, "f16"), to_device(k, "f16"), to_device(v, "f16")
+    ws = attention.DecodeWorkspace(2, 32, 8, 128)
+    buf = torch.zeros(attention.exchange_bytes(2, 32, 128, 1) // 4, device="cuda")
+    want = checker.attn_decode(q.astype(np.float32), k, v)
+    for call in range(3):  # consecutive steps alternate the record parity and advance the device-side step counter
+        out = torch.full((2, 32, 128), float("nan"), device="cuda")
+        _sharded_single_gpu(attention, qd, kd, vd, 1, 0, [buf], out, ws)
+        torch.cuda.synchronize()
+        check_close(wl, out.cpu().numpy(), want, f"fused exchange, call {call}")
+    assert int(ws.status.item()) == 0
+    ctl = buf.view(torch.int32)[-4:-2].tolist()
+    assert ctl == [3, 0]  # three steps completed, no row pending
+
+
+def test_fused_exchange_times_out_cleanly_when_a_peer_never_arrives(attention, wl, checker):
+    """World size 2 with nobody playing rank 1: the wait on rank 1's flags must run out, set the status bit and leave
+    the output untouched; the context stays usable (a normal decode works right after)."""
+    import torch
+    from gpu_util import check_close, to_device
+    q, k, v = _rand(wl, 42, 1, 32, 8, 128, 500, "f16", "f16")
+    qd, kd, vd = to_device(q, "f16"), to_device(k, "f16"), to_device(v, "f16")
+    ws = attention.DecodeWorkspace(1, 32, 8, 128)
+    n = attention.exchange_bytes(1, 32, 128, 2) // 4
+    mine, absent_peer = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    out = torch.full((1, 32, 128), float("nan"), device="cuda")
+    _sharded_single_gpu(attention, qd, kd, vd, 2, 0, [mine, absent_peer], out, ws, step=1, poll_limit=200)
+    torch.cuda.synchronize()
+    assert int(ws.status.item()) & 1  # ATTN_STATUS_WAIT_TIMEOUT
+    assert torch.isnan(out).all()
+    # this rank's record did reach the "peer": what a live rank 1 would have merged
+    rec = absent_peer[: 32 * 129]  # parity 1, source rank 0 -> offset (1*2+0)*rec_floats
+    rec = absent_peer[2 * 32 * 129: 3 * 32 * 129]
+    want = checker.attn_decode(q.astype(np.float32), k, v)
+    check_close(wl, rec[: 32 * 128].view(1, 32, 128).cpu().numpy(), want, "record delivered to the peer buffer")
+    ws.status.zero_()
+    got = attention.attn_decode(qd, kd, vd, workspace=ws)
+    torch.cuda.synchronize()
+    check_close(wl, got.cpu().numpy(), want, "decode after a timed-out exchange")
+    assert int(ws.status.item()) == 0
