@@ -120,16 +120,30 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
 #pragma unroll
         for (int e = 0; e < VEC; ++e) acc[c][e] = 0.f;
     if (mx != -INFINITY) {
-#pragma unroll 8
-        for (uint32_t i = warp; i < n; i += kMergeWarps) {
-            const float w = __expf(__ldcg(pl + i * l_stride) - mx) * inv_z;
-            const float* src = po + i * o_stride + lane * VEC;
+        // four partials per round, all eight loads (LSE and O) issued before any is used: with up to a few hundred
+        // partials per row (one long sequence) this loop is bound by L2 latency, not bandwidth
+        constexpr int kBatch = 4;
+        for (uint32_t i0 = warp; i0 < n; i0 += kMergeWarps * kBatch) {
+            float lw[kBatch];
+            V x[kBatch][CHUNKS];
 #pragma unroll
-            for (int c = 0; c < CHUNKS; ++c) {
-                V x = __ldcg(reinterpret_cast<const V*>(src + c * 32 * VEC));
-                const float* xs = reinterpret_cast<const float*>(&x);
+            for (int b = 0; b < kBatch; ++b) {
+                const uint32_t i = i0 + b * kMergeWarps;
+                const bool valid = i < n;
+                lw[b] = valid ? __ldcg(pl + i * l_stride) : -INFINITY;
+                const float* src = po + (valid ? i : 0) * o_stride + lane * VEC;
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) acc[c][e] = fmaf(w, xs[e], acc[c][e]);
+                for (int c = 0; c < CHUNKS; ++c) x[b][c] = __ldcg(reinterpret_cast<const V*>(src + c * 32 * VEC));
+            }
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                const float w = __expf(lw[b] - mx) * inv_z;  // 0 for the padding of the last round
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c) {
+                    const float* xs = reinterpret_cast<const float*>(&x[b][c]);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) acc[c][e] = fmaf(w, xs[e], acc[c][e]);
+                }
             }
         }
     }
