@@ -118,6 +118,33 @@ typedef struct AttnPrefillArgs {
 
 int attn_prefill_causal(const AttnPrefillArgs* args, void* stream);
 
+/* The step in front of decode attention, for a batch of sequences in one launch: rotary embedding of the current
+ * token's Q and K (adjacent pairs, freq_i = 1/powf(theta, i/rotary_dim), include/kernels_cpu.hpp:82-100), fp16
+ * round-to-nearest-even insert of K and V into cache row kv_pos (src/model/block.cpp:144-148; on the GPU
+ * src/model/block.cu:96-110,147-161), and the one-position re-rotation of the first kv_sink cached K rows
+ * (src/model/block.cpp:150-155, src/model/block.cu:165-205). */
+typedef struct AttnRopeInsertArgs {
+    void* q_out;           /* out: rotated q [batch][n_heads][head_dim], q_out_dtype; may be the same buffer as q (fp32) */
+    const float* q;        /* in : [batch][n_heads][head_dim] fp32 (InferenceState::q) */
+    const float* k;        /* in : [batch][n_kv_heads][head_dim] fp32, before rotation */
+    const float* v;        /* in : [batch][n_kv_heads][head_dim] fp32 */
+    void* k_cache;         /* fp16, sequence b at + b*kv_batch_stride, row t at + t*kv_row_stride (elements) */
+    void* v_cache;
+    const float* inv_freq; /* optional device array [rotary_dim/2] = 1/powf(theta, 2i/rotary_dim) computed on the host
+                              (bit-identical to the CPU path); NULL = evaluated on the device in double precision */
+    const uint32_t* pos;    /* device [batch]: position of the token (rotation angle) */
+    const uint32_t* kv_pos; /* device [batch]: cache row that receives the token */
+    uint64_t kv_row_stride;   /* 0 = n_kv_heads*head_dim */
+    uint64_t kv_batch_stride; /* may be 0 only when batch == 1 */
+    uint32_t batch, n_heads, n_kv_heads, head_dim;
+    uint32_t rotary_dim;   /* 0 = head_dim */
+    uint32_t kv_sink;      /* number of sink rows to re-rotate (KV_SINK = 4 once the window is full, else 0) */
+    float theta;
+    int32_t q_out_dtype;   /* ATTN_DTYPE_F32 | F16 | BF16 */
+} AttnRopeInsertArgs;
+
+int attn_rope_kv_insert(const AttnRopeInsertArgs* args, void* stream);
+
 /* Size of the built-in scratch array used by attn_decode_static_scratch(). */
 #define ATTN_STATIC_SCRATCH_BYTES (8u << 20)
 

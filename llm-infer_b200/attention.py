@@ -166,6 +166,38 @@ def attn_prefill_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, ou
     return out
 
 
+def rope_kv_insert(q, k, v, k_cache, v_cache, pos, kv_pos, *, theta: float, rotary_dim: int = 0, kv_sink: int = 0,
+                   inv_freq=None, q_out=None, q_out_dtype=torch.float32, stream=None) -> torch.Tensor:
+    """Rotate the current token's q and k, insert k and v (fp16) into the caches, re-rotate the sink rows.
+
+    q [B,H,D], k / v [B,Hkv,D] fp32; k_cache / v_cache fp16 [B,T,Hkv,D]; pos, kv_pos int32 CUDA tensors [B].
+    Returns the rotated q (``q_out``, fp32 / fp16 / bf16). Mirrors src/model/block.cpp:140-155 for a batch.
+    """
+    _require_cuda(q, k, v, k_cache, v_cache, pos, kv_pos)
+    B, H, D = q.shape
+    Hkv = k.shape[1]
+    if k.shape != (B, Hkv, D) or v.shape != k.shape or k_cache.shape[0] != B or k_cache.shape[2:] != (Hkv, D):
+        raise ValueError("shape mismatch")
+    if q.dtype != torch.float32 or k.dtype != torch.float32 or v.dtype != torch.float32 or k_cache.dtype != torch.float16:
+        raise TypeError("q, k, v must be fp32 and the caches fp16")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if q_out is None:
+        q_out = torch.empty((B, H, D), dtype=q_out_dtype, device=q.device)
+    a = _b.AttnRopeInsertArgs()
+    a.q_out, a.q, a.k, a.v = q_out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.k_cache, a.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+    a.inv_freq = inv_freq.data_ptr() if inv_freq is not None else None
+    a.pos, a.kv_pos = pos.data_ptr(), kv_pos.data_ptr()
+    a.kv_row_stride = k_cache.stride(1)
+    a.kv_batch_stride = k_cache.stride(0) if B > 1 else max(k_cache.stride(0), 0)
+    a.batch, a.n_heads, a.n_kv_heads, a.head_dim = B, H, Hkv, D
+    a.rotary_dim, a.kv_sink, a.theta = rotary_dim, kv_sink, float(theta)
+    a.q_out_dtype = _dtype_code(q_out)
+    with torch.cuda.device(q.device):
+        _b.check(_b.load().attn_rope_kv_insert(C.byref(a), _stream_ptr(stream)), "attn_rope_kv_insert")
+    return q_out
+
+
 def attn_merge(part_o: torch.Tensor, part_lse: torch.Tensor, *, out=None, lse=None, out_dtype=torch.float32,
                stream=None) -> torch.Tensor:
     """Online-softmax merge of partial results (src/attention.cu:41-65 in log-sum-exp form).

@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "attn_decode_sharded",
     "attn_merge",
     "attn_prefill_causal",
+    "attn_rope_kv_insert",
     "attn_status_string",
     "attn_last_cuda_error",
     "attn_kernel_launch_count",
@@ -103,6 +104,30 @@ class AttnPrefillArgs(C.Structure):
     ]
 
 
+class AttnRopeInsertArgs(C.Structure):
+    _fields_ = [
+        ("q_out", C.c_void_p),
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p),
+        ("inv_freq", C.c_void_p),
+        ("pos", C.c_void_p),
+        ("kv_pos", C.c_void_p),
+        ("kv_row_stride", C.c_uint64),
+        ("kv_batch_stride", C.c_uint64),
+        ("batch", C.c_uint32),
+        ("n_heads", C.c_uint32),
+        ("n_kv_heads", C.c_uint32),
+        ("head_dim", C.c_uint32),
+        ("rotary_dim", C.c_uint32),
+        ("kv_sink", C.c_uint32),
+        ("theta", C.c_float),
+        ("q_out_dtype", C.c_int32),
+    ]
+
+
 class AttnMergeArgs(C.Structure):
     _fields_ = [
         ("o", C.c_void_p),
@@ -151,6 +176,8 @@ def load() -> C.CDLL:
     lib.attn_decode_sharded.argtypes = [C.POINTER(AttnDecodeShardedArgs), C.c_void_p]
     lib.attn_prefill_causal.restype = C.c_int
     lib.attn_prefill_causal.argtypes = [C.POINTER(AttnPrefillArgs), C.c_void_p]
+    lib.attn_rope_kv_insert.restype = C.c_int
+    lib.attn_rope_kv_insert.argtypes = [C.POINTER(AttnRopeInsertArgs), C.c_void_p]
     lib.attn_merge.restype = C.c_int
     lib.attn_merge.argtypes = [C.POINTER(AttnMergeArgs), C.c_void_p]
     lib.attn_status_string.restype = C.c_char_p

@@ -87,7 +87,11 @@ class Oracle:
             L.oracle_attn_decode_sharded.restype = C.c_int
             L.oracle_attn_decode_sharded.argtypes = [_f32p, _f32p, _f32p, _f32p, _u16p, _u16p, C.c_uint32,
                                                      C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_size_t]
+            L.oracle_rope_kv_insert.argtypes = [_f32p, _f32p, _f32p, _u16p, _u16p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                                C.c_uint32, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32]
         else:
+            L.ref_rope_kv_insert.argtypes = [_f32p, _f32p, _f32p, _u16p, _u16p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                             C.c_uint32, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32]
             L.ref_f16_to_f32.restype = C.c_float
             L.ref_f16_to_f32.argtypes = [C.c_uint16]
             L.ref_f32_to_f16.restype = C.c_uint16
@@ -161,6 +165,21 @@ class Oracle:
             if rc != 0:
                 raise RuntimeError(f"oracle attn_prefill_causal failed: {rc}")
         return out
+
+    # -- rotary embedding + cache insert (the step in front of attention) --
+    def rope_kv_insert(self, q, k, v, k_cache, v_cache, pos, kv_pos, kv_sink=0, theta=10000.0, rotary_dim=None):
+        """One token of one sequence (src/model/block.cpp:140-155). q [H,D], k/v [Hkv,D] fp32; caches fp16
+        [T,Hkv,D] are updated in place (as uint16 views). Returns rotated (q, k)."""
+        q, k, v = _f32(q).copy(), _f32(k).copy(), _f32(v)
+        kc, vc = k_cache.view(np.uint16), v_cache.view(np.uint16)
+        assert kc.flags.c_contiguous and vc.flags.c_contiguous
+        H, D = q.shape
+        Hkv = k.shape[0]
+        rot = D if rotary_dim is None else rotary_dim
+        fn = self.lib.oracle_rope_kv_insert if self.kind == "port" else self.lib.ref_rope_kv_insert
+        fn(_ptr(q, _f32p), _ptr(k, _f32p), _ptr(v, _f32p), _ptr(kc, _u16p), _ptr(vc, _u16p), H, Hkv, D, rot, theta,
+           pos, kv_pos, kv_sink)
+        return q, k
 
     # -- state / merge (port only: the reference has them only as device code) --
     def state_from_rows(self, q_head, k, v, kv_head, row_begin, row_end):

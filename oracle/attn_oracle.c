@@ -367,3 +367,52 @@ int oracle_attn_decode_sharded(float* out, float* part_o, float* part_lse, const
     }
     return fail ? -1 : 0;
 }
+
+/* ------------------------------------------------ rotary embedding + cache insert */
+
+/* include/kernels_cpu.hpp:82-100: adjacent pairs (i, i+1), freq = 1 / powf(theta, i / rotary_dim), angle = pos * freq,
+ * all in fp32 with the C library's powf / cosf / sinf. Dimensions >= rotary_dim are left alone. */
+void oracle_rope_f32(float* vec, uint32_t n_heads, uint32_t head_dim, uint32_t pos, float theta, uint32_t rotary_dim) {
+    for (uint32_t h = 0; h < n_heads; ++h) {
+        float* x = vec + (size_t)h * head_dim;
+        for (uint32_t i = 0; i < rotary_dim; i += 2) {
+            float freq = 1.0f / powf(theta, (float)i / (float)rotary_dim);
+            float deg = (float)pos * freq;
+            float c = cosf(deg), s = sinf(deg);
+            float v0 = x[i], v1 = x[i + 1];
+            x[i] = v0 * c - v1 * s;
+            x[i + 1] = v0 * s + v1 * c;
+        }
+    }
+}
+
+/* include/kernels_cpu.hpp:102-120: the same on fp16 storage: widen, rotate in fp32, round back (nearest even). */
+void oracle_rope_f16(uint16_t* vec, uint32_t n_heads, uint32_t head_dim, uint32_t pos, float theta,
+                     uint32_t rotary_dim) {
+    for (uint32_t h = 0; h < n_heads; ++h) {
+        uint16_t* x = vec + (size_t)h * head_dim;
+        for (uint32_t i = 0; i < rotary_dim; i += 2) {
+            float freq = 1.0f / powf(theta, (float)i / (float)rotary_dim);
+            float deg = (float)pos * freq;
+            float c = cosf(deg), s = sinf(deg);
+            float v0 = oracle_f16_to_f32(x[i]), v1 = oracle_f16_to_f32(x[i + 1]);
+            x[i] = oracle_f32_to_f16(v0 * c - v1 * s);
+            x[i + 1] = oracle_f32_to_f16(v0 * s + v1 * c);
+        }
+    }
+}
+
+/* src/model/block.cpp:140-155 for one token of one sequence: rotate q and k, store k and v as fp16 at row kv_pos,
+ * then rotate the first kv_sink cached K rows forward by one position (attention sinks of the sliding window). */
+void oracle_rope_kv_insert(float* q, float* k, const float* v, uint16_t* k_cache, uint16_t* v_cache, uint32_t n_heads,
+                           uint32_t n_kv_heads, uint32_t head_dim, uint32_t rotary_dim, float theta, uint32_t pos,
+                           uint32_t kv_pos, uint32_t kv_sink) {
+    oracle_rope_f32(q, n_heads, head_dim, pos, theta, rotary_dim);
+    oracle_rope_f32(k, n_kv_heads, head_dim, pos, theta, rotary_dim);
+    size_t row = (size_t)n_kv_heads * head_dim;
+    for (size_t i = 0; i < row; ++i) {
+        k_cache[(size_t)kv_pos * row + i] = oracle_f32_to_f16(k[i]);
+        v_cache[(size_t)kv_pos * row + i] = oracle_f32_to_f16(v[i]);
+    }
+    for (uint32_t s = 0; s < kv_sink; ++s) oracle_rope_f16(k_cache + (size_t)s * row, n_kv_heads, head_dim, 1, theta, rotary_dim);
+}

@@ -112,3 +112,34 @@ int ref_attn_prefill_causal_seq(float* out, const float* q, const uint16_t* k, c
 }
 
 }  // extern "C"
+
+// ---- rotary embedding and KV-cache insert (the step in front of attention) ----
+// include/kernels_cpu.hpp:82-100 (fp32) and 102-120 (fp16 in place), called from src/model/block.cpp:140-155.
+extern "C" {
+
+void ref_rope_f32(float* vec, uint32_t n_heads, uint32_t head_dim, uint32_t pos, float theta, uint32_t rotary_dim) {
+    rope(vec, n_heads, head_dim, pos, theta, rotary_dim);
+}
+
+void ref_rope_f16(uint16_t* vec, uint32_t n_heads, uint32_t head_dim, uint32_t pos, float theta, uint32_t rotary_dim) {
+    rope(vec, n_heads, head_dim, pos, theta, rotary_dim);
+}
+
+// One token of one sequence, exactly the sequence of src/model/block.cpp:140-155: rotate q and k at `pos`, store k and v
+// as fp16 at cache row kv_pos, then rotate the first kv_sink cached K rows forward by one position.
+void ref_rope_kv_insert(float* q, float* k, const float* v, uint16_t* k_cache, uint16_t* v_cache, uint32_t n_heads,
+                        uint32_t n_kv_heads, uint32_t head_dim, uint32_t rotary_dim, float theta, uint32_t pos,
+                        uint32_t kv_pos, uint32_t kv_sink) {
+    rope(q, n_heads, head_dim, pos, theta, rotary_dim);
+    rope(k, n_kv_heads, head_dim, pos, theta, rotary_dim);
+    const uint32_t kv_total_dim = n_kv_heads * head_dim;
+    for (uint32_t i = 0; i < kv_total_dim; ++i) {
+        k_cache[static_cast<size_t>(kv_pos) * kv_total_dim + i] = f32_to_f16(k[i]);
+        v_cache[static_cast<size_t>(kv_pos) * kv_total_dim + i] = f32_to_f16(v[i]);
+    }
+    for (uint32_t s = 0; s < kv_sink; ++s) {
+        rope(k_cache + static_cast<size_t>(s) * kv_total_dim, n_kv_heads, head_dim, 1, theta, rotary_dim);
+    }
+}
+
+}  // extern "C"

@@ -80,6 +80,22 @@ def main():
     sm_in = (rng.standard_normal(257) * 3).astype(np.float32)
     np.savez_compressed(os.path.join(HERE, "scalar_golden.npz"), f32=xs, f16_bits=h, softmax_in=sm_in,
                         softmax_out=ref.softmax(sm_in))
+    # ---- rotary embedding + cache insert of one token (src/model/block.cpp:140-155), three positions
+    out = {}
+    H, Hkv, D, T = 8, 2, 64, 12
+    for name, pos, kv_pos, sink, theta in (("early", 5, 5, 0, 10000.0), ("window", 4097, 9, 4, 500000.0),
+                                           ("late", 131071, 7, 4, 500000.0)):
+        q = rng.standard_normal((H, D), dtype=np.float32)
+        k = rng.standard_normal((Hkv, D), dtype=np.float32)
+        v = rng.standard_normal((Hkv, D), dtype=np.float32)
+        kc = rng.standard_normal((T, Hkv, D), dtype=np.float32).astype(np.float16)
+        vc = rng.standard_normal((T, Hkv, D), dtype=np.float32).astype(np.float16)
+        out[f"{name}.q"], out[f"{name}.k"], out[f"{name}.v"] = q, k, v
+        out[f"{name}.k_cache_in"], out[f"{name}.v_cache_in"] = kc.copy(), vc.copy()
+        out[f"{name}.args"] = np.array([pos, kv_pos, sink, theta], dtype=np.float64)
+        q_rot, _ = ref.rope_kv_insert(q, k, v, kc, vc, pos, kv_pos, sink, theta)
+        out[f"{name}.q_out"], out[f"{name}.k_cache_out"], out[f"{name}.v_cache_out"] = q_rot, kc, vc
+    np.savez_compressed(os.path.join(HERE, "rope_golden.npz"), **out)
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 

@@ -161,3 +161,17 @@ def test_kv_len_zero_gives_zeros(port, pkg):
     q, k, v = wl.decode_inputs(wl.C1, kv_len=4)
     out = port.attn_decode(q, k, v, np.zeros(1, np.uint32))
     assert np.array_equal(out, np.zeros_like(out))
+
+
+def test_rope_kv_insert_port_matches_golden(port):
+    g = np.load(os.path.join(GOLDEN, "rope_golden.npz"))
+    for name in ("early", "window", "late"):
+        pos, kv_pos, sink, theta = g[f"{name}.args"]
+        kc, vc = g[f"{name}.k_cache_in"].copy(), g[f"{name}.v_cache_in"].copy()
+        q_rot, _ = port.rope_kv_insert(g[f"{name}.q"], g[f"{name}.k"], g[f"{name}.v"], kc, vc, int(pos), int(kv_pos),
+                                       int(sink), float(theta))
+        np.testing.assert_allclose(q_rot, g[f"{name}.q_out"], rtol=0, atol=5e-7)
+        # fp16 cache contents: the fp32 values agree to an ulp, so at most a few fp16 roundings may flip by one step
+        for got, want in ((kc, g[f"{name}.k_cache_out"]), (vc, g[f"{name}.v_cache_out"])):
+            d = np.abs(got.view(np.int16).astype(np.int32) - want.view(np.int16).astype(np.int32))
+            assert d.max() <= 1 and (d != 0).mean() < 0.01
