@@ -277,20 +277,25 @@ def run_single(args):
                           "gpu_launches": int(launches)}), flush=True)
         return
 
-    # ---- end to end through the public API with host buffers: per decode step the engine moves the new token's
-    # q (and its K/V rows, appended to the resident cache) to the device and reads the attention output back.
-    q_host = qs[0].cpu().pin_memory()
-    knew_host = ks[0][:, T - 1:T].cpu().pin_memory()
-    vnew_host = vs[0][:, T - 1:T].cpu().pin_memory()
+    # ---- end to end through the public API with host buffers. One decode step of the engine's attention block:
+    # the token's fp32 q, k, v arrive from pinned host memory in one copy, attn_rope_kv_insert rotates q and k and
+    # appends k, v (fp16) to the resident cache, attn_decode attends over it, and the output is copied back and the
+    # stream synchronised before the next token. The KV cache itself stays in HBM, as the engine's per-layer cache does.
+    n_q, n_kv = B * H * D, B * Hkv * D
+    host_in = torch.randn(n_q + 2 * n_kv, dtype=torch.float32).pin_memory()
+    dev_in = torch.empty(n_q + 2 * n_kv, dtype=torch.float32, device=dev)
+    q32 = dev_in[:n_q].view(B, H, D)
+    k32 = dev_in[n_q:n_q + n_kv].view(B, Hkv, D)
+    v32 = dev_in[n_q + n_kv:].view(B, Hkv, D)
+    q_rot = torch.empty((B, H, D), dtype=torch.float16, device=dev)
+    pos_dev = torch.full((B,), T - 1, dtype=torch.int32, device=dev)
     out_host = torch.empty((B, H, D), dtype=torch.float32).pin_memory()
-    q_dev = torch.empty_like(qs[0])
 
     def e2e_step(i):
         j = i % n_sets
-        q_dev.copy_(q_host, non_blocking=True)
-        ks[j][:, T - 1:T].copy_(knew_host, non_blocking=True)
-        vs[j][:, T - 1:T].copy_(vnew_host, non_blocking=True)
-        attention.attn_decode(q_dev, ks[j], vs[j], out=out, workspace=ws)
+        dev_in.copy_(host_in, non_blocking=True)
+        attention.rope_kv_insert(q32, k32, v32, ks[j], vs[j], pos_dev, pos_dev, theta=500000.0, q_out=q_rot)
+        attention.attn_decode(q_rot, ks[j], vs[j], out=out, workspace=ws)
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result before the next token
 
@@ -298,13 +303,15 @@ def run_single(args):
         e2e_step(i)
     e2e_steps = args.steps
     e2e_ms = time_steps(torch, e2e_step, e2e_steps) / e2e_steps
-    h2d = q_host.numel() * 2 + knew_host.numel() * 2 + vnew_host.numel() * 2
+    h2d = host_in.numel() * 4
     d2h = out_host.numel() * 4
     e2e = {"value": alg_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-           "what": "q + the new token's K/V rows copied from pinned host memory, attn_decode through the C ABI, "
-                   "output copied back and the stream synchronised every step; the KV cache itself stays resident "
-                   "in HBM, as the engine's per-layer cache does"}
+           "what": "fp32 q, k, v of the token copied from pinned host memory (one copy), attn_rope_kv_insert + "
+                   "attn_decode through the C ABI, output copied back and the stream synchronised every step; the KV "
+                   "cache itself stays resident in HBM, as the engine's per-layer cache does"}
+    q_host = qs[0].cpu().pin_memory()
+    q_dev = torch.empty_like(qs[0])
 
     extra = {}
     # ---- the same call with NOTHING resident: whole KV cache copied from pinned host memory every step
@@ -325,7 +332,7 @@ def run_single(args):
         cold_ms = time_steps(torch, cold_step, n_cold) / n_cold
         extra["e2e_cold_cache"] = {"value": alg_bytes / (cold_ms * 1e-3) / 1e9, "unit": "GB/s",
                                    "ms_per_step": cold_ms,
-                                   "h2d_bytes_per_step": h2d - 2 * knew_host.numel() * 2 + 2 * k_host.numel() * 2,
+                                   "h2d_bytes_per_step": q_host.numel() * 2 + 2 * k_host.numel() * 2,
                                    "what": "whole KV cache copied host->device every step (PCIe-bound)"}
         del k_host, v_host
     except Exception as e:  # host memory for pinning may be short on some boxes; the headline does not depend on it
