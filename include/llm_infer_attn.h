@@ -145,6 +145,23 @@ typedef struct AttnRopeInsertArgs {
 
 int attn_rope_kv_insert(const AttnRopeInsertArgs* args, void* stream);
 
+/* Weight GEMV of the projections around attention: out[b][j] = clamp(sum_i x[b][i] * W[j][i]). Replaces the engine's
+ * fused_gemv_clip / fused_gemv_clip_f2h kernels (include/kernels.cuh:13-16, src/kernels.cu:117-136,229-239) and
+ * matches its CPU matmul() (include/kernels_cpu.hpp:69-80) with the clamp of src/model/block.cpp:130-138. */
+typedef struct AttnGemvArgs {
+    void* out;          /* [batch][d] fp32 or fp16, sequence b at out + b*out_batch_stride (elements) */
+    const float* x;     /* [batch][n] fp32, dense, 16-byte aligned */
+    const void* w;      /* [d][n] fp16, n fastest (GGUF dims [n_in, n_out]), 32-byte aligned */
+    uint64_t out_batch_stride; /* 0 = d */
+    uint32_t n;         /* multiple of 512; batch*n*4 bytes must fit in shared memory */
+    uint32_t d;
+    uint32_t batch;     /* 1 .. 8 */
+    float clip;         /* > 0: clamp to [-clip, clip]; 0 = none */
+    int32_t out_dtype;  /* ATTN_DTYPE_F32 | ATTN_DTYPE_F16 */
+} AttnGemvArgs;
+
+int attn_gemv_f16(const AttnGemvArgs* args, void* stream);
+
 /* Size of the built-in scratch array used by attn_decode_static_scratch(). */
 #define ATTN_STATIC_SCRATCH_BYTES (8u << 20)
 

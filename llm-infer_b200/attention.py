@@ -198,6 +198,29 @@ def rope_kv_insert(q, k, v, k_cache, v_cache, pos, kv_pos, *, theta: float, rota
     return q_out
 
 
+def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.float32, clip: float = 0.0,
+             stream=None) -> torch.Tensor:
+    """out[b] = clamp(W x[b]): x [B, n] fp32, w [d, n] fp16 (n fastest) -> out [B, d] fp32 or fp16 (may be a strided
+    view, e.g. a KV-cache row per sequence). Mirrors matmul() of include/kernels_cpu.hpp:69-80 for a batch."""
+    _require_cuda(x, w)
+    B, n = x.shape
+    d = w.shape[0]
+    if w.shape != (d, n) or w.dtype != torch.float16 or x.dtype != torch.float32:
+        raise ValueError("x must be fp32 [B, n] and w fp16 [d, n]")
+    x, w = x.contiguous(), w.contiguous()
+    if out is None:
+        out = torch.empty((B, d), dtype=out_dtype, device=x.device)
+    if out.shape != (B, d) or out.stride(1) != 1:
+        raise ValueError("out must be [B, d] with dense rows")
+    a = _b.AttnGemvArgs()
+    a.out, a.x, a.w = out.data_ptr(), x.data_ptr(), w.data_ptr()
+    a.out_batch_stride = out.stride(0) if B > 1 else d
+    a.n, a.d, a.batch, a.clip, a.out_dtype = n, d, B, float(clip), _dtype_code(out)
+    with torch.cuda.device(x.device):
+        _b.check(_b.load().attn_gemv_f16(C.byref(a), _stream_ptr(stream)), "attn_gemv_f16")
+    return out
+
+
 def attn_merge(part_o: torch.Tensor, part_lse: torch.Tensor, *, out=None, lse=None, out_dtype=torch.float32,
                stream=None) -> torch.Tensor:
     """Online-softmax merge of partial results (src/attention.cu:41-65 in log-sum-exp form).

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "attn_merge",
     "attn_prefill_causal",
     "attn_rope_kv_insert",
+    "attn_gemv_f16",
     "attn_status_string",
     "attn_last_cuda_error",
     "attn_kernel_launch_count",
@@ -128,6 +129,20 @@ class AttnRopeInsertArgs(C.Structure):
     ]
 
 
+class AttnGemvArgs(C.Structure):
+    _fields_ = [
+        ("out", C.c_void_p),
+        ("x", C.c_void_p),
+        ("w", C.c_void_p),
+        ("out_batch_stride", C.c_uint64),
+        ("n", C.c_uint32),
+        ("d", C.c_uint32),
+        ("batch", C.c_uint32),
+        ("clip", C.c_float),
+        ("out_dtype", C.c_int32),
+    ]
+
+
 class AttnMergeArgs(C.Structure):
     _fields_ = [
         ("o", C.c_void_p),
@@ -176,6 +191,8 @@ def load() -> C.CDLL:
     lib.attn_decode_sharded.argtypes = [C.POINTER(AttnDecodeShardedArgs), C.c_void_p]
     lib.attn_prefill_causal.restype = C.c_int
     lib.attn_prefill_causal.argtypes = [C.POINTER(AttnPrefillArgs), C.c_void_p]
+    lib.attn_gemv_f16.restype = C.c_int
+    lib.attn_gemv_f16.argtypes = [C.POINTER(AttnGemvArgs), C.c_void_p]
     lib.attn_rope_kv_insert.restype = C.c_int
     lib.attn_rope_kv_insert.argtypes = [C.POINTER(AttnRopeInsertArgs), C.c_void_p]
     lib.attn_merge.restype = C.c_int

@@ -1,0 +1,159 @@
+// Weight GEMV for the projections around attention (Q/K/V, output, FFN, classifier): out[b][j] = sum_i x[b][i] *
+// W[j][i] with fp16 weights stored [d][n] (n fastest) and fp32 activations, fp32 accumulation, optional symmetric
+// clamp, fp32 or fp16 result (the fp16 form writes V straight into its KV-cache row).
+//
+// Replaces the engine's warp-per-row kernels fused_gemv_clip / fused_gemv_clip_f2h (src/kernels.cu:117-136,229-239,
+// scalar 2-byte loads) and matches its CPU matmul() (include/kernels_cpu.hpp:69-80) with the clamp of
+// src/model/block.cpp:130-138 (both sides; the engine's GPU kernel clamps only from above, src/kernels.cu:218-227,
+// which the CPU path - the model of record - does not).
+//
+// HBM-bound: every weight byte is read exactly once per call, whatever the batch. One persistent CTA per SM, 16
+// warps; the activations of all sequences of the batch are staged once in shared memory (fp32); each warp owns
+// output rows j, j + #warps, ... and streams a row with 256-bit loads, eight in flight per lane (128 KB in flight per
+// SM), streaming (no-allocate) cache policy. Algorithmic bytes per call = d*n*2 + batch*(n*4 + d*sizeof(out)).
+#include "attn_internal.cuh"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kGemvWarps = 16;
+constexpr int kGemvThreads = kGemvWarps * 32;
+constexpr int kUnroll = 8;  // 32-byte loads in flight per lane (a whole 8 KB row per warp and round)
+
+struct GemvParams {
+    void* out;
+    const float* x;
+    const uint16_t* w;
+    uint64_t out_batch_stride;
+    uint32_t n, d;
+    float clip;
+    int32_t out_dtype;
+};
+
+struct alignas(32) U8 {
+    uint32_t v[8];
+};
+
+// 256-bit streaming load (sm_100): read-only path, no L1 allocation, evict-first in L2.
+__device__ __forceinline__ U8 ld_stream32(const void* p) {
+    U8 r;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]), "=r"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+
+template <int BATCH>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_f16_kernel(const __grid_constant__ GemvParams p) {
+    extern __shared__ __align__(16) float s_x[];  // [BATCH][n]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // Activations are staged permuted: inside every span of 512 elements, the four elements (16L + 4q .. +3) that
+    // lane L multiplies with the q-th quarter of its 32-byte weight chunk are stored at q*128 + 4L, so that the 32
+    // lanes of a warp read 512 consecutive bytes (no bank conflicts) although each lane owns 16 consecutive weights.
+    for (uint32_t i = tid * 4; i < BATCH * p.n; i += kGemvThreads * 4) {
+        const uint32_t r = i & 511u;
+        const uint32_t dst = (i - r) + ((r & 15u) >> 2) * 128u + (r >> 4) * 4u;
+        *reinterpret_cast<float4*>(s_x + dst) = *reinterpret_cast<const float4*>(p.x + i);
+    }
+    __syncthreads();
+    const uint32_t chunks = p.n / 16;  // 32-byte chunks (16 weights) per row
+    for (uint32_t j = blockIdx.x * kGemvWarps + warp; j < p.d; j += gridDim.x * kGemvWarps) {
+        const uint16_t* row = p.w + static_cast<size_t>(j) * p.n;
+        float acc[BATCH];
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) acc[b] = 0.f;
+        for (uint32_t c0 = lane; c0 < chunks; c0 += 32 * kUnroll) {
+            U8 wv[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const uint32_t c = c0 + u * 32;
+                if (c < chunks) wv[u] = ld_stream32(row + static_cast<size_t>(c) * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const uint32_t c = c0 + u * 32;
+                if (c < chunks) {
+                    const __half2* h = reinterpret_cast<const __half2*>(&wv[u]);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {  // 4 weights per step
+                        const float2 wa = __half22float2(h[2 * q4]), wb = __half22float2(h[2 * q4 + 1]);
+#pragma unroll
+                        for (int b = 0; b < BATCH; ++b) {
+                            // chunk c = span (c / 32), lane (c % 32); see the permutation above
+                            const float4 xv = *reinterpret_cast<const float4*>(s_x + b * p.n + (c >> 5) * 512 + q4 * 128 + (c & 31u) * 4);
+                            acc[b] = fmaf(xv.x, wa.x, acc[b]);
+                            acc[b] = fmaf(xv.y, wa.y, acc[b]);
+                            acc[b] = fmaf(xv.z, wb.x, acc[b]);
+                            acc[b] = fmaf(xv.w, wb.y, acc[b]);
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+#pragma unroll
+            for (int off = 16; off; off >>= 1) acc[b] += __shfl_xor_sync(0xffffffffu, acc[b], off);
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int b = 0; b < BATCH; ++b) {
+                float y = acc[b];
+                if (p.clip > 0.f) y = fminf(fmaxf(y, -p.clip), p.clip);
+                const size_t o = static_cast<size_t>(b) * p.out_batch_stride + j;
+                if (p.out_dtype == ATTN_DTYPE_F32) reinterpret_cast<float*>(p.out)[o] = y;
+                else reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(y);
+            }
+        }
+    }
+}
+
+template <int BATCH>
+int launch_gemv(const GemvParams& p, int sm_count, size_t smem, cudaStream_t stream) {
+    auto kernel = gemv_f16_kernel<BATCH>;
+    B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    const uint32_t row_blocks = (p.d + kGemvWarps - 1) / kGemvWarps;
+    const uint32_t grid = row_blocks < static_cast<uint32_t>(sm_count) ? row_blocks : static_cast<uint32_t>(sm_count);
+    kernel<<<grid, kGemvThreads, smem, stream>>>(p);
+    B200_CUDA_TRY(cudaGetLastError());
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return ATTN_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
+    if (!a || !a->out || !a->x || !a->w || a->n == 0 || a->d == 0 || a->batch == 0) return ATTN_ERR_INVALID_ARG;
+    if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16) return ATTN_ERR_INVALID_ARG;
+    if (a->n % 512 != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(a->x) & 15u) || (reinterpret_cast<uintptr_t>(a->w) & 31u)) return ATTN_ERR_ALIGNMENT;
+    DeviceInfo dev{};
+    int rc = current_device_info(&dev);
+    if (rc != ATTN_OK) return rc;
+    const size_t smem = static_cast<size_t>(a->batch) * a->n * sizeof(float);
+    if (smem > static_cast<size_t>(dev.max_smem_optin)) return ATTN_ERR_UNSUPPORTED;  // activations must fit in shared memory
+    GemvParams p{};
+    p.out = a->out;
+    p.x = a->x;
+    p.w = static_cast<const uint16_t*>(a->w);
+    p.out_batch_stride = a->out_batch_stride ? a->out_batch_stride : a->d;
+    p.n = a->n;
+    p.d = a->d;
+    p.clip = a->clip;
+    p.out_dtype = a->out_dtype;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    switch (a->batch) {
+        case 1: return launch_gemv<1>(p, dev.sm_count, smem, stream);
+        case 2: return launch_gemv<2>(p, dev.sm_count, smem, stream);
+        case 3: return launch_gemv<3>(p, dev.sm_count, smem, stream);
+        case 4: return launch_gemv<4>(p, dev.sm_count, smem, stream);
+        case 5: return launch_gemv<5>(p, dev.sm_count, smem, stream);
+        case 6: return launch_gemv<6>(p, dev.sm_count, smem, stream);
+        case 7: return launch_gemv<7>(p, dev.sm_count, smem, stream);
+        default: return launch_gemv<8>(p, dev.sm_count, smem, stream);
+    }
+}

@@ -87,9 +87,11 @@ class Oracle:
             L.oracle_attn_decode_sharded.restype = C.c_int
             L.oracle_attn_decode_sharded.argtypes = [_f32p, _f32p, _f32p, _f32p, _u16p, _u16p, C.c_uint32,
                                                      C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_size_t]
+            L.oracle_matmul_clip.argtypes = [_f32p, _f32p, _u16p, C.c_uint32, C.c_uint32, C.c_float]
             L.oracle_rope_kv_insert.argtypes = [_f32p, _f32p, _f32p, _u16p, _u16p, C.c_uint32, C.c_uint32, C.c_uint32,
                                                 C.c_uint32, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32]
         else:
+            L.ref_matmul_clip.argtypes = [_f32p, _f32p, _u16p, C.c_uint32, C.c_uint32, C.c_float]
             L.ref_rope_kv_insert.argtypes = [_f32p, _f32p, _f32p, _u16p, _u16p, C.c_uint32, C.c_uint32, C.c_uint32,
                                              C.c_uint32, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32]
             L.ref_f16_to_f32.restype = C.c_float
@@ -164,6 +166,17 @@ class Oracle:
                     row_begin, row_end, row_step)
             if rc != 0:
                 raise RuntimeError(f"oracle attn_prefill_causal failed: {rc}")
+        return out
+
+    # -- weight GEMV --
+    def matmul_clip(self, x, w, clip=0.0) -> np.ndarray:
+        """x [n] fp32, w [d, n] fp16 -> out [d] fp32 (include/kernels_cpu.hpp:69-80, clamp of block.cpp:130-138)."""
+        x = _f32(x)
+        w = _u16(w)
+        d, n = w.shape
+        out = np.zeros(d, dtype=np.float32)
+        fn = self.lib.oracle_matmul_clip if self.kind == "port" else self.lib.ref_matmul_clip
+        fn(_ptr(out, _f32p), _ptr(x, _f32p), _ptr(w, _u16p), n, d, clip)
         return out
 
     # -- rotary embedding + cache insert (the step in front of attention) --

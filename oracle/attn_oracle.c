@@ -416,3 +416,16 @@ void oracle_rope_kv_insert(float* q, float* k, const float* v, uint16_t* k_cache
     }
     for (uint32_t s = 0; s < kv_sink; ++s) oracle_rope_f16(k_cache + (size_t)s * row, n_kv_heads, head_dim, 1, theta, rotary_dim);
 }
+
+/* ------------------------------------------------------------------ weight GEMV */
+
+/* include/kernels_cpu.hpp:69-80 with the clamp of src/model/block.cpp:130-138: w is [d][n] fp16, n fastest. */
+void oracle_matmul_clip(float* out, const float* x, const uint16_t* w, uint32_t n, uint32_t d, float clip) {
+#pragma omp parallel for
+    for (uint32_t j = 0; j < d; ++j) {
+        float sum = 0.0f;
+        for (uint32_t i = 0; i < n; ++i) sum += x[i] * oracle_f16_to_f32(w[(size_t)j * n + i]);
+        if (clip > 0.0f) sum = sum > clip ? clip : (sum < -clip ? -clip : sum);
+        out[j] = sum;
+    }
+}

@@ -143,3 +143,13 @@ void ref_rope_kv_insert(float* q, float* k, const float* v, uint16_t* k_cache, u
 }
 
 }  // extern "C"
+
+// ---- weight GEMV (QKV / output / FFN / classifier projections) ----
+// include/kernels_cpu.hpp:69-80: out[j] = sum_i x[i] * f16(w[j*n + i]), fp32 sequential sum, OpenMP over j;
+// optional symmetric clamp as src/model/block.cpp:130-138.
+extern "C" void ref_matmul_clip(float* out, const float* x, const uint16_t* w, uint32_t n, uint32_t d, float clip) {
+    matmul(out, x, w, n, d);
+    if (clip > 0.f) {
+        for (uint32_t j = 0; j < d; ++j) out[j] = std::min(std::max(out[j], -clip), clip);
+    }
+}
