@@ -158,9 +158,28 @@ typedef struct AttnGemvArgs {
     uint32_t batch;     /* 1 .. 8 */
     float clip;         /* > 0: clamp to [-clip, clip]; 0 = none */
     int32_t out_dtype;  /* ATTN_DTYPE_F32 | ATTN_DTYPE_F16 */
+    int32_t accumulate; /* != 0 (fp32 out only): out += result, the residual connection of src/model/block.cpp:169-172 */
 } AttnGemvArgs;
 
 int attn_gemv_f16(const AttnGemvArgs* args, void* stream);
+
+/* The per-token steps between the GEMVs and attention, for a batch of sequences per launch. They restate on the device
+ * the CPU steps of the engine's forward pass, which its CUDA backend does not have yet (the CUDA block ends after
+ * attention, src/model/block.cu:235-239; the CUDA model has no final norm or classifier, src/model/model.cu:67-87). */
+
+/* x[b][0..dim) = fp32(table[tokens[b]][0..dim)), fp16 table [vocab][dim] (src/model/model.cpp:101-118). A token id
+ * >= vocab is not read: ATTN_STATUS_BAD_SHAPE is ORed into *status (optional) and that row of x is left as it was. */
+int attn_embed_f16(float* x, const void* table, const uint32_t* tokens, uint32_t batch, uint32_t dim, uint32_t vocab,
+                   uint32_t* status, void* stream);
+
+/* out[b][i] = x[b][i] / sqrt(mean_i(x[b][i]^2) + eps) * weight[i]; out may be x (include/kernels_cpu.hpp:43-67). */
+int attn_rmsnorm(float* out, const float* x, const float* weight, uint32_t batch, uint32_t dim, float eps, void* stream);
+
+/* hb[i] = silu(hb[i]) * hb2[i], silu(x) = x / (1 + expf(-x)), over count elements (src/model/block.cpp:206-210). */
+int attn_swiglu(float* hb, const float* hb2, uint64_t count, void* stream);
+
+/* out[b] = first index of the maximum of logits[b][0..vocab) (greedy sampling, tools/infer.cpp:64-74). */
+int attn_argmax(uint32_t* out, const float* logits, uint32_t batch, uint32_t vocab, void* stream);
 
 /* Size of the built-in scratch array used by attn_decode_static_scratch(). */
 #define ATTN_STATIC_SCRATCH_BYTES (8u << 20)

@@ -199,7 +199,7 @@ def rope_kv_insert(q, k, v, k_cache, v_cache, pos, kv_pos, *, theta: float, rota
 
 
 def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.float32, clip: float = 0.0,
-             stream=None) -> torch.Tensor:
+             accumulate: bool = False, stream=None) -> torch.Tensor:
     """out[b] = clamp(W x[b]): x [B, n] fp32, w [d, n] fp16 (n fastest) -> out [B, d] fp32 or fp16 (may be a strided
     view, e.g. a KV-cache row per sequence). Mirrors matmul() of include/kernels_cpu.hpp:69-80 for a batch."""
     _require_cuda(x, w)
@@ -216,8 +216,63 @@ def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.floa
     a.out, a.x, a.w = out.data_ptr(), x.data_ptr(), w.data_ptr()
     a.out_batch_stride = out.stride(0) if B > 1 else d
     a.n, a.d, a.batch, a.clip, a.out_dtype = n, d, B, float(clip), _dtype_code(out)
+    a.accumulate = int(accumulate)  # out += W x (residual connection); fp32 out only
     with torch.cuda.device(x.device):
         _b.check(_b.load().attn_gemv_f16(C.byref(a), _stream_ptr(stream)), "attn_gemv_f16")
+    return out
+
+
+def embed_f16(table: torch.Tensor, tokens: torch.Tensor, *, out=None, status=None, stream=None) -> torch.Tensor:
+    """x[b] = fp32(table[tokens[b]]): fp16 table [vocab, dim], uint32/int32 tokens [B] (src/model/model.cpp:101-118)."""
+    _require_cuda(table, tokens)
+    vocab, dim = table.shape
+    if table.dtype != torch.float16 or tokens.dtype not in (torch.int32, torch.uint32) or not table.is_contiguous():
+        raise ValueError("table must be dense fp16 [vocab, dim] and tokens 32-bit integers")
+    B = tokens.numel()
+    if out is None:
+        out = torch.empty((B, dim), dtype=torch.float32, device=table.device)
+    with torch.cuda.device(table.device):
+        _b.check(_b.load().attn_embed_f16(out.data_ptr(), table.data_ptr(), tokens.data_ptr(), B, dim, vocab,
+                                          status.data_ptr() if status is not None else None, _stream_ptr(stream)),
+                 "attn_embed_f16")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, out=None, stream=None) -> torch.Tensor:
+    """out[b] = x[b] / sqrt(mean(x[b]^2) + eps) * weight, fp32 (include/kernels_cpu.hpp:43-67); out may be x."""
+    _require_cuda(x, weight)
+    B, dim = x.shape
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != dim or not x.is_contiguous():
+        raise ValueError("x must be dense fp32 [B, dim] and weight fp32 [dim]")
+    if out is None:
+        out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        _b.check(_b.load().attn_rmsnorm(out.data_ptr(), x.data_ptr(), weight.data_ptr(), B, dim, float(eps),
+                                        _stream_ptr(stream)), "attn_rmsnorm")
+    return out
+
+
+def swiglu_(hb: torch.Tensor, hb2: torch.Tensor, *, stream=None) -> torch.Tensor:
+    """hb = silu(hb) * hb2 in place (src/model/block.cpp:206-210)."""
+    _require_cuda(hb, hb2)
+    if hb.dtype != torch.float32 or hb2.dtype != torch.float32 or hb.shape != hb2.shape or \
+            not (hb.is_contiguous() and hb2.is_contiguous()):
+        raise ValueError("hb and hb2 must be dense fp32 tensors of one shape")
+    with torch.cuda.device(hb.device):
+        _b.check(_b.load().attn_swiglu(hb.data_ptr(), hb2.data_ptr(), hb.numel(), _stream_ptr(stream)), "attn_swiglu")
+    return hb
+
+
+def argmax(logits: torch.Tensor, *, out=None, stream=None) -> torch.Tensor:
+    """First index of the maximum of each row of fp32 logits [B, vocab] (tools/infer.cpp:64-74) -> int32 [B]."""
+    _require_cuda(logits)
+    B, vocab = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise ValueError("logits must be dense fp32 [B, vocab]")
+    if out is None:
+        out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _b.check(_b.load().attn_argmax(out.data_ptr(), logits.data_ptr(), B, vocab, _stream_ptr(stream)), "attn_argmax")
     return out
 
 

@@ -29,6 +29,10 @@ EXPORTED_SYMBOLS = (
     "attn_prefill_causal",
     "attn_rope_kv_insert",
     "attn_gemv_f16",
+    "attn_embed_f16",
+    "attn_rmsnorm",
+    "attn_swiglu",
+    "attn_argmax",
     "attn_status_string",
     "attn_last_cuda_error",
     "attn_kernel_launch_count",
@@ -140,6 +144,7 @@ class AttnGemvArgs(C.Structure):
         ("batch", C.c_uint32),
         ("clip", C.c_float),
         ("out_dtype", C.c_int32),
+        ("accumulate", C.c_int32),
     ]
 
 
@@ -193,6 +198,15 @@ def load() -> C.CDLL:
     lib.attn_prefill_causal.argtypes = [C.POINTER(AttnPrefillArgs), C.c_void_p]
     lib.attn_gemv_f16.restype = C.c_int
     lib.attn_gemv_f16.argtypes = [C.POINTER(AttnGemvArgs), C.c_void_p]
+    lib.attn_embed_f16.restype = C.c_int
+    lib.attn_embed_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
+                                   C.c_void_p]
+    lib.attn_rmsnorm.restype = C.c_int
+    lib.attn_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p]
+    lib.attn_swiglu.restype = C.c_int
+    lib.attn_swiglu.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]
+    lib.attn_argmax.restype = C.c_int
+    lib.attn_argmax.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
     lib.attn_rope_kv_insert.restype = C.c_int
     lib.attn_rope_kv_insert.argtypes = [C.POINTER(AttnRopeInsertArgs), C.c_void_p]
     lib.attn_merge.restype = C.c_int

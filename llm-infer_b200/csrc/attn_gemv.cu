@@ -1,6 +1,7 @@
 // Weight GEMV for the projections around attention (Q/K/V, output, FFN, classifier): out[b][j] = sum_i x[b][i] *
 // W[j][i] with fp16 weights stored [d][n] (n fastest) and fp32 activations, fp32 accumulation, optional symmetric
-// clamp, fp32 or fp16 result (the fp16 form writes V straight into its KV-cache row).
+// clamp, fp32 or fp16 result (the fp16 form writes V straight into its KV-cache row), optionally added to what the
+// fp32 output already holds (the residual connections of src/model/block.cpp:169-172,219-222).
 //
 // Replaces the engine's warp-per-row kernels fused_gemv_clip / fused_gemv_clip_f2h (src/kernels.cu:117-136,229-239,
 // scalar 2-byte loads) and matches its CPU matmul() (include/kernels_cpu.hpp:69-80) with the clamp of
@@ -29,6 +30,7 @@ struct GemvParams {
     uint32_t n, d;
     float clip;
     int32_t out_dtype;
+    int32_t accumulate;
 };
 
 struct alignas(32) U8 {
@@ -102,7 +104,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_f16_kernel(const __grid_
                 float y = acc[b];
                 if (p.clip > 0.f) y = fminf(fmaxf(y, -p.clip), p.clip);
                 const size_t o = static_cast<size_t>(b) * p.out_batch_stride + j;
-                if (p.out_dtype == ATTN_DTYPE_F32) reinterpret_cast<float*>(p.out)[o] = y;
+                if (p.out_dtype == ATTN_DTYPE_F32) {
+                    float* dst = reinterpret_cast<float*>(p.out) + o;
+                    *dst = p.accumulate ? *dst + y : y;  // residual connection: x += W h (src/model/block.cpp:169-172)
+                }
                 else reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(y);
             }
         }
@@ -130,6 +135,7 @@ extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
     if (!a || !a->out || !a->x || !a->w || a->n == 0 || a->d == 0 || a->batch == 0) return ATTN_ERR_INVALID_ARG;
     if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16) return ATTN_ERR_INVALID_ARG;
     if (a->n % 512 != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
+    if (a->accumulate && a->out_dtype != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a->x) & 15u) || (reinterpret_cast<uintptr_t>(a->w) & 31u)) return ATTN_ERR_ALIGNMENT;
     DeviceInfo dev{};
     int rc = current_device_info(&dev);
@@ -145,6 +151,7 @@ extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
     p.d = a->d;
     p.clip = a->clip;
     p.out_dtype = a->out_dtype;
+    p.accumulate = a->accumulate;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     switch (a->batch) {
         case 1: return launch_gemv<1>(p, dev.sm_count, smem, stream);

@@ -1,0 +1,190 @@
+"""Host-side mirror of the engine's Model / Block forward for a batch of sequences, every step on the device.
+
+The engine's forward is one token of one sequence at a time (``Model::forward``, src/model/model.cpp:60-98;
+``Block::block_cpu_``, src/model/block.cpp:105-223); its CUDA block stops after attention
+(src/model/block.cu:235-239). This class runs the same sequence of steps for ``batch`` independent sequences per
+call, each with its own position and KV cache, through the C ABI kernels only (GEMV, RMSNorm, RoPE + cache insert,
+split-KV attention, SwiGLU, argmax): 13 launches per layer, none of them on the host, no CPU fallback.
+
+Weights are the engine's: fp16 ``[d][n]`` matrices (n fastest, GGUF dims ``[n_in, n_out]``), fp32 norm vectors,
+stacked over the layers here. The KV caches keep the engine's ``[row][kv_head][head_dim]`` fp16 layout, one cache
+per layer and sequence.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import attention as A
+
+KV_SINK = 4  # attention-sink rows of the sliding window (include/model/model.hpp)
+
+
+@dataclass
+class ModelConfig:
+    """The fields of the engine's ModelConfig (include/model/config.hpp) that the forward pass reads."""
+    dim: int
+    hidden_dim: int
+    n_layers: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    vocab_size: int
+    max_seq_len: int
+    norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rotary_dim: int = 0      # 0 = head_dim
+    qkv_clip: float = 0.0    # 0 = no clamp
+
+    def as_dict(self) -> dict:
+        return dict(self.__dict__)
+
+
+WEIGHT_SHAPES = {
+    # name -> shape as a function of the config; all fp16 except the norms
+    "embed": lambda c: (c.vocab_size, c.dim),
+    "wcls": lambda c: (c.vocab_size, c.dim),
+    "rms_final": lambda c: (c.dim,),
+    "rms_att": lambda c: (c.n_layers, c.dim),
+    "rms_ffn": lambda c: (c.n_layers, c.dim),
+    "wq": lambda c: (c.n_layers, c.n_heads * c.head_dim, c.dim),
+    "wk": lambda c: (c.n_layers, c.n_kv_heads * c.head_dim, c.dim),
+    "wv": lambda c: (c.n_layers, c.n_kv_heads * c.head_dim, c.dim),
+    "wo": lambda c: (c.n_layers, c.dim, c.n_heads * c.head_dim),
+    "w1": lambda c: (c.n_layers, c.hidden_dim, c.dim),
+    "w3": lambda c: (c.n_layers, c.hidden_dim, c.dim),
+    "w2": lambda c: (c.n_layers, c.dim, c.hidden_dim),
+}
+NORM_NAMES = ("rms_final", "rms_att", "rms_ffn")
+
+
+def random_weights(cfg: ModelConfig, seed: int, device="cpu") -> dict:
+    """Seeded random-init weights of the architecture (there are no checkpoints here): matrices ~ N(0, 1/n_in) in
+    fp16, norm weights ~ 1 + 0.1 N(0, 1) in fp32, embedding ~ N(0, 1)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    out = {}
+    for name, shape_of in WEIGHT_SHAPES.items():
+        shape = shape_of(cfg)
+        if name in NORM_NAMES:
+            w = 1.0 + 0.1 * torch.randn(shape, generator=g, dtype=torch.float32)
+        elif name == "embed":
+            w = torch.randn(shape, generator=g, dtype=torch.float32).half()
+        else:
+            w = (torch.randn(shape, generator=g, dtype=torch.float32) * (shape[-1] ** -0.5)).half()
+        out[name] = w.to(device)
+    return out
+
+
+class Llama:
+    """Batched token-at-a-time forward and greedy generation on one GPU."""
+
+    def __init__(self, cfg: ModelConfig, weights: dict, batch: int, device=None):
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        if dev.type != "cuda":
+            raise ValueError("the model runs on a CUDA device only (there is no CPU path)")
+        self.cfg, self.batch, self.device = cfg, batch, dev
+        c = cfg
+        self.w = {}
+        for name, shape_of in WEIGHT_SHAPES.items():
+            t = weights[name]
+            want = torch.float32 if name in NORM_NAMES else torch.float16
+            if tuple(t.shape) != shape_of(c) or t.dtype != want:
+                raise ValueError(f"weight {name}: expected {shape_of(c)} {want}, got {tuple(t.shape)} {t.dtype}")
+            self.w[name] = t.to(dev).contiguous()
+        B, f32 = batch, torch.float32
+        q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
+        z = lambda *s, dtype=f32: torch.zeros(*s, dtype=dtype, device=dev)  # noqa: E731
+        self.x, self.xb = z(B, c.dim), z(B, c.dim)
+        self.q, self.k, self.v = z(B, c.n_heads, c.head_dim), z(B, c.n_kv_heads, c.head_dim), z(B, c.n_kv_heads, c.head_dim)
+        self.att = z(B, c.n_heads, c.head_dim)
+        self.hb, self.hb2 = z(B, c.hidden_dim), z(B, c.hidden_dim)
+        self.logits = z(B, c.vocab_size)
+        self.next_token = z(B, dtype=torch.int32)
+        self.pos, self.kv_pos, self.kv_len = (z(B, dtype=torch.int32) for _ in range(3))
+        self.status = z(1, dtype=torch.int32)
+        # one cache per layer and sequence, the engine's layout
+        self.k_cache = z(c.n_layers, B, c.max_seq_len, c.n_kv_heads, c.head_dim, dtype=torch.float16)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.workspace = A.DecodeWorkspace(B, c.n_heads, c.n_kv_heads, c.head_dim, dev)
+        self._q_dim, self._kv_dim = q_dim, kv_dim
+
+    # -- positions: sliding-window arithmetic of src/model/model.cpp:66-68, per sequence --
+    def _set_positions(self, pos) -> int:
+        c = self.cfg
+        pos = [int(p) for p in pos]
+        over = [p >= c.max_seq_len for p in pos]
+        if any(over) and not all(over):
+            raise ValueError("sequences inside and outside the sliding window cannot share a step")
+        kv_sink = KV_SINK if all(over) and over else 0
+        kv_pos = [kv_sink + ((p - kv_sink) % (c.max_seq_len - kv_sink)) for p in pos]
+        kv_len = [c.max_seq_len if p >= c.max_seq_len else p + 1 for p in pos]
+        host = torch.tensor([pos, kv_pos, kv_len], dtype=torch.int32).pin_memory()
+        self.pos.copy_(host[0], non_blocking=True)
+        self.kv_pos.copy_(host[1], non_blocking=True)
+        self.kv_len.copy_(host[2], non_blocking=True)
+        return kv_sink
+
+    def forward(self, tokens: torch.Tensor, pos, want_logits: bool = True):
+        """One token per sequence: tokens int32 [B] on the device, pos a list of B positions (or one int for all).
+        Returns the logits [B, vocab] (a view of the model's buffer) or None in prefill mode."""
+        c, w, B = self.cfg, self.w, self.batch
+        if isinstance(pos, int):
+            pos = [pos] * B
+        kv_sink = self._set_positions(pos)
+        A.embed_f16(w["embed"], tokens, out=self.x, status=self.status)
+        xb_q = self.att.view(B, self._q_dim)
+        for l in range(c.n_layers):
+            A.rmsnorm(self.x, w["rms_att"][l], c.norm_eps, out=self.xb)
+            A.gemv_f16(self.xb, w["wq"][l], out=self.q.view(B, self._q_dim), clip=c.qkv_clip)
+            A.gemv_f16(self.xb, w["wk"][l], out=self.k.view(B, self._kv_dim), clip=c.qkv_clip)
+            A.gemv_f16(self.xb, w["wv"][l], out=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
+            A.rope_kv_insert(self.q, self.k, self.v, self.k_cache[l], self.v_cache[l], self.pos, self.kv_pos,
+                             theta=c.rope_theta, rotary_dim=c.rotary_dim, kv_sink=kv_sink, q_out=self.q)
+            A.attn_decode(self.q, self.k_cache[l], self.v_cache[l], self.kv_len, out=self.att,
+                          workspace=self.workspace)
+            A.gemv_f16(xb_q, w["wo"][l], out=self.x, accumulate=True)           # x += Wo att
+            A.rmsnorm(self.x, w["rms_ffn"][l], c.norm_eps, out=self.xb)
+            A.gemv_f16(self.xb, w["w1"][l], out=self.hb)
+            A.gemv_f16(self.xb, w["w3"][l], out=self.hb2)
+            A.swiglu_(self.hb, self.hb2)
+            A.gemv_f16(self.hb, w["w2"][l], out=self.x, accumulate=True)        # x += W2 (silu(W1 xb) * W3 xb)
+        if not want_logits:
+            return None
+        A.rmsnorm(self.x, w["rms_final"], c.norm_eps, out=self.x)
+        A.gemv_f16(self.x, w["wcls"], out=self.logits)
+        return self.logits
+
+    def generate(self, prompts, n_new: int, want_logits: bool = False):
+        """Greedy generation for a ragged batch: prompts is a list of B token-id lists. Every sequence is fed one
+        token per step from position 0 (its prompt, then its own picks), exactly the engine's loop
+        (tools/infer.cpp:271-300, without the end-of-sequence stop); sequences start late so that all prompts end
+        at the same step and the generation steps run as one dense batch. Returns int32 [B, n_new] on the host
+        (and the logits each pick was made from, [B, n_new, vocab], when asked)."""
+        B = self.batch
+        if len(prompts) != B or any(len(p) == 0 for p in prompts):
+            raise ValueError("one non-empty prompt per sequence of the batch")
+        longest = max(len(p) for p in prompts)
+        if longest + n_new > self.cfg.max_seq_len and any(len(p) != longest for p in prompts):
+            raise ValueError("only prompts of one length may run past max_seq_len (one sink setting per step)")
+        delay = [longest - len(p) for p in prompts]
+        out = torch.zeros((B, n_new), dtype=torch.int32, device=self.device)
+        out_logits = torch.zeros((B, n_new, self.cfg.vocab_size), device=self.device) if want_logits else None
+        feed = torch.zeros(B, dtype=torch.int32, device=self.device)
+        for step in range(longest):
+            # a sequence that has not started yet is fed its first token at position 0 again (row 0 is rewritten)
+            pos = [max(step - d, 0) for d in delay]
+            host = torch.tensor([p[q] for p, q in zip(prompts, pos)], dtype=torch.int32)
+            feed.copy_(host)
+            self.forward(feed, pos, want_logits=(step + 1 == longest))
+        for i in range(n_new):
+            A.argmax(self.logits, out=self.next_token)
+            out[:, i] = self.next_token
+            if want_logits:
+                out_logits[:, i] = self.logits
+            if i + 1 < n_new:
+                self.forward(self.next_token, [len(p) + i for p in prompts])
+        torch.cuda.synchronize(self.device)
+        if int(self.status.item()) != 0 or int(self.workspace.status.item()) != 0:
+            raise RuntimeError("a kernel reported a status bit (token id out of range or a wait that ran out)")
+        return (out.cpu(), out_logits.cpu()) if want_logits else out.cpu()

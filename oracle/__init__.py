@@ -27,6 +27,15 @@ REF_SO = os.path.join(_HERE, "_ref", "libref_attn.so")
 
 _f32p = C.POINTER(C.c_float)
 _u16p = C.POINTER(C.c_uint16)
+
+
+class LlamaModelStruct(C.Structure):
+    """Field-for-field the LlamaModel struct of attn_oracle.c / ref_driver.cpp."""
+    _fields_ = [(n, C.c_uint32) for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "head_dim",
+                                          "vocab_size", "max_seq_len", "rotary_dim")] + \
+               [(n, C.c_float) for n in ("norm_eps", "rope_theta", "qkv_clip")] + \
+               [(n, C.c_void_p) for n in ("embed", "wcls", "rms_final", "rms_att", "rms_ffn", "wq", "wk", "wv", "wo",
+                                          "w1", "w2", "w3")]
 _u32p = C.POINTER(C.c_uint32)
 
 
@@ -90,7 +99,16 @@ class Oracle:
             L.oracle_matmul_clip.argtypes = [_f32p, _f32p, _u16p, C.c_uint32, C.c_uint32, C.c_float]
             L.oracle_rope_kv_insert.argtypes = [_f32p, _f32p, _f32p, _u16p, _u16p, C.c_uint32, C.c_uint32, C.c_uint32,
                                                 C.c_uint32, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32]
+            L.oracle_rmsnorm.argtypes = [_f32p, _f32p, _f32p, C.c_uint32, C.c_float]
+            L.oracle_swiglu.argtypes = [_f32p, _f32p, C.c_size_t]
+            L.oracle_argmax.restype = C.c_uint32
+            L.oracle_argmax.argtypes = [_f32p, C.c_uint32]
+            L.oracle_generate_greedy.restype = C.c_int
+            L.oracle_generate_greedy.argtypes = [C.POINTER(LlamaModelStruct), _u32p, C.c_uint32, C.c_uint32, _u32p,
+                                                 _f32p]
         else:
+            L.ref_generate_greedy.restype = C.c_int
+            L.ref_generate_greedy.argtypes = [C.POINTER(LlamaModelStruct), _u32p, C.c_uint32, C.c_uint32, _u32p, _f32p]
             L.ref_matmul_clip.argtypes = [_f32p, _f32p, _u16p, C.c_uint32, C.c_uint32, C.c_float]
             L.ref_rope_kv_insert.argtypes = [_f32p, _f32p, _f32p, _u16p, _u16p, C.c_uint32, C.c_uint32, C.c_uint32,
                                              C.c_uint32, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32]
@@ -178,6 +196,56 @@ class Oracle:
         fn = self.lib.oracle_matmul_clip if self.kind == "port" else self.lib.ref_matmul_clip
         fn(_ptr(out, _f32p), _ptr(x, _f32p), _ptr(w, _u16p), n, d, clip)
         return out
+
+    # -- the small per-token steps (port only; the reference versions run inside generate_greedy) --
+    def rmsnorm(self, x, weight, eps) -> np.ndarray:
+        assert self.kind == "port"
+        x, weight = _f32(x), _f32(weight)
+        out = np.empty_like(x)
+        self.lib.oracle_rmsnorm(_ptr(out, _f32p), _ptr(x, _f32p), _ptr(weight, _f32p), x.size, eps)
+        return out
+
+    def swiglu(self, hb, hb2) -> np.ndarray:
+        assert self.kind == "port"
+        out, hb2 = _f32(hb).copy(), _f32(hb2)
+        self.lib.oracle_swiglu(_ptr(out, _f32p), _ptr(hb2, _f32p), out.size)
+        return out
+
+    def argmax(self, logits) -> int:
+        assert self.kind == "port"
+        logits = _f32(logits)
+        return int(self.lib.oracle_argmax(_ptr(logits, _f32p), logits.size))
+
+    # -- whole model: greedy generation of one sequence, token at a time --
+    def generate_greedy(self, cfg: dict, weights: dict, prompt, n_new: int, want_logits: bool = True):
+        """cfg: dim, hidden_dim, n_layers, n_heads, n_kv_heads, head_dim, vocab_size, max_seq_len, [rotary_dim],
+        norm_eps, rope_theta, [qkv_clip]. weights: numpy arrays embed/wcls fp16 [vocab, dim], rms_final [dim],
+        rms_att/rms_ffn [L, dim] fp32, wq [L, H*D, dim], wk/wv [L, Hkv*D, dim], wo [L, dim, H*D], w1/w3
+        [L, hidden, dim], w2 [L, dim, hidden] fp16. Returns (tokens [n_new], logits [n_new, vocab] or None):
+        src/model/model.cpp:60-98 + src/model/block.cpp:105-223 + tools/infer.cpp:64-74,271-300."""
+        m = LlamaModelStruct()
+        for name in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "head_dim", "vocab_size", "max_seq_len"):
+            setattr(m, name, int(cfg[name]))
+        m.rotary_dim = int(cfg.get("rotary_dim", 0))
+        m.norm_eps, m.rope_theta, m.qkv_clip = float(cfg["norm_eps"]), float(cfg["rope_theta"]), float(cfg.get("qkv_clip", 0.0))
+        keep = []
+        for name in ("embed", "wcls", "wq", "wk", "wv", "wo", "w1", "w2", "w3"):
+            a = _u16(weights[name])
+            keep.append(a)
+            setattr(m, name, a.ctypes.data)
+        for name in ("rms_final", "rms_att", "rms_ffn"):
+            a = _f32(weights[name])
+            keep.append(a)
+            setattr(m, name, a.ctypes.data)
+        prompt = np.ascontiguousarray(prompt, dtype=np.uint32)
+        tokens = np.zeros(n_new, dtype=np.uint32)
+        logits = np.zeros((n_new, m.vocab_size), dtype=np.float32) if want_logits else None
+        fn = self.lib.oracle_generate_greedy if self.kind == "port" else self.lib.ref_generate_greedy
+        rc = fn(C.byref(m), _ptr(prompt, _u32p), prompt.size, n_new, _ptr(tokens, _u32p),
+                _ptr(logits, _f32p) if want_logits else None)
+        if rc != 0:
+            raise RuntimeError(f"generate_greedy failed: {rc}")
+        return tokens, logits
 
     # -- rotary embedding + cache insert (the step in front of attention) --
     def rope_kv_insert(self, q, k, v, k_cache, v_cache, pos, kv_pos, kv_sink=0, theta=10000.0, rotary_dim=None):

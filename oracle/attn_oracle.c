@@ -429,3 +429,124 @@ void oracle_matmul_clip(float* out, const float* x, const uint16_t* w, uint32_t 
         out[j] = sum;
     }
 }
+
+/* ------------------------------------------------------------------ whole model, greedy generation */
+
+/* Restates Block::block_cpu_ (src/model/block.cpp:105-223: RMSNorm, Q/K/V GEMVs, clamp, RoPE, cache insert, sink
+ * rotation, attention, output GEMV + residual, RMSNorm, SwiGLU FFN + residual), Model::forward_cpu_
+ * (src/model/model.cpp:60-98: embedding, sliding-window positions with 4 sink rows, final RMSNorm, classifier) and the
+ * greedy sampler and generation loop of tools/infer.cpp:64-74,271-300 (without the end-of-sequence stop). */
+typedef struct LlamaModel {
+    uint32_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, head_dim, vocab_size, max_seq_len, rotary_dim;
+    float norm_eps, rope_theta, qkv_clip;
+    const uint16_t* embed;   /* [vocab][dim] fp16 */
+    const uint16_t* wcls;    /* [vocab][dim] fp16 */
+    const float* rms_final;  /* [dim] */
+    const float* rms_att;    /* [layers][dim] */
+    const float* rms_ffn;    /* [layers][dim] */
+    const uint16_t *wq, *wk, *wv, *wo, *w1, *w2, *w3; /* stacked over layers, each [d][n] fp16 */
+} LlamaModel;
+
+/* include/kernels_cpu.hpp:43-67 (out may be x) */
+void oracle_rmsnorm(float* out, const float* x, const float* weight, uint32_t size, float eps) {
+    float rms = 0.0f;
+    for (uint32_t i = 0; i < size; ++i) rms += x[i] * x[i];
+    rms = sqrtf(rms / (float)size + eps);
+    for (uint32_t i = 0; i < size; ++i) out[i] = x[i] / rms * weight[i];
+}
+
+/* include/kernels_cpu.hpp:198 and src/model/block.cpp:206-210 */
+void oracle_swiglu(float* hb, const float* hb2, size_t count) {
+    for (size_t i = 0; i < count; ++i) hb[i] = hb[i] / (1.0f + expf(-hb[i])) * hb2[i];
+}
+
+/* tools/infer.cpp:64-74 */
+uint32_t oracle_argmax(const float* logits, uint32_t vocab) {
+    uint32_t max_i = 0;
+    float max_val = logits[0];
+    for (uint32_t i = 1; i < vocab; ++i) {
+        if (logits[i] > max_val) {
+            max_val = logits[i];
+            max_i = i;
+        }
+    }
+    return max_i;
+}
+
+static int forward_token(const LlamaModel* c, uint16_t* k_cache, uint16_t* v_cache, float* buf, uint32_t token,
+                         uint32_t pos, float* logits) {
+    const uint32_t q_dim = c->n_heads * c->head_dim, kv_dim = c->n_kv_heads * c->head_dim;
+    float* x = buf;
+    float* xb = x + c->dim;
+    float* xb2 = xb + c->dim;
+    float* q = xb2 + c->dim;
+    float* k = q + q_dim;
+    float* v = k + kv_dim;
+    float* att = v + kv_dim;
+    float* hb = att + q_dim;
+    float* hb2 = hb + c->hidden_dim;
+    float* scores = hb2 + c->hidden_dim; /* [n_heads][max_seq_len] */
+    for (uint32_t i = 0; i < c->dim; ++i) x[i] = oracle_f16_to_f32(c->embed[(size_t)token * c->dim + i]);
+    const uint32_t kv_sink = pos >= c->max_seq_len ? 4u : 0u;
+    const uint32_t kv_pos = kv_sink + ((pos - kv_sink) % (c->max_seq_len - kv_sink));
+    const uint32_t kv_len = pos >= c->max_seq_len ? c->max_seq_len : pos + 1;
+    const uint32_t rotary_dim = c->rotary_dim ? c->rotary_dim : c->head_dim;
+    const uint32_t group = c->n_heads / c->n_kv_heads;
+    for (uint32_t l = 0; l < c->n_layers; ++l) {
+        uint16_t* kc = k_cache + (size_t)l * c->max_seq_len * kv_dim;
+        uint16_t* vc = v_cache + (size_t)l * c->max_seq_len * kv_dim;
+        oracle_rmsnorm(xb, x, c->rms_att + (size_t)l * c->dim, c->dim, c->norm_eps);
+        oracle_matmul_clip(q, xb, c->wq + (size_t)l * q_dim * c->dim, c->dim, q_dim, c->qkv_clip);
+        oracle_matmul_clip(k, xb, c->wk + (size_t)l * kv_dim * c->dim, c->dim, kv_dim, c->qkv_clip);
+        oracle_matmul_clip(v, xb, c->wv + (size_t)l * kv_dim * c->dim, c->dim, kv_dim, c->qkv_clip);
+        oracle_rope_kv_insert(q, k, v, kc, vc, c->n_heads, c->n_kv_heads, c->head_dim, rotary_dim, c->rope_theta, pos,
+                              kv_pos, kv_sink);
+#pragma omp parallel for
+        for (uint32_t h = 0; h < c->n_heads; ++h) {
+            oracle_attn_head(att + (size_t)h * c->head_dim, scores + (size_t)h * c->max_seq_len, q + (size_t)h * c->head_dim,
+                             kc, vc, h / group, c->head_dim, (size_t)kv_dim, kv_len);
+        }
+        oracle_matmul_clip(xb, att, c->wo + (size_t)l * c->dim * q_dim, q_dim, c->dim, 0.0f);
+        for (uint32_t i = 0; i < c->dim; ++i) x[i] += xb[i];
+        oracle_rmsnorm(xb, x, c->rms_ffn + (size_t)l * c->dim, c->dim, c->norm_eps);
+        const size_t ffn = (size_t)l * c->hidden_dim * c->dim;
+        oracle_matmul_clip(hb, xb, c->w1 + ffn, c->dim, c->hidden_dim, 0.0f);
+        oracle_matmul_clip(hb2, xb, c->w3 + ffn, c->dim, c->hidden_dim, 0.0f);
+        oracle_swiglu(hb, hb2, c->hidden_dim);
+        oracle_matmul_clip(xb2, hb, c->w2 + ffn, c->hidden_dim, c->dim, 0.0f);
+        for (uint32_t i = 0; i < c->dim; ++i) x[i] += xb2[i] * 1.0f;
+    }
+    if (!logits) return 0;
+    oracle_rmsnorm(x, x, c->rms_final, c->dim, c->norm_eps);
+    oracle_matmul_clip(logits, x, c->wcls, c->dim, c->vocab_size, 0.0f);
+    return 0;
+}
+
+int oracle_generate_greedy(const LlamaModel* m, const uint32_t* prompt, uint32_t n_prompt, uint32_t n_new,
+                           uint32_t* out_tokens, float* out_logits) {
+    if (!m || !prompt || n_prompt == 0 || !out_tokens) return -1;
+    const size_t cache = (size_t)m->n_layers * m->max_seq_len * m->n_kv_heads * m->head_dim;
+    const size_t nbuf = 3 * (size_t)m->dim + 2 * (size_t)m->n_heads * m->head_dim + 2 * (size_t)m->n_kv_heads * m->head_dim +
+                        2 * (size_t)m->hidden_dim + (size_t)m->n_heads * m->max_seq_len;
+    uint16_t* k_cache = (uint16_t*)calloc(cache, sizeof(uint16_t));
+    uint16_t* v_cache = (uint16_t*)calloc(cache, sizeof(uint16_t));
+    float* buf = (float*)malloc(nbuf * sizeof(float));
+    float* logits = (float*)malloc((size_t)m->vocab_size * sizeof(float));
+    int rc = -1;
+    if (k_cache && v_cache && buf && logits) {
+        for (uint32_t pos = 0; pos < n_prompt; ++pos)
+            forward_token(m, k_cache, v_cache, buf, prompt[pos], pos, pos + 1 == n_prompt ? logits : NULL);
+        for (uint32_t i = 0; i < n_new; ++i) {
+            const uint32_t next = oracle_argmax(logits, m->vocab_size);
+            out_tokens[i] = next;
+            if (out_logits) memcpy(out_logits + (size_t)i * m->vocab_size, logits, (size_t)m->vocab_size * sizeof(float));
+            if (i + 1 < n_new) forward_token(m, k_cache, v_cache, buf, next, n_prompt + i, logits);
+        }
+        rc = 0;
+    }
+    free(k_cache);
+    free(v_cache);
+    free(buf);
+    free(logits);
+    return rc;
+}

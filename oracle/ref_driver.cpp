@@ -153,3 +153,92 @@ extern "C" void ref_matmul_clip(float* out, const float* x, const uint16_t* w, u
         for (uint32_t j = 0; j < d; ++j) out[j] = std::min(std::max(out[j], -clip), clip);
     }
 }
+
+// ---- one token through the whole model, and greedy generation ----
+// The engine's classes (Model, Block, InferenceState) need its GGUF loader and device layer; this driver instead
+// calls the same primitives of include/kernels_cpu.hpp in the same order as Block::block_cpu_
+// (src/model/block.cpp:105-223) and Model::forward_cpu_ (src/model/model.cpp:60-98) on plain arrays, with the
+// sliding-window arithmetic of model.cpp:66-68 (KV_SINK = 4, include/model/model.hpp) and the greedy sampler of
+// tools/infer.cpp:64-74. Weights are fp16 [d][n], norms fp32, stacked over the layers.
+struct LlamaModel {
+    uint32_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, head_dim, vocab_size, max_seq_len, rotary_dim;
+    float norm_eps, rope_theta, qkv_clip;
+    const uint16_t* embed;
+    const uint16_t* wcls;
+    const float* rms_final;
+    const float* rms_att;
+    const float* rms_ffn;
+    const uint16_t *wq, *wk, *wv, *wo, *w1, *w2, *w3;
+};
+
+namespace {
+constexpr uint32_t kKvSink = 4;
+
+void forward_token(const LlamaModel& c, uint16_t* k_cache, uint16_t* v_cache, uint32_t token, uint32_t pos,
+                   float* logits) {
+    const uint32_t q_dim = c.n_heads * c.head_dim, kv_dim = c.n_kv_heads * c.head_dim;
+    std::vector<float> x(c.dim), xb(c.dim), xb2(c.dim), q(q_dim), k(kv_dim), v(kv_dim), att(q_dim), hb(c.hidden_dim),
+        hb2(c.hidden_dim), scores(static_cast<size_t>(c.n_heads) * c.max_seq_len);
+    for (uint32_t i = 0; i < c.dim; ++i) x[i] = f16_to_f32(c.embed[static_cast<size_t>(token) * c.dim + i]);
+    const uint32_t kv_sink = pos >= c.max_seq_len ? kKvSink : 0;
+    const uint32_t kv_pos = kv_sink + ((pos - kv_sink) % (c.max_seq_len - kv_sink));
+    const uint32_t kv_len = pos >= c.max_seq_len ? c.max_seq_len : pos + 1;
+    const uint32_t rotary_dim = c.rotary_dim ? c.rotary_dim : c.head_dim;
+    for (uint32_t l = 0; l < c.n_layers; ++l) {
+        uint16_t* kc = k_cache + static_cast<size_t>(l) * c.max_seq_len * kv_dim;
+        uint16_t* vc = v_cache + static_cast<size_t>(l) * c.max_seq_len * kv_dim;
+        rmsnorm(xb.data(), x.data(), c.rms_att + static_cast<size_t>(l) * c.dim, c.dim, c.norm_eps);
+        matmul(q.data(), xb.data(), c.wq + static_cast<size_t>(l) * q_dim * c.dim, c.dim, q_dim);
+        matmul(k.data(), xb.data(), c.wk + static_cast<size_t>(l) * kv_dim * c.dim, c.dim, kv_dim);
+        matmul(v.data(), xb.data(), c.wv + static_cast<size_t>(l) * kv_dim * c.dim, c.dim, kv_dim);
+        if (c.qkv_clip > 0.f) {
+            for (auto& e : q) e = std::min(std::max(e, -c.qkv_clip), c.qkv_clip);
+            for (auto& e : k) e = std::min(std::max(e, -c.qkv_clip), c.qkv_clip);
+            for (auto& e : v) e = std::min(std::max(e, -c.qkv_clip), c.qkv_clip);
+        }
+        ref_rope_kv_insert(q.data(), k.data(), v.data(), kc, vc, c.n_heads, c.n_kv_heads, c.head_dim, rotary_dim,
+                           c.rope_theta, pos, kv_pos, kv_sink);
+        ref_attn_decode_seq(att.data(), scores.data(), c.max_seq_len, q.data(), kc, vc, c.n_heads, c.n_kv_heads,
+                            c.head_dim, kv_len);
+        matmul(xb.data(), att.data(), c.wo + static_cast<size_t>(l) * c.dim * q_dim, q_dim, c.dim);
+        for (uint32_t i = 0; i < c.dim; ++i) x[i] += xb[i];
+        rmsnorm(xb.data(), x.data(), c.rms_ffn + static_cast<size_t>(l) * c.dim, c.dim, c.norm_eps);
+        const size_t ffn = static_cast<size_t>(l) * c.hidden_dim * c.dim;
+        matmul(hb.data(), xb.data(), c.w1 + ffn, c.dim, c.hidden_dim);
+        matmul(hb2.data(), xb.data(), c.w3 + ffn, c.dim, c.hidden_dim);
+        for (uint32_t i = 0; i < c.hidden_dim; ++i) hb[i] = silu(hb[i]) * hb2[i];
+        matmul(xb2.data(), hb.data(), c.w2 + ffn, c.hidden_dim, c.dim);
+        for (uint32_t i = 0; i < c.dim; ++i) x[i] += xb2[i] * 1.F;
+    }
+    if (!logits) return;  // prefill mode: no classifier (model.cpp:74-76)
+    rmsnorm(x.data(), c.rms_final, c.dim, c.norm_eps);
+    matmul(logits, x.data(), c.wcls, c.dim, c.vocab_size);
+}
+}  // namespace
+
+// Greedy generation of one sequence, token at a time (tools/infer.cpp:271-300 without the end-of-sequence stop):
+// out_tokens [n_new]; out_logits optional [n_new][vocab] (the logits each token was picked from). Returns 0.
+extern "C" int ref_generate_greedy(const LlamaModel* m, const uint32_t* prompt, uint32_t n_prompt, uint32_t n_new,
+                                   uint32_t* out_tokens, float* out_logits) {
+    if (!m || !prompt || n_prompt == 0 || !out_tokens) return -1;
+    const size_t cache = static_cast<size_t>(m->n_layers) * m->max_seq_len * m->n_kv_heads * m->head_dim;
+    std::vector<uint16_t> k_cache(cache), v_cache(cache);
+    std::vector<float> logits(m->vocab_size);
+    for (uint32_t pos = 0; pos < n_prompt; ++pos) {
+        forward_token(*m, k_cache.data(), v_cache.data(), prompt[pos], pos, pos + 1 == n_prompt ? logits.data() : nullptr);
+    }
+    for (uint32_t i = 0; i < n_new; ++i) {
+        uint32_t max_i = 0;
+        float max_val = logits[0];
+        for (uint32_t t = 1; t < m->vocab_size; ++t) {
+            if (logits[t] > max_val) {
+                max_val = logits[t];
+                max_i = t;
+            }
+        }
+        out_tokens[i] = max_i;
+        if (out_logits) std::memcpy(out_logits + static_cast<size_t>(i) * m->vocab_size, logits.data(), logits.size() * sizeof(float));
+        if (i + 1 < n_new) forward_token(*m, k_cache.data(), v_cache.data(), max_i, n_prompt + i, logits.data());
+    }
+    return 0;
+}
