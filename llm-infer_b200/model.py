@@ -101,6 +101,8 @@ class Llama:
         self.hb, self.hb2 = z(B, c.hidden_dim), z(B, c.hidden_dim)
         self.logits = z(B, c.vocab_size)
         self.next_token = z(B, dtype=torch.int32)
+        self.tokens = z(B, dtype=torch.int32)   # the step's input tokens; a decode step writes its picks back here
+        self._graphs = None
         self.pos, self.kv_pos, self.kv_len = (z(B, dtype=torch.int32) for _ in range(3))
         self.status = z(1, dtype=torch.int32)
         # one cache per layer and sequence, the engine's layout
@@ -125,15 +127,12 @@ class Llama:
         self.kv_len.copy_(host[2], non_blocking=True)
         return kv_sink
 
-    def forward(self, tokens: torch.Tensor, pos, want_logits: bool = True):
-        """One token per sequence: tokens int32 [B] on the device, pos a list of B positions (or one int for all).
-        Returns the logits [B, vocab] (a view of the model's buffer) or None in prefill mode."""
+    def _launch_step(self, kv_sink: int, want_logits: bool) -> None:
+        """Every launch of one step, reading self.tokens / pos / kv_pos / kv_len. With logits the step ends with the
+        greedy pick (self.next_token) and feeds it back into self.tokens for the next step."""
         c, w, B = self.cfg, self.w, self.batch
-        if isinstance(pos, int):
-            pos = [pos] * B
-        kv_sink = self._set_positions(pos)
-        A.embed_f16(w["embed"], tokens, out=self.x, status=self.status)
-        xb_q = self.att.view(B, self._q_dim)
+        A.embed_f16(w["embed"], self.tokens, out=self.x, status=self.status)
+        att_flat = self.att.view(B, self._q_dim)
         for l in range(c.n_layers):
             A.rmsnorm(self.x, w["rms_att"][l], c.norm_eps, out=self.xb)
             A.gemv_f16(self.xb, w["wq"][l], out=self.q.view(B, self._q_dim), clip=c.qkv_clip)
@@ -143,17 +142,55 @@ class Llama:
                              theta=c.rope_theta, rotary_dim=c.rotary_dim, kv_sink=kv_sink, q_out=self.q)
             A.attn_decode(self.q, self.k_cache[l], self.v_cache[l], self.kv_len, out=self.att,
                           workspace=self.workspace)
-            A.gemv_f16(xb_q, w["wo"][l], out=self.x, accumulate=True)           # x += Wo att
+            A.gemv_f16(att_flat, w["wo"][l], out=self.x, accumulate=True)       # x += Wo att
             A.rmsnorm(self.x, w["rms_ffn"][l], c.norm_eps, out=self.xb)
             A.gemv_f16(self.xb, w["w1"][l], out=self.hb)
             A.gemv_f16(self.xb, w["w3"][l], out=self.hb2)
             A.swiglu_(self.hb, self.hb2)
             A.gemv_f16(self.hb, w["w2"][l], out=self.x, accumulate=True)        # x += W2 (silu(W1 xb) * W3 xb)
         if not want_logits:
-            return None
+            return  # prefill mode: no final norm, no classifier (src/model/model.cpp:74-76)
         A.rmsnorm(self.x, w["rms_final"], c.norm_eps, out=self.x)
         A.gemv_f16(self.x, w["wcls"], out=self.logits)
-        return self.logits
+        A.argmax(self.logits, out=self.next_token)
+        self.tokens.copy_(self.next_token)
+
+    def capture(self) -> None:
+        """Record the step once per mode (prefill: no classifier; decode: classifier + greedy pick + feedback) as CUDA
+        graphs, the way the engine drives its CUDA step (include/model/device.hpp:161-262): a step then costs one
+        graph launch instead of 13 launches per layer. Positions inside the sliding window only (kv_sink = 0)."""
+        if self._graphs is not None:
+            return
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):   # one eager step first: every kernel does its lazy set-up outside the capture
+            self._set_positions([0] * self.batch)
+            self._launch_step(0, True)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graphs = {}
+        for want_logits in (False, True):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._launch_step(0, want_logits)
+            graphs[want_logits] = g
+        self._graphs = graphs
+
+    def forward(self, tokens, pos, want_logits: bool = True):
+        """One token per sequence: tokens int32 [B] on the device (None = keep self.tokens, i.e. the previous picks),
+        pos a list of B positions (or one int for all). Returns the logits [B, vocab] (a view of the model's buffer)
+        or None in prefill mode. Replays the captured graph when capture() was called and no position has left the
+        sliding window."""
+        if isinstance(pos, int):
+            pos = [pos] * self.batch
+        if tokens is not None and tokens is not self.tokens:
+            self.tokens.copy_(tokens, non_blocking=True)
+        kv_sink = self._set_positions(pos)
+        if self._graphs is not None and kv_sink == 0:
+            self._graphs[bool(want_logits)].replay()
+        else:
+            self._launch_step(kv_sink, want_logits)
+        return self.logits if want_logits else None
 
     def generate(self, prompts, n_new: int, want_logits: bool = False):
         """Greedy generation for a ragged batch: prompts is a list of B token-id lists. Every sequence is fed one
@@ -170,20 +207,17 @@ class Llama:
         delay = [longest - len(p) for p in prompts]
         out = torch.zeros((B, n_new), dtype=torch.int32, device=self.device)
         out_logits = torch.zeros((B, n_new, self.cfg.vocab_size), device=self.device) if want_logits else None
-        feed = torch.zeros(B, dtype=torch.int32, device=self.device)
         for step in range(longest):
             # a sequence that has not started yet is fed its first token at position 0 again (row 0 is rewritten)
             pos = [max(step - d, 0) for d in delay]
-            host = torch.tensor([p[q] for p, q in zip(prompts, pos)], dtype=torch.int32)
-            feed.copy_(host)
-            self.forward(feed, pos, want_logits=(step + 1 == longest))
+            host = torch.tensor([p[q] for p, q in zip(prompts, pos)], dtype=torch.int32).pin_memory()
+            self.forward(host, pos, want_logits=(step + 1 == longest))
         for i in range(n_new):
-            A.argmax(self.logits, out=self.next_token)
             out[:, i] = self.next_token
             if want_logits:
                 out_logits[:, i] = self.logits
             if i + 1 < n_new:
-                self.forward(self.next_token, [len(p) + i for p in prompts])
+                self.forward(None, [len(p) + i for p in prompts])
         torch.cuda.synchronize(self.device)
         if int(self.status.item()) != 0 or int(self.workspace.status.item()) != 0:
             raise RuntimeError("a kernel reported a status bit (token id out of range or a wait that ran out)")

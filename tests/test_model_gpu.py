@@ -22,10 +22,12 @@ def _numpy_weights(w):
     return {k: v.numpy() for k, v in w.items()}
 
 
-def _run_case(M, checker, cfg, prompts, n_new, seed):
+def _run_case(M, checker, cfg, prompts, n_new, seed, graph=False):
     import torch
     w = M.random_weights(cfg, seed)
     llama = M.Llama(cfg, w, batch=len(prompts))
+    if graph:
+        llama.capture()
     got_tokens, got_logits = llama.generate(prompts, n_new, want_logits=True)
     wn = _numpy_weights(w)
     safe_all = True
@@ -53,6 +55,15 @@ def test_tiny_model_ragged_batch_token_equality(M, checker):
     rng = np.random.default_rng(11)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (5, 9, 3)]
     _run_case(M, checker, cfg, prompts, n_new=24, seed=1)
+
+
+def test_cuda_graph_replay_gives_the_same_tokens(M, checker):
+    """The step captured once per mode as a CUDA graph and replayed (one launch per step)."""
+    cfg = M.ModelConfig(dim=512, hidden_dim=1024, n_layers=2, n_heads=8, n_kv_heads=2, head_dim=64, vocab_size=1000,
+                        max_seq_len=64, norm_eps=1e-5, rope_theta=10000.0)
+    rng = np.random.default_rng(21)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (4, 11, 7, 1, 2)]
+    _run_case(M, checker, cfg, prompts, n_new=20, seed=5, graph=True)
 
 
 def test_head_dim_128_gqa4_clip_and_partial_rotary(M, checker):
