@@ -151,17 +151,25 @@ int attn_rope_kv_insert(const AttnRopeInsertArgs* args, void* stream);
 typedef struct AttnGemvArgs {
     void* out;          /* [batch][d] fp32 or fp16, sequence b at out + b*out_batch_stride (elements) */
     const float* x;     /* [batch][n] fp32, dense, 16-byte aligned */
-    const void* w;      /* [d][n] fp16, n fastest (GGUF dims [n_in, n_out]), 32-byte aligned */
+    const void* w;      /* [d][n] fp16, n fastest (GGUF dims [n_in, n_out]), 32-byte aligned (attn_gemv_q8_0: blocks) */
     uint64_t out_batch_stride; /* 0 = d */
-    uint32_t n;         /* multiple of 512; batch*n*4 bytes must fit in shared memory */
+    uint32_t n;         /* multiple of 512; when batch*n*4 bytes exceed shared memory the call runs as several launches
+                           over column slices (fp32 out and no clamp only) */
     uint32_t d;
     uint32_t batch;     /* 1 .. 8 */
     float clip;         /* > 0: clamp to [-clip, clip]; 0 = none */
     int32_t out_dtype;  /* ATTN_DTYPE_F32 | ATTN_DTYPE_F16 */
     int32_t accumulate; /* != 0 (fp32 out only): out += result, the residual connection of src/model/block.cpp:169-172 */
+    uint32_t* status;   /* optional device word: ATTN_STATUS_WAIT_TIMEOUT is ORed in if a bounded wait ran out (Q8_0) */
 } AttnGemvArgs;
 
 int attn_gemv_f16(const AttnGemvArgs* args, void* stream);
+
+/* The same GEMV over Q8_0 weights, the public GGML block format: rows of n/32 blocks, a block = little-endian fp16
+ * scale + 32 signed bytes (34 bytes), value = scale * q. `w` points at the blocks of row 0 (16-byte aligned), n is a
+ * multiple of 256, |x| is clamped to 65504. The engine names the type (include/gguf.hpp:28) but neither loads nor
+ * computes it (src/model/config.cpp:11-17,26-34), so there is no reference kernel this one replaces. */
+int attn_gemv_q8_0(const AttnGemvArgs* args, void* stream);
 
 /* The per-token steps between the GEMVs and attention, for a batch of sequences per launch. They restate on the device
  * the CPU steps of the engine's forward pass, which its CUDA backend does not have yet (the CUDA block ends after

@@ -222,6 +222,31 @@ def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.floa
     return out
 
 
+def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.float32, clip: float = 0.0,
+              accumulate: bool = False, status=None, stream=None) -> torch.Tensor:
+    """out[b] = clamp(W x[b]) over Q8_0 weights: x [B, n] fp32, w uint8 [d, n/32*34] (GGML blocks: fp16 scale + 32
+    signed bytes) -> out [B, d] fp32 or fp16. Same conventions as gemv_f16."""
+    _require_cuda(x, w)
+    B, n = x.shape
+    d = w.shape[0]
+    if w.dtype != torch.uint8 or w.shape != (d, n // 32 * 34) or n % 32 or x.dtype != torch.float32:
+        raise ValueError("x must be fp32 [B, n] and w uint8 [d, n/32*34]")
+    x, w = x.contiguous(), w.contiguous()
+    if out is None:
+        out = torch.empty((B, d), dtype=out_dtype, device=x.device)
+    if out.shape != (B, d) or out.stride(1) != 1:
+        raise ValueError("out must be [B, d] with dense rows")
+    a = _b.AttnGemvArgs()
+    a.out, a.x, a.w = out.data_ptr(), x.data_ptr(), w.data_ptr()
+    a.out_batch_stride = out.stride(0) if B > 1 else d
+    a.n, a.d, a.batch, a.clip, a.out_dtype = n, d, B, float(clip), _dtype_code(out)
+    a.accumulate = int(accumulate)
+    a.status = status.data_ptr() if status is not None else None
+    with torch.cuda.device(x.device):
+        _b.check(_b.load().attn_gemv_q8_0(C.byref(a), _stream_ptr(stream)), "attn_gemv_q8_0")
+    return out
+
+
 def embed_f16(table: torch.Tensor, tokens: torch.Tensor, *, out=None, status=None, stream=None) -> torch.Tensor:
     """x[b] = fp32(table[tokens[b]]): fp16 table [vocab, dim], uint32/int32 tokens [B] (src/model/model.cpp:101-118)."""
     _require_cuda(table, tokens)

@@ -29,6 +29,7 @@ EXPORTED_SYMBOLS = (
     "attn_prefill_causal",
     "attn_rope_kv_insert",
     "attn_gemv_f16",
+    "attn_gemv_q8_0",
     "attn_embed_f16",
     "attn_rmsnorm",
     "attn_swiglu",
@@ -145,6 +146,7 @@ class AttnGemvArgs(C.Structure):
         ("clip", C.c_float),
         ("out_dtype", C.c_int32),
         ("accumulate", C.c_int32),
+        ("status", C.c_void_p),
     ]
 
 
@@ -198,6 +200,8 @@ def load() -> C.CDLL:
     lib.attn_prefill_causal.argtypes = [C.POINTER(AttnPrefillArgs), C.c_void_p]
     lib.attn_gemv_f16.restype = C.c_int
     lib.attn_gemv_f16.argtypes = [C.POINTER(AttnGemvArgs), C.c_void_p]
+    lib.attn_gemv_q8_0.restype = C.c_int
+    lib.attn_gemv_q8_0.argtypes = [C.POINTER(AttnGemvArgs), C.c_void_p]
     lib.attn_embed_f16.restype = C.c_int
     lib.attn_embed_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                    C.c_void_p]

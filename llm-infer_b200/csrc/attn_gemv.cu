@@ -27,6 +27,8 @@ struct GemvParams {
     const float* x;
     const uint16_t* w;
     uint64_t out_batch_stride;
+    uint64_t w_row_stride;    // elements between rows of W (>= n: a launch may cover a column slice)
+    uint64_t x_batch_stride;  // elements between sequences of x
     uint32_t n, d;
     float clip;
     int32_t out_dtype;
@@ -50,18 +52,21 @@ template <int BATCH>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_f16_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(16) float s_x[];  // [BATCH][n]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    grid_dep_launch_dependents();  // the next kernel of the stream may be scheduled as SMs free up
+    grid_dep_wait();               // x (and out, when accumulating) come from the previous kernel
     // Activations are staged permuted: inside every span of 512 elements, the four elements (16L + 4q .. +3) that
     // lane L multiplies with the q-th quarter of its 32-byte weight chunk are stored at q*128 + 4L, so that the 32
     // lanes of a warp read 512 consecutive bytes (no bank conflicts) although each lane owns 16 consecutive weights.
     for (uint32_t i = tid * 4; i < BATCH * p.n; i += kGemvThreads * 4) {
-        const uint32_t r = i & 511u;
+        const uint32_t b = i / p.n, col = i - b * p.n;
+        const uint32_t r = col & 511u;
         const uint32_t dst = (i - r) + ((r & 15u) >> 2) * 128u + (r >> 4) * 4u;
-        *reinterpret_cast<float4*>(s_x + dst) = *reinterpret_cast<const float4*>(p.x + i);
+        *reinterpret_cast<float4*>(s_x + dst) = *reinterpret_cast<const float4*>(p.x + b * p.x_batch_stride + col);
     }
     __syncthreads();
     const uint32_t chunks = p.n / 16;  // 32-byte chunks (16 weights) per row
     for (uint32_t j = blockIdx.x * kGemvWarps + warp; j < p.d; j += gridDim.x * kGemvWarps) {
-        const uint16_t* row = p.w + static_cast<size_t>(j) * p.n;
+        const uint16_t* row = p.w + static_cast<size_t>(j) * p.w_row_stride;
         float acc[BATCH];
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) acc[b] = 0.f;
@@ -120,8 +125,7 @@ int launch_gemv(const GemvParams& p, int sm_count, size_t smem, cudaStream_t str
     B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     const uint32_t row_blocks = (p.d + kGemvWarps - 1) / kGemvWarps;
     const uint32_t grid = row_blocks < static_cast<uint32_t>(sm_count) ? row_blocks : static_cast<uint32_t>(sm_count);
-    kernel<<<grid, kGemvThreads, smem, stream>>>(p);
-    B200_CUDA_TRY(cudaGetLastError());
+    B200_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(kGemvThreads), smem, stream, p));
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return ATTN_OK;
 }
@@ -140,27 +144,40 @@ extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
     DeviceInfo dev{};
     int rc = current_device_info(&dev);
     if (rc != ATTN_OK) return rc;
-    const size_t smem = static_cast<size_t>(a->batch) * a->n * sizeof(float);
-    if (smem > static_cast<size_t>(dev.max_smem_optin)) return ATTN_ERR_UNSUPPORTED;  // activations must fit in shared memory
-    GemvParams p{};
-    p.out = a->out;
-    p.x = a->x;
-    p.w = static_cast<const uint16_t*>(a->w);
-    p.out_batch_stride = a->out_batch_stride ? a->out_batch_stride : a->d;
-    p.n = a->n;
-    p.d = a->d;
-    p.clip = a->clip;
-    p.out_dtype = a->out_dtype;
-    p.accumulate = a->accumulate;
+    // The activations of one launch must fit in shared memory. A longer inner dimension (batch 8 x 14336 for the
+    // FFN's down projection) is covered by several launches over column slices of W, each adding to the output: the
+    // sums of the slices are added in a fixed order, so the result does not depend on scheduling.
+    const uint32_t slice_max = static_cast<uint32_t>(static_cast<size_t>(dev.max_smem_optin) / (a->batch * sizeof(float))) & ~511u;
+    if (slice_max == 0) return ATTN_ERR_UNSUPPORTED;
+    const uint32_t slices = (a->n + slice_max - 1) / slice_max;
+    if (slices > 1 && (a->clip > 0.f || a->out_dtype != ATTN_DTYPE_F32)) return ATTN_ERR_UNSUPPORTED;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    switch (a->batch) {
-        case 1: return launch_gemv<1>(p, dev.sm_count, smem, stream);
-        case 2: return launch_gemv<2>(p, dev.sm_count, smem, stream);
-        case 3: return launch_gemv<3>(p, dev.sm_count, smem, stream);
-        case 4: return launch_gemv<4>(p, dev.sm_count, smem, stream);
-        case 5: return launch_gemv<5>(p, dev.sm_count, smem, stream);
-        case 6: return launch_gemv<6>(p, dev.sm_count, smem, stream);
-        case 7: return launch_gemv<7>(p, dev.sm_count, smem, stream);
-        default: return launch_gemv<8>(p, dev.sm_count, smem, stream);
+    for (uint32_t s = 0; s < slices; ++s) {
+        const uint32_t n0 = s * slice_max;
+        GemvParams p{};
+        p.out = a->out;
+        p.x = a->x + n0;
+        p.w = static_cast<const uint16_t*>(a->w) + n0;
+        p.out_batch_stride = a->out_batch_stride ? a->out_batch_stride : a->d;
+        p.w_row_stride = a->n;
+        p.x_batch_stride = a->n;
+        p.n = (a->n - n0 < slice_max) ? a->n - n0 : slice_max;
+        p.d = a->d;
+        p.clip = a->clip;
+        p.out_dtype = a->out_dtype;
+        p.accumulate = (s > 0) ? 1 : a->accumulate;
+        const size_t smem = static_cast<size_t>(a->batch) * p.n * sizeof(float);
+        switch (a->batch) {
+            case 1: rc = launch_gemv<1>(p, dev.sm_count, smem, stream); break;
+            case 2: rc = launch_gemv<2>(p, dev.sm_count, smem, stream); break;
+            case 3: rc = launch_gemv<3>(p, dev.sm_count, smem, stream); break;
+            case 4: rc = launch_gemv<4>(p, dev.sm_count, smem, stream); break;
+            case 5: rc = launch_gemv<5>(p, dev.sm_count, smem, stream); break;
+            case 6: rc = launch_gemv<6>(p, dev.sm_count, smem, stream); break;
+            case 7: rc = launch_gemv<7>(p, dev.sm_count, smem, stream); break;
+            default: rc = launch_gemv<8>(p, dev.sm_count, smem, stream); break;
+        }
+        if (rc != ATTN_OK) return rc;
     }
+    return ATTN_OK;
 }

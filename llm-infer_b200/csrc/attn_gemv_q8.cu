@@ -1,0 +1,361 @@
+// Weight GEMV over Q8_0 weights: out[b][j] = clamp(sum_i x[b][i] * W[j][i]) with W stored in the public GGML Q8_0
+// block format - blocks of 32 consecutive elements of a row, each block a little-endian fp16 scale followed by 32
+// signed bytes (34 bytes), value = scale * q - rows [d][n/32] blocks, n fastest. The engine lists the type
+// (include/gguf.hpp:28) but has no kernel or CPU path for it (its loader accepts F32 / F16 only,
+// src/model/config.cpp:11-17,26-34); this kernel is what the projections of a Q8_0 model need, with the same
+// interface as the fp16 GEMV next to it (clamp of src/model/block.cpp:130-138, residual accumulate).
+//
+// 34 bytes per 32 weights, every byte read once. One persistent CTA per SM, 8 warps. A CTA owns groups of
+// 16 consecutive rows; its warps split the inner dimension in chunks of 8 blocks (256 elements). Each warp runs its
+// own ring of shared-memory stages, each filled by one TMA tile load (16 rows x 272 bytes; one request per stage - 16
+// separate row copies per stage were limited by the copy engine's request rate, 2.5 TB/s), completion counted on an
+// mbarrier; the warp refills a stage as soon as it has consumed it, so up to 139 KB per SM are in flight with no
+// register cost. The arithmetic runs on the tensor cores as m16n8k16 fp16 MMAs: A = the 16 rows' int8
+// values, exactly representable in fp16 (built with one byte-permute and one half2 subtract per pair), B = the
+// activations of up to 8 sequences split into an fp16 value plus an fp16 residual (two MMAs, ~ 22 significant bits;
+// |x| is clamped to the fp16 range, 65504), fp32 accumulation per block, then one fp32 multiply-add by the block's
+// scale per row. The eight warps' partial sums of a row group are added in a fixed order.
+//
+// Algorithmic bytes per call = d * n/32 * 34 + batch * (n*4 + d*sizeof(out)).
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "attn_internal.cuh"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kQ8Warps = 8;
+constexpr int kQ8Threads = kQ8Warps * 32;
+constexpr uint32_t kBlockBytes = 34;                        // fp16 scale + 32 int8
+constexpr uint32_t kChunkBlocks = 8;                        // blocks of one row per stage
+constexpr uint32_t kSegBytes = kChunkBlocks * kBlockBytes;  // 272: one row's share of a stage (multiple of 16)
+constexpr uint32_t kSegPitch = kSegBytes;                   // 68 words = 4 mod 32: the 8 rows x 4 lanes of one load hit 32 banks
+constexpr uint32_t kRows = 16;                              // rows of a group = M of the MMA
+constexpr uint32_t kStageBytes = kRows * kSegPitch;         // 4352 = 34 x 128
+constexpr uint32_t kMaxStages = 4;
+
+struct Q8Params {
+    void* out;
+    const float* x;
+    uint32_t* status;
+    uint64_t out_batch_stride;
+    uint32_t x_elem0;         // first 32-bit element of this launch's column slice inside a row of W
+    uint64_t x_batch_stride;  // elements between sequences of x
+    uint32_t n_blocks;        // blocks of this launch's column slice (multiple of kChunkBlocks)
+    uint32_t d, batch;
+    uint32_t stages;
+    uint32_t x_col_pitch;     // 32-bit words between sequences of the staged activations
+    float clip;
+    int32_t out_dtype;
+    int32_t accumulate;
+};
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The first MMA of a block: accumulates onto zero (constant inputs, no registers to clear).
+__device__ __forceinline__ void mma_f16_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// Two bytes of w (already XORed with 0x80, i.e. q + 128) -> half2 (q_lo, q_hi): 0x6400 | u is the fp16 number
+// 1024 + u, and 1024 + u - 1152 = q exactly.
+template <int FIRST>
+__device__ __forceinline__ uint32_t bytes_to_half2(uint32_t w) {
+    constexpr uint32_t sel = 0x4040u | FIRST | ((FIRST + 1) << 8);
+    const uint32_t biased = __byte_perm(w, 0x64646464u, sel);
+    const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&biased), __half2half2(__ushort_as_half(0x6480)));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds_scale(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return __half2float(__ushort_as_half(v));
+}
+
+// The eight int8 values of block `bi` of one staged row segment that lane quarter t owns, as the lane's A-fragment
+// halves: q[4t .. 4t+4) feed the first k-step (r[0], r[1]), q[16+4t .. 16+4t+4) the second (r[2], r[3]). The four
+// lanes of a row read consecutive words and the rows are 68 words apart, so a load touches every bank once. A block
+// starts at 34*bi, its values at +2: four-byte aligned for odd bi, two bytes off for even bi (two words, one permute).
+template <bool EVEN>
+__device__ __forceinline__ void load_a(uint32_t (&r)[4], uint32_t seg_addr, uint32_t bi, uint32_t t) {
+    const uint32_t base = seg_addr + kBlockBytes * bi + 4 * t;
+    uint32_t v0, v1;
+    if constexpr (EVEN) {
+        v0 = __byte_perm(lds32(base), lds32(base + 4), 0x5432);
+        v1 = __byte_perm(lds32(base + 16), lds32(base + 20), 0x5432);
+    } else {
+        v0 = lds32(base + 2);
+        v1 = lds32(base + 18);
+    }
+    v0 ^= 0x80808080u;
+    v1 ^= 0x80808080u;
+    r[0] = bytes_to_half2<0>(v0);
+    r[1] = bytes_to_half2<2>(v0);
+    r[2] = bytes_to_half2<0>(v1);
+    r[3] = bytes_to_half2<2>(v1);
+}
+
+// Tile load through the TMA engine: 16 rows x 272 bytes of W in one request (rows beyond d read as zeros).
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y,
+                                              uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_constant__ CUtensorMap tm_w,
+                                                                  const __grid_constant__ Q8Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // tile loads want 128-byte alignment
+    // layout: [ring: warps x stages x kStageBytes][red: 2 x warps x 128 floats][bars: warps x kMaxStages][x fragments]
+    const uint32_t ring_bytes = kQ8Warps * p.stages * kStageBytes;
+    float* s_red = reinterpret_cast<float*>(smem + ring_bytes);
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + ring_bytes + 2 * kQ8Warps * 128 * sizeof(float));
+    uint32_t* s_x = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(s_bar) + kQ8Warps * kMaxStages * sizeof(uint64_t));
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3;
+    const uint32_t groups = (p.d + kRows - 1) / kRows;
+    const uint32_t n_chunks = p.n_blocks / kChunkBlocks;
+    const uint32_t cpw = (n_chunks > warp) ? (n_chunks - warp + kQ8Warps - 1) / kQ8Warps : 0;  // chunks per warp and group
+    const uint32_t my_groups = (groups > blockIdx.x) ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t total = my_groups * cpw;
+
+    const uint32_t ring0 = smem_u32(smem) + warp * p.stages * kStageBytes;
+    const uint32_t bar0 = smem_u32(s_bar) + warp * kMaxStages * 8;
+    const uint64_t policy = l2_policy_evict_first();
+
+    if (lane == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) mbar_init(bar0 + 8 * s, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+
+    auto issue = [&](uint32_t item) {
+        const uint32_t rg = blockIdx.x + (item / cpw) * gridDim.x;
+        const uint32_t chunk = warp + (item % cpw) * kQ8Warps;
+        const uint32_t stage = item % p.stages;
+        const uint32_t bar = bar0 + 8 * stage;
+        if (lane == 0) {
+            mbar_arrive_expect_tx(bar, kStageBytes);
+            // x in 32-bit elements (a multiple of 4: 16-byte rule), y = first row of the group
+            tma_load_rows(ring0 + stage * kStageBytes, &tm_w, bar, static_cast<int>(p.x_elem0 + chunk * (kSegBytes / 4)),
+                          static_cast<int>(rg * kRows), policy);
+        }
+    };
+    // The weights do not depend on the activations (no kernel writes them): start streaming them at once, let the next
+    // kernel of the stream be scheduled, and only then wait for the previous kernel, whose output x (and out) are.
+    for (uint32_t i = 0; i < p.stages && i < total; ++i) issue(i);
+    grid_dep_launch_dependents();
+    grid_dep_wait();
+
+    // Activations as B fragments: for sequence c, block blk, k-step s, quarter t: four 32-bit words
+    // {hi(x0,x1), hi(x2,x3), lo(x0,x1), lo(x2,x3)} of the elements x[32 blk + 16 s + 4 t .. +4).
+    for (uint32_t i = tid; i < p.batch * p.n_blocks * 8; i += kQ8Threads) {
+        const uint32_t c = i / (p.n_blocks * 8), r = i - c * (p.n_blocks * 8);
+        const uint32_t blk = r >> 3, s = (r >> 2) & 1, tt = r & 3;
+        float4 v = *reinterpret_cast<const float4*>(p.x + c * p.x_batch_stride + 32 * blk + 16 * s + 4 * tt);
+        v.x = fminf(fmaxf(v.x, -65504.f), 65504.f);
+        v.y = fminf(fmaxf(v.y, -65504.f), 65504.f);
+        v.z = fminf(fmaxf(v.z, -65504.f), 65504.f);
+        v.w = fminf(fmaxf(v.w, -65504.f), 65504.f);
+        const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+        const __half2 l01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y), l23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
+        uint4 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&h01);
+        o.y = *reinterpret_cast<const uint32_t*>(&h23);
+        o.z = *reinterpret_cast<const uint32_t*>(&l01);
+        o.w = *reinterpret_cast<const uint32_t*>(&l23);
+        *reinterpret_cast<uint4*>(s_x + c * p.x_col_pitch + (blk * 2 + s) * 16 + tt * 4) = o;
+    }
+    __syncthreads();
+
+    const bool has_col = g < p.batch;  // lanes of the other columns feed zeros
+    const uint32_t* my_x = s_x + (has_col ? g : 0) * p.x_col_pitch + t * 4;
+    bool timed_out = false;
+    uint32_t item = 0;
+    for (uint32_t gi = 0; gi < my_groups; ++gi) {
+        const uint32_t rg = blockIdx.x + gi * gridDim.x;
+        float tot[4] = {0.f, 0.f, 0.f, 0.f};
+        for (uint32_t ci = 0; ci < cpw; ++ci, ++item) {
+            const uint32_t stage = item % p.stages;
+            if (!mbar_wait(bar0 + 8 * stage, (item / p.stages) & 1)) timed_out = true;
+            const uint32_t chunk = warp + ci * kQ8Warps;
+            const uint32_t seg_lo = ring0 + stage * kStageBytes + g * kSegPitch;
+            const uint32_t seg_hi = seg_lo + 8 * kSegPitch;
+            const uint32_t* xb = my_x + chunk * kChunkBlocks * 32;
+#pragma unroll
+            for (uint32_t bi = 0; bi < kChunkBlocks; ++bi) {
+                uint32_t alo[4], ahi[4];
+                if (bi & 1) {
+                    load_a<false>(alo, seg_lo, bi, t);
+                    load_a<false>(ahi, seg_hi, bi, t);
+                } else {
+                    load_a<true>(alo, seg_lo, bi, t);
+                    load_a<true>(ahi, seg_hi, bi, t);
+                }
+                uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+                if (has_col) {
+                    x0 = *reinterpret_cast<const uint4*>(xb + bi * 32);
+                    x1 = *reinterpret_cast<const uint4*>(xb + bi * 32 + 16);
+                }
+                float acc[4];
+                mma_f16_first(acc, alo[0], ahi[0], alo[1], ahi[1], x0.z, x0.w);  // k-step 0, residual
+                mma_f16(acc, alo[2], ahi[2], alo[3], ahi[3], x1.z, x1.w);        // k-step 1, residual
+                mma_f16(acc, alo[0], ahi[0], alo[1], ahi[1], x0.x, x0.y);        // k-step 0, value
+                mma_f16(acc, alo[2], ahi[2], alo[3], ahi[3], x1.x, x1.y);        // k-step 1, value
+                const float s_lo = lds_scale(seg_lo + kBlockBytes * bi), s_hi = lds_scale(seg_hi + kBlockBytes * bi);
+                tot[0] = fmaf(s_lo, acc[0], tot[0]);
+                tot[1] = fmaf(s_lo, acc[1], tot[1]);
+                tot[2] = fmaf(s_hi, acc[2], tot[2]);
+                tot[3] = fmaf(s_hi, acc[3], tot[3]);
+            }
+            __syncwarp();
+            if (item + p.stages < total) {
+                // order this warp's reads of the stage before the asynchronous writes that refill it
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue(item + p.stages);
+            }
+        }
+        // fixed-order sum of the warps' partial sums
+        float* red = s_red + (gi & 1) * kQ8Warps * 128 + warp * 128;
+        red[g * 8 + 2 * t] = tot[0];
+        red[g * 8 + 2 * t + 1] = tot[1];
+        red[(g + 8) * 8 + 2 * t] = tot[2];
+        red[(g + 8) * 8 + 2 * t + 1] = tot[3];
+        __syncthreads();
+        if (tid < 128) {
+            const uint32_t r = tid >> 3, c = tid & 7;
+            const float* src = s_red + (gi & 1) * kQ8Warps * 128 + tid;
+            float y = 0.f;
+#pragma unroll
+            for (int w = 0; w < kQ8Warps; ++w) y += src[w * 128];
+            const uint32_t row = rg * kRows + r;
+            if (row < p.d && c < p.batch) {
+                if (p.clip > 0.f) y = fminf(fmaxf(y, -p.clip), p.clip);
+                const size_t o = static_cast<size_t>(c) * p.out_batch_stride + row;
+                if (p.out_dtype == ATTN_DTYPE_F32) {
+                    float* dst = reinterpret_cast<float*>(p.out) + o;
+                    *dst = p.accumulate ? *dst + y : y;
+                } else {
+                    reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(y);
+                }
+            }
+        }
+    }
+    if (timed_out && lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up once (a host-side computation; nothing is allocated).
+EncodeTiledFn encode_tiled_fn() {
+    static std::atomic<void*> cached{nullptr};
+    void* fn = cached.load(std::memory_order_acquire);
+    if (!fn) {
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        cached.store(fn, std::memory_order_release);
+    }
+    return reinterpret_cast<EncodeTiledFn>(fn);
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
+    if (!a || !a->out || !a->x || !a->w || a->n == 0 || a->d == 0 || a->batch == 0) return ATTN_ERR_INVALID_ARG;
+    if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16) return ATTN_ERR_INVALID_ARG;
+    if (a->n % (32 * kChunkBlocks) != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
+    if (a->accumulate && a->out_dtype != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(a->x) & 15u) || (reinterpret_cast<uintptr_t>(a->w) & 15u)) return ATTN_ERR_ALIGNMENT;
+    DeviceInfo dev{};
+    int rc = current_device_info(&dev);
+    if (rc != ATTN_OK) return rc;
+    const uint32_t n_blocks = a->n / 32;
+    const size_t fixed = 2 * kQ8Warps * 128 * sizeof(float) + kQ8Warps * kMaxStages * sizeof(uint64_t) + 128;
+    // staged activations: 128 bytes per block and sequence, sequences 64 bytes apart modulo 128 (bank spread)
+    auto x_bytes = [&](uint32_t blocks) { return static_cast<size_t>(a->batch) * (blocks * 128 + 64); };
+    // as many ring stages as fit next to the activations, and column slices when even two do not
+    const size_t budget = static_cast<size_t>(dev.max_smem_optin);
+    if (budget < fixed + 2 * kQ8Warps * kStageBytes + x_bytes(kChunkBlocks)) return ATTN_ERR_UNSUPPORTED;
+    uint32_t slice_blocks = n_blocks;
+    const size_t room = budget - fixed - 2 * kQ8Warps * kStageBytes;
+    if (x_bytes(slice_blocks) > room) {
+        slice_blocks = static_cast<uint32_t>((room / a->batch - 64) / 128) / kChunkBlocks * kChunkBlocks;
+    }
+    const uint32_t slices = (n_blocks + slice_blocks - 1) / slice_blocks;
+    if (slices > 1 && (a->clip > 0.f || a->out_dtype != ATTN_DTYPE_F32)) return ATTN_ERR_UNSUPPORTED;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const uint32_t groups = (a->d + kRows - 1) / kRows;
+    const uint32_t grid = groups < static_cast<uint32_t>(dev.sm_count) ? groups : static_cast<uint32_t>(dev.sm_count);
+    // W as a 2-D tensor of 32-bit elements [d][row_bytes / 4]; one box = 16 rows x 272 bytes, no swizzle.
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return ATTN_ERR_CUDA;
+    CUtensorMap tm_w;
+    {
+        const cuuint64_t row_bytes = static_cast<cuuint64_t>(n_blocks) * kBlockBytes;
+        const cuuint64_t dims[2] = {row_bytes / 4, a->d};
+        const cuuint64_t strides[1] = {row_bytes};
+        const cuuint32_t box[2] = {kSegBytes / 4, kRows};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = enc(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a->w), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            g_last_cuda_error = static_cast<int>(r);
+            return ATTN_ERR_CUDA;
+        }
+    }
+    for (uint32_t s = 0; s < slices; ++s) {
+        const uint32_t b0 = s * slice_blocks;
+        Q8Params p{};
+        p.out = a->out;
+        p.x = a->x + static_cast<size_t>(b0) * 32;
+        p.x_elem0 = b0 * kBlockBytes / 4;  // b0 is a multiple of 8: 272 bytes per 8 blocks
+        p.status = a->status;
+        p.out_batch_stride = a->out_batch_stride ? a->out_batch_stride : a->d;
+        p.x_batch_stride = a->n;
+        p.n_blocks = (n_blocks - b0 < slice_blocks) ? n_blocks - b0 : slice_blocks;
+        p.d = a->d;
+        p.batch = a->batch;
+        p.x_col_pitch = p.n_blocks * 32 + 16;
+        p.clip = a->clip;
+        p.out_dtype = a->out_dtype;
+        p.accumulate = (s > 0) ? 1 : a->accumulate;
+        uint32_t stages = kMaxStages;
+        while (stages > 2 && fixed + stages * kQ8Warps * kStageBytes + x_bytes(p.n_blocks) > budget) --stages;
+        p.stages = stages;
+        const size_t smem = fixed + static_cast<size_t>(stages) * kQ8Warps * kStageBytes + x_bytes(p.n_blocks);
+        B200_CUDA_TRY(cudaFuncSetAttribute(gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        B200_CUDA_TRY(launch_dependent(gemv_q8_0_kernel, dim3(grid), dim3(kQ8Threads), smem, stream, tm_w, p));
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    }
+    return ATTN_OK;
+}

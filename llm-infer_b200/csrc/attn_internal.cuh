@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <utility>
 #include <cstdint>
 
 #include "../../include/llm_infer_attn.h"
@@ -121,6 +122,26 @@ inline int cuda_fail(cudaError_t e) {
         cudaError_t e_ = (expr);                             \
         if (e_ != cudaSuccess) return ::b200::cuda_fail(e_); \
     } while (0)
+
+// Launch with programmatic dependent launch allowed: the grid may be scheduled while the previous grid of the stream
+// is still running (its CTAs start as SMs free up), so launch latency, barrier set-up and prefetches of data that no
+// kernel writes (weights) overlap the previous kernel's tail. Such a kernel must execute griddepcontrol.wait before
+// it reads anything another kernel produces and before it writes global memory.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 struct DeviceInfo {
     int device;

@@ -6,10 +6,12 @@
 //   rmsnorm     include/kernels_cpu.hpp:43-67 (x / sqrt(mean(x^2) + eps) * weight, division before the multiply)
 //   swiglu      src/model/block.cpp:206-210 with silu(x) = x / (1 + expf(-x)), include/kernels_cpu.hpp:198
 //   argmax      tools/infer.cpp:64-74 (first index of the maximum)
-// All of them move a few KB to a few hundred KB per sequence: latency-bound, no roofline is quoted for them.
+// All of them move a few KB to a few hundred KB per sequence: latency-bound, no roofline is quoted for them. They are
+// launched as programmatic dependents (their launch overlaps the previous kernel's tail) and wait for it first thing.
 #include <cuda_fp16.h>
 
 #include "attn_internal.cuh"
+#include "ptx_sm100.cuh"
 
 namespace b200 {
 namespace {
@@ -31,6 +33,8 @@ __device__ __forceinline__ float block_sum(float v, float* s_red) {
 
 __global__ void __launch_bounds__(kOpsThreads) embed_kernel(float* x, const __half* table, const uint32_t* tokens,
                                                             uint32_t dim, uint32_t vocab, uint32_t* status) {
+    grid_dep_launch_dependents();
+    grid_dep_wait();
     const uint32_t b = blockIdx.x;
     const uint32_t tok = tokens[b];
     if (tok >= vocab) {  // never read outside the table; report instead
@@ -44,6 +48,8 @@ __global__ void __launch_bounds__(kOpsThreads) embed_kernel(float* x, const __ha
 __global__ void __launch_bounds__(kOpsThreads) rmsnorm_kernel(float* out, const float* x, const float* weight,
                                                               uint32_t dim, float eps) {
     __shared__ float s_red[kOpsThreads / 32];
+    grid_dep_launch_dependents();
+    grid_dep_wait();
     const size_t base = static_cast<size_t>(blockIdx.x) * dim;
     float ss = 0.f;
     for (uint32_t i = threadIdx.x; i < dim; i += kOpsThreads) {
@@ -56,6 +62,8 @@ __global__ void __launch_bounds__(kOpsThreads) rmsnorm_kernel(float* out, const 
 }
 
 __global__ void __launch_bounds__(kOpsThreads) swiglu_kernel(float* hb, const float* hb2, size_t count) {
+    grid_dep_launch_dependents();
+    grid_dep_wait();
     const size_t i = static_cast<size_t>(blockIdx.x) * kOpsThreads + threadIdx.x;
     if (i < count) {
         const float a = hb[i];
@@ -66,6 +74,8 @@ __global__ void __launch_bounds__(kOpsThreads) swiglu_kernel(float* hb, const fl
 __global__ void __launch_bounds__(1024) argmax_kernel(uint32_t* out, const float* logits, uint32_t vocab) {
     __shared__ float s_val[32];
     __shared__ uint32_t s_idx[32];
+    grid_dep_launch_dependents();
+    grid_dep_wait();
     const float* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
     float best = -INFINITY;
     uint32_t best_i = 0xffffffffu;
@@ -117,9 +127,8 @@ using namespace b200;
 extern "C" int attn_embed_f16(float* x, const void* table, const uint32_t* tokens, uint32_t batch, uint32_t dim,
                               uint32_t vocab, uint32_t* status, void* stream) {
     if (!x || !table || !tokens || batch == 0 || dim == 0 || vocab == 0) return ATTN_ERR_INVALID_ARG;
-    embed_kernel<<<batch, kOpsThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, static_cast<const __half*>(table),
-                                                                               tokens, dim, vocab, status);
-    B200_CUDA_TRY(cudaGetLastError());
+    B200_CUDA_TRY(launch_dependent(embed_kernel, dim3(batch), dim3(kOpsThreads), 0, static_cast<cudaStream_t>(stream), x,
+                                   static_cast<const __half*>(table), tokens, dim, vocab, status));
     count_launch();
     return ATTN_OK;
 }
@@ -127,8 +136,8 @@ extern "C" int attn_embed_f16(float* x, const void* table, const uint32_t* token
 extern "C" int attn_rmsnorm(float* out, const float* x, const float* weight, uint32_t batch, uint32_t dim, float eps,
                             void* stream) {
     if (!out || !x || !weight || batch == 0 || dim == 0) return ATTN_ERR_INVALID_ARG;
-    rmsnorm_kernel<<<batch, kOpsThreads, 0, static_cast<cudaStream_t>(stream)>>>(out, x, weight, dim, eps);
-    B200_CUDA_TRY(cudaGetLastError());
+    B200_CUDA_TRY(launch_dependent(rmsnorm_kernel, dim3(batch), dim3(kOpsThreads), 0, static_cast<cudaStream_t>(stream), out, x,
+                                   weight, dim, eps));
     count_launch();
     return ATTN_OK;
 }
@@ -137,16 +146,15 @@ extern "C" int attn_swiglu(float* hb, const float* hb2, uint64_t count, void* st
     if (!hb || !hb2 || count == 0) return ATTN_ERR_INVALID_ARG;
     const uint64_t blocks = (count + kOpsThreads - 1) / kOpsThreads;
     if (blocks > 0x7fffffffull) return ATTN_ERR_UNSUPPORTED;
-    swiglu_kernel<<<static_cast<uint32_t>(blocks), kOpsThreads, 0, static_cast<cudaStream_t>(stream)>>>(hb, hb2, count);
-    B200_CUDA_TRY(cudaGetLastError());
+    B200_CUDA_TRY(launch_dependent(swiglu_kernel, dim3(static_cast<uint32_t>(blocks)), dim3(kOpsThreads), 0,
+                                   static_cast<cudaStream_t>(stream), hb, hb2, static_cast<size_t>(count)));
     count_launch();
     return ATTN_OK;
 }
 
 extern "C" int attn_argmax(uint32_t* out, const float* logits, uint32_t batch, uint32_t vocab, void* stream) {
     if (!out || !logits || batch == 0 || vocab == 0) return ATTN_ERR_INVALID_ARG;
-    argmax_kernel<<<batch, 1024, 0, static_cast<cudaStream_t>(stream)>>>(out, logits, vocab);
-    B200_CUDA_TRY(cudaGetLastError());
+    B200_CUDA_TRY(launch_dependent(argmax_kernel, dim3(batch), dim3(1024), 0, static_cast<cudaStream_t>(stream), out, logits, vocab));
     count_launch();
     return ATTN_OK;
 }

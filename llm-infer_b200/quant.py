@@ -1,0 +1,37 @@
+"""Q8_0, the public GGML block format: 32 consecutive elements share one fp16 scale d = max|x| / 127, each element is
+stored as the signed byte round(x / d); a block is the little-endian scale followed by the 32 bytes (34 bytes), and the
+value read back is fp32(d) * q. The engine only names the type (include/gguf.hpp:28; docs/gguf.md lists the id), so
+this module is the writer for seed-generated models and the fp32 dequantiser that checks are made against."""
+from __future__ import annotations
+
+import numpy as np
+
+BLOCK = 32
+BLOCK_BYTES = 34
+
+
+def quantize_q8_0(w: np.ndarray) -> np.ndarray:
+    """fp32 / fp16 array [..., n] (n a multiple of 32) -> uint8 array [..., n/32*34]."""
+    w = np.asarray(w, dtype=np.float32)
+    if w.shape[-1] % BLOCK:
+        raise ValueError("the last dimension must be a multiple of 32")
+    blocks = w.reshape(*w.shape[:-1], w.shape[-1] // BLOCK, BLOCK)
+    amax = np.abs(blocks).max(axis=-1, keepdims=True)
+    d = amax / np.float32(127.0)
+    inv = np.where(d > 0, np.float32(1.0) / np.where(d > 0, d, 1), np.float32(0.0)).astype(np.float32)
+    # roundf: half away from zero
+    scaled = blocks * inv
+    q = (np.sign(scaled) * np.floor(np.abs(scaled) + np.float32(0.5))).astype(np.int8)
+    out = np.empty(blocks.shape[:-1] + (BLOCK_BYTES,), dtype=np.uint8)
+    out[..., :2] = d.astype(np.float16).view(np.uint8).reshape(*d.shape[:-1], 2)
+    out[..., 2:] = q.view(np.uint8)
+    return out.reshape(*w.shape[:-1], -1)
+
+
+def dequantize_q8_0(blocks: np.ndarray) -> np.ndarray:
+    """uint8 [..., n/32*34] -> fp32 [..., n] (fp32(d) * q, exact in fp32)."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8)
+    b = b.reshape(*b.shape[:-1], b.shape[-1] // BLOCK_BYTES, BLOCK_BYTES)
+    d = b[..., :2].copy().view(np.float16).astype(np.float32)
+    q = b[..., 2:].view(np.int8).astype(np.float32)
+    return (d * q).reshape(*blocks.shape[:-1], -1)

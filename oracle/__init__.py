@@ -99,6 +99,7 @@ class Oracle:
             L.oracle_matmul_clip.argtypes = [_f32p, _f32p, _u16p, C.c_uint32, C.c_uint32, C.c_float]
             L.oracle_rope_kv_insert.argtypes = [_f32p, _f32p, _f32p, _u16p, _u16p, C.c_uint32, C.c_uint32, C.c_uint32,
                                                 C.c_uint32, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32]
+            L.oracle_matmul_q8_0.argtypes = [_f32p, _f32p, C.POINTER(C.c_uint8), C.c_uint32, C.c_uint32, C.c_float]
             L.oracle_rmsnorm.argtypes = [_f32p, _f32p, _f32p, C.c_uint32, C.c_float]
             L.oracle_swiglu.argtypes = [_f32p, _f32p, C.c_size_t]
             L.oracle_argmax.restype = C.c_uint32
@@ -246,6 +247,17 @@ class Oracle:
         if rc != 0:
             raise RuntimeError(f"generate_greedy failed: {rc}")
         return tokens, logits
+
+    def matmul_q8_0(self, x, w_blocks, clip=0.0) -> np.ndarray:
+        """x [n] fp32, w_blocks uint8 [d, n/32*34] (GGML Q8_0) -> out [d] fp32. Port only: the reference has no Q8_0."""
+        assert self.kind == "port"
+        x = _f32(x)
+        w = np.ascontiguousarray(w_blocks, dtype=np.uint8)
+        d, n = w.shape[0], x.size
+        assert w.shape[1] == n // 32 * 34
+        out = np.zeros(d, dtype=np.float32)
+        self.lib.oracle_matmul_q8_0(_ptr(out, _f32p), _ptr(x, _f32p), _ptr(w, C.POINTER(C.c_uint8)), n, d, clip)
+        return out
 
     # -- rotary embedding + cache insert (the step in front of attention) --
     def rope_kv_insert(self, q, k, v, k_cache, v_cache, pos, kv_pos, kv_sink=0, theta=10000.0, rotary_dim=None):

@@ -430,6 +430,25 @@ void oracle_matmul_clip(float* out, const float* x, const uint16_t* w, uint32_t 
     }
 }
 
+/* The same GEMV over Q8_0 weights (public GGML block format: 34-byte blocks of an fp16 scale d and 32 signed bytes,
+ * value = fp32(d) * q, exact in fp32). The reference has no Q8_0 path (src/model/config.cpp:11-17 rejects the type):
+ * this is its fp16 matmul loop (include/kernels_cpu.hpp:69-80) applied to the dequantised value. */
+void oracle_matmul_q8_0(float* out, const float* x, const uint8_t* w, uint32_t n, uint32_t d, float clip) {
+    const size_t row_bytes = (size_t)(n / 32) * 34;
+#pragma omp parallel for
+    for (uint32_t j = 0; j < d; ++j) {
+        const uint8_t* row = w + (size_t)j * row_bytes;
+        float sum = 0.0f;
+        for (uint32_t i = 0; i < n; ++i) {
+            const uint8_t* blk = row + (size_t)(i / 32) * 34;
+            const float scale = oracle_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+            sum += x[i] * (scale * (float)(int8_t)blk[2 + (i % 32)]);
+        }
+        if (clip > 0.0f) sum = sum > clip ? clip : (sum < -clip ? -clip : sum);
+        out[j] = sum;
+    }
+}
+
 /* ------------------------------------------------------------------ whole model, greedy generation */
 
 /* Restates Block::block_cpu_ (src/model/block.cpp:105-223: RMSNorm, Q/K/V GEMVs, clamp, RoPE, cache insert, sink

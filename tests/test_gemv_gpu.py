@@ -48,6 +48,32 @@ def test_fp16_result_into_a_strided_cache_row(attention, checker):
         assert not got[b, row - 1].any() and not got[b, row + 1].any()  # neighbours untouched
 
 
+def _graph_time_us(call, n_buffers, rounds=10):
+    """Device time per call with the host's launch cost taken out: the calls over all rotated buffers are captured
+    in one CUDA graph and the graph is replayed."""
+    import torch
+    for i in range(n_buffers):
+        call(i)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph):
+            for i in range(n_buffers):
+                call(i)
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(rounds):
+        graph.replay()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) * 1e3 / (rounds * n_buffers)
+
+
 def test_streams_weights_near_hbm_rate(attention):
     """Not a parity test: the FFN-sized projection (14336 x 4096 fp16, 117 MB) must stream at a large fraction of HBM."""
     import torch
@@ -55,14 +81,80 @@ def test_streams_weights_near_hbm_rate(attention):
     ws = [torch.randn(d, n, device="cuda").half() for _ in range(3)]  # 352 MB > L2, rotated
     x = torch.randn(1, n, device="cuda")
     out = torch.empty(1, d, device="cuda")
-    for i in range(3):
-        attention.gemv_f16(x, ws[i % 3], out=out)
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    for i in range(30):
-        attention.gemv_f16(x, ws[i % 3], out=out)
-    e.record()
+    us = _graph_time_us(lambda i: attention.gemv_f16(x, ws[i], out=out), 3)
+    gbs = (d * n * 2 + n * 4 + d * 4) / us / 1e3
+    print(f"gemv 14336x4096 fp16: {us:.1f} us, {gbs:.0f} GB/s")
+    assert gbs > 3000
+
+
+def test_many_sequences_long_inner_dimension_runs_as_column_slices(attention, checker):
+    """batch 8 x n 14336 (the FFN down projection of a batch of 8) does not fit in shared memory at once."""
+    import torch
+    rng = np.random.default_rng(8)
+    n, d, batch = 14336, 512, 8
+    x = rng.standard_normal((batch, n), dtype=np.float32)
+    w = (rng.standard_normal((d, n), dtype=np.float32) * 0.03).astype(np.float16)
+    base = rng.standard_normal((batch, d), dtype=np.float32)
+    out = torch.from_numpy(base.copy()).cuda()
+    attention.gemv_f16(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), out=out, accumulate=True)
+    got = out.cpu().numpy()
+    mag = np.abs(x) @ np.abs(w.astype(np.float32)).T
+    for b in range(batch):
+        want = base[b] + checker.matmul_clip(x[b], w, 0.0)
+        assert (np.abs(got[b] - want) <= 4e-6 * (mag[b] + np.abs(base[b])) + 1e-7).all()
+
+
+# ---- Q8_0 weights ----
+
+@pytest.mark.parametrize("n,d,batch,clip", [(4096, 4096, 1, 0.0), (4096, 1024, 3, 0.0), (14336, 512, 1, 0.0),
+                                            (4096, 777, 8, 0.5), (256, 33, 2, 0.0), (2048, 14336, 2, 0.0),
+                                            (14336, 100, 8, 0.0), (1280, 16, 5, 0.0)])
+def test_q8_0_against_cpu_matmul(attention, port, pkg, n, d, batch, clip):
+    import torch
+    from llm_infer_b200 import quant
+    rng = np.random.default_rng(n + d + batch)
+    x = rng.standard_normal((batch, n), dtype=np.float32)
+    x[0, :7] *= 300.0  # large activations: the fp16 value + residual split must still hold
+    blocks = quant.quantize_q8_0(rng.standard_normal((d, n), dtype=np.float32) * 0.03)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = attention.gemv_q8_0(torch.from_numpy(x).cuda(), torch.from_numpy(blocks).cuda(), clip=clip, status=status)
     torch.cuda.synchronize()
-    gbs = d * n * 2 / (s.elapsed_time(e) / 30 * 1e-3) / 1e9
-    print(f"gemv 14336x4096 fp16: {gbs:.0f} GB/s")
+    assert status.item() == 0
+    got = got.cpu().numpy()
+    wf = quant.dequantize_q8_0(blocks)
+    mag = np.abs(x) @ np.abs(wf).T
+    for b in range(batch):
+        want = port.matmul_q8_0(x[b], blocks, clip)
+        assert (np.abs(got[b] - want) <= 4e-6 * mag[b] + 1e-7).all(), (n, d, b, np.abs(got[b] - want).max())
+
+
+def test_q8_0_roundtrip_and_reference_f16_path(port, checker, pkg):
+    """The writer against the dequantiser (|w - dq| <= d/2 per block, plus the fp16 rounding of d itself) and the Q8_0 sum against the engine's F16 matmul
+    fed the values rounded once to fp16 (2^-11 per weight: 1e-3 of the magnitude)."""
+    from llm_infer_b200 import quant
+    rng = np.random.default_rng(1)
+    w = rng.standard_normal((64, 512), dtype=np.float32)
+    blocks = quant.quantize_q8_0(w)
+    assert blocks.shape == (64, 512 // 32 * 34)
+    dq = quant.dequantize_q8_0(blocks)
+    step = np.abs(w).reshape(64, 16, 32).max(-1, keepdims=True) / 127
+    assert (np.abs(w - dq).reshape(64, 16, 32) <= step * (0.5 + 127 * 2.0 ** -11) * 1.001 + 1e-8).all()
+    x = rng.standard_normal(512, dtype=np.float32)
+    a = port.matmul_q8_0(x, blocks)
+    b = checker.matmul_clip(x, dq.astype(np.float16), 0.0)
+    assert np.abs(a - b).max() <= 1e-3 * (np.abs(x) @ np.abs(dq).T).max()
+
+
+def test_q8_0_streams_weights_near_hbm_rate(attention, pkg):
+    import torch
+    from llm_infer_b200 import quant
+    d, n = 14336, 4096
+    rng = np.random.default_rng(0)
+    base = torch.from_numpy(quant.quantize_q8_0(rng.standard_normal((d, n), dtype=np.float32))).cuda()
+    ws = [base.clone() for _ in range(6)]  # 6 x 62 MB = 374 MB > L2, rotated
+    x = torch.randn(1, n, device="cuda")
+    out = torch.empty(1, d, device="cuda")
+    us = _graph_time_us(lambda i: attention.gemv_q8_0(x, ws[i], out=out), 6)
+    gbs = (d * n // 32 * 34 + n * 4 + d * 4) / us / 1e3
+    print(f"gemv {d}x{n} q8_0: {us:.1f} us, {gbs:.0f} GB/s")
     assert gbs > 3000
