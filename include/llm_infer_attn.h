@@ -180,6 +180,10 @@ int attn_gemv_q8_0(const AttnGemvArgs* args, void* stream);
 int attn_embed_f16(float* x, const void* table, const uint32_t* tokens, uint32_t batch, uint32_t dim, uint32_t vocab,
                    uint32_t* status, void* stream);
 
+/* The same from a Q8_0 table: rows of dim/32 GGML blocks (fp16 scale + 32 signed bytes), value = scale * q. */
+int attn_embed_q8_0(float* x, const void* table, const uint32_t* tokens, uint32_t batch, uint32_t dim, uint32_t vocab,
+                    uint32_t* status, void* stream);
+
 /* out[b][i] = x[b][i] / sqrt(mean_i(x[b][i]^2) + eps) * weight[i]; out may be x (include/kernels_cpu.hpp:43-67). */
 int attn_rmsnorm(float* out, const float* x, const float* weight, uint32_t batch, uint32_t dim, float eps, void* stream);
 

@@ -263,6 +263,24 @@ def embed_f16(table: torch.Tensor, tokens: torch.Tensor, *, out=None, status=Non
     return out
 
 
+def embed_q8_0(table: torch.Tensor, tokens: torch.Tensor, *, out=None, status=None, stream=None) -> torch.Tensor:
+    """x[b] = dequantised row tokens[b] of a Q8_0 table: uint8 [vocab, dim/32*34] -> fp32 [B, dim]."""
+    _require_cuda(table, tokens)
+    vocab = table.shape[0]
+    dim = table.shape[1] // 34 * 32
+    if table.dtype != torch.uint8 or table.shape[1] % 34 or not table.is_contiguous() or \
+            tokens.dtype not in (torch.int32, torch.uint32):
+        raise ValueError("table must be dense uint8 [vocab, dim/32*34] and tokens 32-bit integers")
+    B = tokens.numel()
+    if out is None:
+        out = torch.empty((B, dim), dtype=torch.float32, device=table.device)
+    with torch.cuda.device(table.device):
+        _b.check(_b.load().attn_embed_q8_0(out.data_ptr(), table.data_ptr(), tokens.data_ptr(), B, dim, vocab,
+                                           status.data_ptr() if status is not None else None, _stream_ptr(stream)),
+                 "attn_embed_q8_0")
+    return out
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, out=None, stream=None) -> torch.Tensor:
     """out[b] = x[b] / sqrt(mean(x[b]^2) + eps) * weight, fp32 (include/kernels_cpu.hpp:43-67); out may be x."""
     _require_cuda(x, weight)

@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "attn_gemv_f16",
     "attn_gemv_q8_0",
     "attn_embed_f16",
+    "attn_embed_q8_0",
     "attn_rmsnorm",
     "attn_swiglu",
     "attn_argmax",
@@ -205,6 +206,8 @@ def load() -> C.CDLL:
     lib.attn_embed_f16.restype = C.c_int
     lib.attn_embed_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                    C.c_void_p]
+    lib.attn_embed_q8_0.restype = C.c_int
+    lib.attn_embed_q8_0.argtypes = lib.attn_embed_f16.argtypes
     lib.attn_rmsnorm.restype = C.c_int
     lib.attn_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p]
     lib.attn_swiglu.restype = C.c_int

@@ -45,6 +45,25 @@ __global__ void __launch_bounds__(kOpsThreads) embed_kernel(float* x, const __ha
     for (uint32_t i = threadIdx.x; i < dim; i += kOpsThreads) x[static_cast<size_t>(b) * dim + i] = __half2float(row[i]);
 }
 
+// The same row copy from a Q8_0 table (GGML blocks: fp16 scale + 32 signed bytes per 32 elements).
+__global__ void __launch_bounds__(kOpsThreads) embed_q8_kernel(float* x, const uint8_t* table, const uint32_t* tokens,
+                                                               uint32_t dim, uint32_t vocab, uint32_t* status) {
+    grid_dep_launch_dependents();
+    grid_dep_wait();
+    const uint32_t b = blockIdx.x;
+    const uint32_t tok = tokens[b];
+    if (tok >= vocab) {
+        if (threadIdx.x == 0 && status) atomicOr(status, ATTN_STATUS_BAD_SHAPE);
+        return;
+    }
+    const uint8_t* row = table + static_cast<size_t>(tok) * (dim / 32) * 34;
+    for (uint32_t i = threadIdx.x; i < dim; i += kOpsThreads) {
+        const uint8_t* blk = row + static_cast<size_t>(i / 32) * 34;
+        const float scale = __half2float(__ushort_as_half(static_cast<unsigned short>(blk[0] | (blk[1] << 8))));
+        x[static_cast<size_t>(b) * dim + i] = scale * static_cast<float>(static_cast<int8_t>(blk[2 + (i % 32)]));
+    }
+}
+
 __global__ void __launch_bounds__(kOpsThreads) rmsnorm_kernel(float* out, const float* x, const float* weight,
                                                               uint32_t dim, float eps) {
     __shared__ float s_red[kOpsThreads / 32];
@@ -129,6 +148,15 @@ extern "C" int attn_embed_f16(float* x, const void* table, const uint32_t* token
     if (!x || !table || !tokens || batch == 0 || dim == 0 || vocab == 0) return ATTN_ERR_INVALID_ARG;
     B200_CUDA_TRY(launch_dependent(embed_kernel, dim3(batch), dim3(kOpsThreads), 0, static_cast<cudaStream_t>(stream), x,
                                    static_cast<const __half*>(table), tokens, dim, vocab, status));
+    count_launch();
+    return ATTN_OK;
+}
+
+extern "C" int attn_embed_q8_0(float* x, const void* table, const uint32_t* tokens, uint32_t batch, uint32_t dim,
+                               uint32_t vocab, uint32_t* status, void* stream) {
+    if (!x || !table || !tokens || batch == 0 || dim == 0 || vocab == 0 || dim % 32 != 0) return ATTN_ERR_INVALID_ARG;
+    B200_CUDA_TRY(launch_dependent(embed_q8_kernel, dim3(batch), dim3(kOpsThreads), 0, static_cast<cudaStream_t>(stream), x,
+                                   static_cast<const uint8_t*>(table), tokens, dim, vocab, status));
     count_launch();
     return ATTN_OK;
 }

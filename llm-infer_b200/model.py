@@ -59,38 +59,55 @@ WEIGHT_SHAPES = {
 NORM_NAMES = ("rms_final", "rms_att", "rms_ffn")
 
 
-def random_weights(cfg: ModelConfig, seed: int, device="cpu") -> dict:
-    """Seeded random-init weights of the architecture (there are no checkpoints here): matrices ~ N(0, 1/n_in) in
-    fp16, norm weights ~ 1 + 0.1 N(0, 1) in fp32, embedding ~ N(0, 1)."""
-    g = torch.Generator(device="cpu").manual_seed(seed)
+def random_weights(cfg: ModelConfig, seed: int, device="cpu", weight_type: str = "f16") -> dict:
+    """Seeded random-init weights of the architecture (there are no checkpoints here): matrices ~ N(0, 1/n_in),
+    embedding ~ N(0, 1), stored as fp16 or as Q8_0 blocks (uint8 [..., n/32*34]); norm weights ~ 1 + 0.1 N(0, 1) in
+    fp32. Generated on ``device`` one layer at a time, so an 8B-parameter model never exists in fp32."""
+    from . import quant
+    g = torch.Generator(device=device).manual_seed(seed)
     out = {}
     for name, shape_of in WEIGHT_SHAPES.items():
         shape = shape_of(cfg)
         if name in NORM_NAMES:
-            w = 1.0 + 0.1 * torch.randn(shape, generator=g, dtype=torch.float32)
-        elif name == "embed":
-            w = torch.randn(shape, generator=g, dtype=torch.float32).half()
-        else:
-            w = (torch.randn(shape, generator=g, dtype=torch.float32) * (shape[-1] ** -0.5)).half()
-        out[name] = w.to(device)
+            out[name] = 1.0 + 0.1 * torch.randn(shape, generator=g, dtype=torch.float32, device=device)
+            continue
+        std = 1.0 if name == "embed" else shape[-1] ** -0.5
+        parts = []
+        lead = shape[0] if len(shape) == 3 else 1
+        for _ in range(lead):  # one layer's matrix at a time
+            w = torch.randn(shape[-2:], generator=g, dtype=torch.float32, device=device) * std
+            parts.append(quant.quantize_q8_0_torch(w) if weight_type == "q8_0" else w.half())
+        out[name] = torch.stack(parts) if len(shape) == 3 else parts[0]
     return out
 
 
 class Llama:
     """Batched token-at-a-time forward and greedy generation on one GPU."""
 
-    def __init__(self, cfg: ModelConfig, weights: dict, batch: int, device=None):
+    def __init__(self, cfg: ModelConfig, weights: dict, batch: int, device=None, weight_type: str = "f16"):
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         if dev.type != "cuda":
             raise ValueError("the model runs on a CUDA device only (there is no CPU path)")
         self.cfg, self.batch, self.device = cfg, batch, dev
         c = cfg
         self.w = {}
+        if weight_type not in ("f16", "q8_0"):
+            raise ValueError("weight_type must be 'f16' (the engine's) or 'q8_0'")
+        self.weight_type = weight_type
+        q8 = weight_type == "q8_0"
+        self._gemv = A.gemv_q8_0 if q8 else A.gemv_f16
+        self._embed = A.embed_q8_0 if q8 else A.embed_f16
         for name, shape_of in WEIGHT_SHAPES.items():
             t = weights[name]
-            want = torch.float32 if name in NORM_NAMES else torch.float16
-            if tuple(t.shape) != shape_of(c) or t.dtype != want:
-                raise ValueError(f"weight {name}: expected {shape_of(c)} {want}, got {tuple(t.shape)} {t.dtype}")
+            shape = shape_of(c)
+            if name in NORM_NAMES:
+                want = torch.float32
+            elif q8:
+                want, shape = torch.uint8, shape[:-1] + (shape[-1] // 32 * 34,)
+            else:
+                want = torch.float16
+            if tuple(t.shape) != shape or t.dtype != want:
+                raise ValueError(f"weight {name}: expected {shape} {want}, got {tuple(t.shape)} {t.dtype}")
             self.w[name] = t.to(dev).contiguous()
         B, f32 = batch, torch.float32
         q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
@@ -131,27 +148,28 @@ class Llama:
         """Every launch of one step, reading self.tokens / pos / kv_pos / kv_len. With logits the step ends with the
         greedy pick (self.next_token) and feeds it back into self.tokens for the next step."""
         c, w, B = self.cfg, self.w, self.batch
-        A.embed_f16(w["embed"], self.tokens, out=self.x, status=self.status)
+        gemv = self._gemv
+        self._embed(w["embed"], self.tokens, out=self.x, status=self.status)
         att_flat = self.att.view(B, self._q_dim)
         for l in range(c.n_layers):
             A.rmsnorm(self.x, w["rms_att"][l], c.norm_eps, out=self.xb)
-            A.gemv_f16(self.xb, w["wq"][l], out=self.q.view(B, self._q_dim), clip=c.qkv_clip)
-            A.gemv_f16(self.xb, w["wk"][l], out=self.k.view(B, self._kv_dim), clip=c.qkv_clip)
-            A.gemv_f16(self.xb, w["wv"][l], out=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
+            gemv(self.xb, w["wq"][l], out=self.q.view(B, self._q_dim), clip=c.qkv_clip)
+            gemv(self.xb, w["wk"][l], out=self.k.view(B, self._kv_dim), clip=c.qkv_clip)
+            gemv(self.xb, w["wv"][l], out=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
             A.rope_kv_insert(self.q, self.k, self.v, self.k_cache[l], self.v_cache[l], self.pos, self.kv_pos,
                              theta=c.rope_theta, rotary_dim=c.rotary_dim, kv_sink=kv_sink, q_out=self.q)
             A.attn_decode(self.q, self.k_cache[l], self.v_cache[l], self.kv_len, out=self.att,
                           workspace=self.workspace)
-            A.gemv_f16(att_flat, w["wo"][l], out=self.x, accumulate=True)       # x += Wo att
+            gemv(att_flat, w["wo"][l], out=self.x, accumulate=True)       # x += Wo att
             A.rmsnorm(self.x, w["rms_ffn"][l], c.norm_eps, out=self.xb)
-            A.gemv_f16(self.xb, w["w1"][l], out=self.hb)
-            A.gemv_f16(self.xb, w["w3"][l], out=self.hb2)
+            gemv(self.xb, w["w1"][l], out=self.hb)
+            gemv(self.xb, w["w3"][l], out=self.hb2)
             A.swiglu_(self.hb, self.hb2)
-            A.gemv_f16(self.hb, w["w2"][l], out=self.x, accumulate=True)        # x += W2 (silu(W1 xb) * W3 xb)
+            gemv(self.hb, w["w2"][l], out=self.x, accumulate=True)        # x += W2 (silu(W1 xb) * W3 xb)
         if not want_logits:
             return  # prefill mode: no final norm, no classifier (src/model/model.cpp:74-76)
         A.rmsnorm(self.x, w["rms_final"], c.norm_eps, out=self.x)
-        A.gemv_f16(self.x, w["wcls"], out=self.logits)
+        gemv(self.x, w["wcls"], out=self.logits)
         A.argmax(self.logits, out=self.next_token)
         self.tokens.copy_(self.next_token)
 

@@ -35,3 +35,19 @@ def dequantize_q8_0(blocks: np.ndarray) -> np.ndarray:
     d = b[..., :2].copy().view(np.float16).astype(np.float32)
     q = b[..., 2:].view(np.int8).astype(np.float32)
     return (d * q).reshape(*blocks.shape[:-1], -1)
+
+
+def quantize_q8_0_torch(w):
+    """The same writer on torch tensors of any device: [..., n] float -> uint8 [..., n/32*34]."""
+    import torch
+    w = w.float()
+    blocks = w.reshape(*w.shape[:-1], w.shape[-1] // BLOCK, BLOCK)
+    amax = blocks.abs().amax(dim=-1, keepdim=True)
+    d = amax / 127.0
+    inv = torch.where(d > 0, 1.0 / torch.where(d > 0, d, torch.ones_like(d)), torch.zeros_like(d))
+    scaled = blocks * inv
+    q = (torch.sign(scaled) * torch.floor(scaled.abs() + 0.5)).to(torch.int8)
+    out = torch.empty(blocks.shape[:-1] + (BLOCK_BYTES,), dtype=torch.uint8, device=w.device)
+    out[..., :2] = d.half().view(torch.uint8).reshape(*d.shape[:-1], 2)
+    out[..., 2:] = q.view(torch.uint8)
+    return out.reshape(*w.shape[:-1], -1)

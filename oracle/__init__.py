@@ -35,7 +35,7 @@ class LlamaModelStruct(C.Structure):
                                           "vocab_size", "max_seq_len", "rotary_dim")] + \
                [(n, C.c_float) for n in ("norm_eps", "rope_theta", "qkv_clip")] + \
                [(n, C.c_void_p) for n in ("embed", "wcls", "rms_final", "rms_att", "rms_ffn", "wq", "wk", "wv", "wo",
-                                          "w1", "w2", "w3")]
+                                          "w1", "w2", "w3")] + [("weight_type", C.c_uint32)]
 _u32p = C.POINTER(C.c_uint32)
 
 
@@ -230,8 +230,12 @@ class Oracle:
         m.rotary_dim = int(cfg.get("rotary_dim", 0))
         m.norm_eps, m.rope_theta, m.qkv_clip = float(cfg["norm_eps"]), float(cfg["rope_theta"]), float(cfg.get("qkv_clip", 0.0))
         keep = []
+        q8 = cfg.get("weight_type", "f16") == "q8_0"  # matrices are uint8 GGML Q8_0 blocks (port only)
+        if q8 and self.kind != "port":
+            raise ValueError("the reference has no Q8_0 path")
+        m.weight_type = 1 if q8 else 0
         for name in ("embed", "wcls", "wq", "wk", "wv", "wo", "w1", "w2", "w3"):
-            a = _u16(weights[name])
+            a = np.ascontiguousarray(weights[name], dtype=np.uint8) if q8 else _u16(weights[name])
             keep.append(a)
             setattr(m, name, a.ctypes.data)
         for name in ("rms_final", "rms_att", "rms_ffn"):

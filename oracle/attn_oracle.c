@@ -464,6 +464,7 @@ typedef struct LlamaModel {
     const float* rms_att;    /* [layers][dim] */
     const float* rms_ffn;    /* [layers][dim] */
     const uint16_t *wq, *wk, *wv, *wo, *w1, *w2, *w3; /* stacked over layers, each [d][n] fp16 */
+    uint32_t weight_type; /* 0: fp16 matrices (the engine's type); 1: every matrix incl. embed / wcls is Q8_0 blocks */
 } LlamaModel;
 
 /* include/kernels_cpu.hpp:43-67 (out may be x) */
@@ -492,6 +493,16 @@ uint32_t oracle_argmax(const float* logits, uint32_t vocab) {
     return max_i;
 }
 
+/* Row-major matrix l of a stack of [d][n] matrices, either type. */
+static void model_matmul(const LlamaModel* c, float* out, const float* x, const void* w, size_t layer, uint32_t n,
+                         uint32_t d, float clip) {
+    if (c->weight_type == 1) {
+        oracle_matmul_q8_0(out, x, (const uint8_t*)w + layer * (size_t)d * (n / 32) * 34, n, d, clip);
+    } else {
+        oracle_matmul_clip(out, x, (const uint16_t*)w + layer * (size_t)d * n, n, d, clip);
+    }
+}
+
 static int forward_token(const LlamaModel* c, uint16_t* k_cache, uint16_t* v_cache, float* buf, uint32_t token,
                          uint32_t pos, float* logits) {
     const uint32_t q_dim = c->n_heads * c->head_dim, kv_dim = c->n_kv_heads * c->head_dim;
@@ -505,7 +516,15 @@ static int forward_token(const LlamaModel* c, uint16_t* k_cache, uint16_t* v_cac
     float* hb = att + q_dim;
     float* hb2 = hb + c->hidden_dim;
     float* scores = hb2 + c->hidden_dim; /* [n_heads][max_seq_len] */
-    for (uint32_t i = 0; i < c->dim; ++i) x[i] = oracle_f16_to_f32(c->embed[(size_t)token * c->dim + i]);
+    if (c->weight_type == 1) {
+        const uint8_t* row = (const uint8_t*)c->embed + (size_t)token * (c->dim / 32) * 34;
+        for (uint32_t i = 0; i < c->dim; ++i) {
+            const uint8_t* blk = row + (size_t)(i / 32) * 34;
+            x[i] = oracle_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8))) * (float)(int8_t)blk[2 + (i % 32)];
+        }
+    } else {
+        for (uint32_t i = 0; i < c->dim; ++i) x[i] = oracle_f16_to_f32(c->embed[(size_t)token * c->dim + i]);
+    }
     const uint32_t kv_sink = pos >= c->max_seq_len ? 4u : 0u;
     const uint32_t kv_pos = kv_sink + ((pos - kv_sink) % (c->max_seq_len - kv_sink));
     const uint32_t kv_len = pos >= c->max_seq_len ? c->max_seq_len : pos + 1;
@@ -515,9 +534,9 @@ static int forward_token(const LlamaModel* c, uint16_t* k_cache, uint16_t* v_cac
         uint16_t* kc = k_cache + (size_t)l * c->max_seq_len * kv_dim;
         uint16_t* vc = v_cache + (size_t)l * c->max_seq_len * kv_dim;
         oracle_rmsnorm(xb, x, c->rms_att + (size_t)l * c->dim, c->dim, c->norm_eps);
-        oracle_matmul_clip(q, xb, c->wq + (size_t)l * q_dim * c->dim, c->dim, q_dim, c->qkv_clip);
-        oracle_matmul_clip(k, xb, c->wk + (size_t)l * kv_dim * c->dim, c->dim, kv_dim, c->qkv_clip);
-        oracle_matmul_clip(v, xb, c->wv + (size_t)l * kv_dim * c->dim, c->dim, kv_dim, c->qkv_clip);
+        model_matmul(c, q, xb, c->wq, l, c->dim, q_dim, c->qkv_clip);
+        model_matmul(c, k, xb, c->wk, l, c->dim, kv_dim, c->qkv_clip);
+        model_matmul(c, v, xb, c->wv, l, c->dim, kv_dim, c->qkv_clip);
         oracle_rope_kv_insert(q, k, v, kc, vc, c->n_heads, c->n_kv_heads, c->head_dim, rotary_dim, c->rope_theta, pos,
                               kv_pos, kv_sink);
 #pragma omp parallel for
@@ -525,19 +544,18 @@ static int forward_token(const LlamaModel* c, uint16_t* k_cache, uint16_t* v_cac
             oracle_attn_head(att + (size_t)h * c->head_dim, scores + (size_t)h * c->max_seq_len, q + (size_t)h * c->head_dim,
                              kc, vc, h / group, c->head_dim, (size_t)kv_dim, kv_len);
         }
-        oracle_matmul_clip(xb, att, c->wo + (size_t)l * c->dim * q_dim, q_dim, c->dim, 0.0f);
+        model_matmul(c, xb, att, c->wo, l, q_dim, c->dim, 0.0f);
         for (uint32_t i = 0; i < c->dim; ++i) x[i] += xb[i];
         oracle_rmsnorm(xb, x, c->rms_ffn + (size_t)l * c->dim, c->dim, c->norm_eps);
-        const size_t ffn = (size_t)l * c->hidden_dim * c->dim;
-        oracle_matmul_clip(hb, xb, c->w1 + ffn, c->dim, c->hidden_dim, 0.0f);
-        oracle_matmul_clip(hb2, xb, c->w3 + ffn, c->dim, c->hidden_dim, 0.0f);
+        model_matmul(c, hb, xb, c->w1, l, c->dim, c->hidden_dim, 0.0f);
+        model_matmul(c, hb2, xb, c->w3, l, c->dim, c->hidden_dim, 0.0f);
         oracle_swiglu(hb, hb2, c->hidden_dim);
-        oracle_matmul_clip(xb2, hb, c->w2 + ffn, c->hidden_dim, c->dim, 0.0f);
+        model_matmul(c, xb2, hb, c->w2, l, c->hidden_dim, c->dim, 0.0f);
         for (uint32_t i = 0; i < c->dim; ++i) x[i] += xb2[i] * 1.0f;
     }
     if (!logits) return 0;
     oracle_rmsnorm(x, x, c->rms_final, c->dim, c->norm_eps);
-    oracle_matmul_clip(logits, x, c->wcls, c->dim, c->vocab_size, 0.0f);
+    model_matmul(c, logits, x, c->wcls, 0, c->dim, c->vocab_size, 0.0f);
     return 0;
 }
 

@@ -22,17 +22,18 @@ def _numpy_weights(w):
     return {k: v.numpy() for k, v in w.items()}
 
 
-def _run_case(M, checker, cfg, prompts, n_new, seed, graph=False):
+def _run_case(M, checker, cfg, prompts, n_new, seed, graph=False, weight_type="f16"):
     import torch
-    w = M.random_weights(cfg, seed)
-    llama = M.Llama(cfg, w, batch=len(prompts))
+    w = M.random_weights(cfg, seed, weight_type=weight_type)
+    llama = M.Llama(cfg, w, batch=len(prompts), weight_type=weight_type)
     if graph:
         llama.capture()
     got_tokens, got_logits = llama.generate(prompts, n_new, want_logits=True)
     wn = _numpy_weights(w)
     safe_all = True
+    cfg_dict = dict(cfg.as_dict(), weight_type=weight_type)
     for b, prompt in enumerate(prompts):
-        want_tokens, want_logits = checker.generate_greedy(cfg.as_dict(), wn, prompt, n_new)
+        want_tokens, want_logits = checker.generate_greedy(cfg_dict, wn, prompt, n_new)
         g_tok, g_log = got_tokens[b].numpy(), got_logits[b].numpy()
         for i in range(n_new):
             srt = np.sort(want_logits[i])
@@ -64,6 +65,16 @@ def test_cuda_graph_replay_gives_the_same_tokens(M, checker):
     rng = np.random.default_rng(21)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (4, 11, 7, 1, 2)]
     _run_case(M, checker, cfg, prompts, n_new=20, seed=5, graph=True)
+
+
+def test_q8_0_model_token_equality(M, port):
+    """Every matrix (embedding and classifier included) stored as Q8_0 blocks, graph replay, batch of 8: against the
+    restated forward pass reading the same blocks (the engine itself has no Q8_0 path to compare with)."""
+    cfg = M.ModelConfig(dim=512, hidden_dim=1024, n_layers=2, n_heads=8, n_kv_heads=2, head_dim=64, vocab_size=1000,
+                        max_seq_len=48, norm_eps=1e-5, rope_theta=500000.0)
+    rng = np.random.default_rng(31)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (4, 11, 7, 1, 2, 16, 9, 5)]
+    _run_case(M, port, cfg, prompts, n_new=12, seed=6, graph=True, weight_type="q8_0")
 
 
 def test_head_dim_128_gqa4_clip_and_partial_rotary(M, checker):
