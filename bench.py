@@ -213,6 +213,42 @@ def prefill_measure(torch, attention, wl, steps: int, warmup: int, tflops_peak: 
 
 
 # --------------------------------------------------------------------------- our arm, 1 GPU
+def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5):
+    """End-to-end greedy generation with a random-init Llama-3-8B-shaped model stored as Q8_0 (32 layers, 4096,
+    32/8 heads of 128, FFN 14336, vocab 128256, theta 5e5): a ragged batch of 8 prompts with lengths uniform in
+    [128, 2048] (seeded random token ids), 128 new tokens each, token-at-a-time as the engine does, every step one
+    CUDA-graph launch. Weights are generated on the device from a seed (no checkpoint, no file)."""
+    import numpy as np
+    from llm_infer_b200 import model as M
+    rng = np.random.default_rng(seed)
+    lengths = rng.integers(128, 2049, size=batch).tolist()
+    cfg = M.ModelConfig(dim=4096, hidden_dim=14336, n_layers=32, n_heads=32, n_kv_heads=8, head_dim=128,
+                        vocab_size=128256, max_seq_len=max(lengths) + n_new, norm_eps=1e-5, rope_theta=500000.0)
+    w = M.random_weights(cfg, seed, device="cuda", weight_type="q8_0")
+    weight_bytes = sum(t.numel() * t.element_size() for k, t in w.items() if k != "embed")
+    llama = M.Llama(cfg, w, batch, weight_type="q8_0")
+    del w
+    llama.capture()
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lengths]
+    llama.generate([p[:4] for p in prompts], 4)  # warm-up
+    timing = {}
+    tokens = llama.generate(prompts, n_new, timing=timing)
+    gen_ms = timing["generate_ms"] / max(1, timing["generate_steps"])
+    res = {
+        "workload": "Llama-3-8B-shaped random-init model, Q8_0 weights (8.5 GB incl. embedding), batch 8, prompts "
+                    f"{lengths}, {n_new} new tokens each, greedy, token-at-a-time, one CUDA graph launch per step",
+        "generate_tok_per_s": batch * 1e3 / gen_ms, "generate_ms_per_step": gen_ms,
+        "prompt_tok_per_s": sum(lengths) * 1e3 / timing["prompt_ms"],
+        "prompt_ms_per_step": timing["prompt_ms"] / timing["prompt_steps"],
+        "weight_bytes_per_decode_step": weight_bytes,
+        "weight_stream_gbs": weight_bytes / (gen_ms * 1e-3) / 1e9,
+        "distinct_tokens_generated": int(len(set(tokens.flatten().tolist()))),
+    }
+    del llama
+    torch.cuda.empty_cache()
+    return res
+
+
 def time_steps(torch, fn, steps: int):
     """CUDA-event time of `steps` calls of fn(i) on the current stream, in ms."""
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -379,6 +415,11 @@ def run_single(args):
     extra["kv_sweep"] = {"timing": "median of 5 single calls, CUDA events, L2 flushed when KV < 400 MB",
                          "points": sweep}
     del kbig, vbig, flush
+    torch.cuda.empty_cache()
+    try:
+        extra["generate_c5"] = generate_measure(torch)
+    except Exception as e:
+        extra["generate_c5"] = {"error": str(e)[:300]}
 
     # ---- CPU baseline on the host cores of this box (bounded sample)
     try:
@@ -558,6 +599,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prefill-only", action="store_true",
                     help="time only the causal-prefill workload (used for profiler captures)")
+    ap.add_argument("--generate-only", action="store_true",
+                    help="run only the end-to-end greedy generation workload (Q8_0 8B-shaped model) and print it")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the resident-input steps of the 1-GPU workload (used for profiler captures)")
     args = ap.parse_args()
@@ -566,6 +609,11 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, max(world, args.gpus), rank)
+        return
+    if args.generate_only:
+        import torch
+        load_package()
+        print(json.dumps({"generate_c5": generate_measure(torch)}), flush=True)
         return
     if world == 1 and args.gpus == 1:
         run_single(args)

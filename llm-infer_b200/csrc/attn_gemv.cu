@@ -150,10 +150,11 @@ extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
     const uint32_t slice_max = static_cast<uint32_t>(static_cast<size_t>(dev.max_smem_optin) / (a->batch * sizeof(float))) & ~511u;
     if (slice_max == 0) return ATTN_ERR_UNSUPPORTED;
     const uint32_t slices = (a->n + slice_max - 1) / slice_max;
+    const uint32_t slice_len = ((a->n + slices - 1) / slices + 511u) & ~511u;  // equal slices, multiples of 512
     if (slices > 1 && (a->clip > 0.f || a->out_dtype != ATTN_DTYPE_F32)) return ATTN_ERR_UNSUPPORTED;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     for (uint32_t s = 0; s < slices; ++s) {
-        const uint32_t n0 = s * slice_max;
+        const uint32_t n0 = s * slice_len;
         GemvParams p{};
         p.out = a->out;
         p.x = a->x + n0;
@@ -161,7 +162,7 @@ extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
         p.out_batch_stride = a->out_batch_stride ? a->out_batch_stride : a->d;
         p.w_row_stride = a->n;
         p.x_batch_stride = a->n;
-        p.n = (a->n - n0 < slice_max) ? a->n - n0 : slice_max;
+        p.n = (a->n - n0 < slice_len) ? a->n - n0 : slice_len;
         p.d = a->d;
         p.clip = a->clip;
         p.out_dtype = a->out_dtype;

@@ -311,6 +311,8 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
         slice_blocks = static_cast<uint32_t>((room / a->batch - 64) / 128) / kChunkBlocks * kChunkBlocks;
     }
     const uint32_t slices = (n_blocks + slice_blocks - 1) / slice_blocks;
+    // equal slices (a multiple of the chunk) rather than full ones and a remainder
+    slice_blocks = ((n_blocks + slices - 1) / slices + kChunkBlocks - 1) / kChunkBlocks * kChunkBlocks;
     if (slices > 1 && (a->clip > 0.f || a->out_dtype != ATTN_DTYPE_F32)) return ATTN_ERR_UNSUPPORTED;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const uint32_t groups = (a->d + kRows - 1) / kRows;

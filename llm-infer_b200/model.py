@@ -128,6 +128,17 @@ class Llama:
         self.workspace = A.DecodeWorkspace(B, c.n_heads, c.n_kv_heads, c.head_dim, dev)
         self._q_dim, self._kv_dim = q_dim, kv_dim
 
+    @classmethod
+    def from_gguf(cls, path: str, batch: int, device=None) -> "Llama":
+        """Load a GGUF file (llama architecture, matrices all F16 or all Q8_0, F32 norms) as written by gguf.write_gguf
+        or by any writer of the engine's format (tensor names of src/model/model.cpp:25-38, block.cpp:18-69)."""
+        import numpy as np
+
+        from . import gguf
+        cfg, w, weight_type = gguf.read_gguf(path)
+        weights = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in w.items()}
+        return cls(cfg, weights, batch, device, weight_type=weight_type)
+
     # -- positions: sliding-window arithmetic of src/model/model.cpp:66-68, per sequence --
     def _set_positions(self, pos) -> int:
         c = self.cfg
@@ -210,12 +221,13 @@ class Llama:
             self._launch_step(kv_sink, want_logits)
         return self.logits if want_logits else None
 
-    def generate(self, prompts, n_new: int, want_logits: bool = False):
+    def generate(self, prompts, n_new: int, want_logits: bool = False, timing: dict | None = None):
         """Greedy generation for a ragged batch: prompts is a list of B token-id lists. Every sequence is fed one
         token per step from position 0 (its prompt, then its own picks), exactly the engine's loop
         (tools/infer.cpp:271-300, without the end-of-sequence stop); sequences start late so that all prompts end
         at the same step and the generation steps run as one dense batch. Returns int32 [B, n_new] on the host
-        (and the logits each pick was made from, [B, n_new, vocab], when asked)."""
+        (and the logits each pick was made from, [B, n_new, vocab], when asked). ``timing`` (a dict) receives the
+        device time of the prompt phase and of the generation phase in ms (CUDA events)."""
         B = self.batch
         if len(prompts) != B or any(len(p) == 0 for p in prompts):
             raise ValueError("one non-empty prompt per sequence of the batch")
@@ -225,18 +237,25 @@ class Llama:
         delay = [longest - len(p) for p in prompts]
         out = torch.zeros((B, n_new), dtype=torch.int32, device=self.device)
         out_logits = torch.zeros((B, n_new, self.cfg.vocab_size), device=self.device) if want_logits else None
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record()
         for step in range(longest):
             # a sequence that has not started yet is fed its first token at position 0 again (row 0 is rewritten)
             pos = [max(step - d, 0) for d in delay]
             host = torch.tensor([p[q] for p, q in zip(prompts, pos)], dtype=torch.int32).pin_memory()
             self.forward(host, pos, want_logits=(step + 1 == longest))
+        ev[1].record()
         for i in range(n_new):
             out[:, i] = self.next_token
             if want_logits:
                 out_logits[:, i] = self.logits
             if i + 1 < n_new:
                 self.forward(None, [len(p) + i for p in prompts])
+        ev[2].record()
         torch.cuda.synchronize(self.device)
+        if timing is not None:
+            timing.update(prompt_ms=ev[0].elapsed_time(ev[1]), generate_ms=ev[1].elapsed_time(ev[2]),
+                          prompt_steps=longest, generate_steps=n_new - 1)
         if int(self.status.item()) != 0 or int(self.workspace.status.item()) != 0:
             raise RuntimeError("a kernel reported a status bit (token id out of range or a wait that ran out)")
         return (out.cpu(), out_logits.cpu()) if want_logits else out.cpu()

@@ -77,6 +77,21 @@ def test_q8_0_model_token_equality(M, port):
     _run_case(M, port, cfg, prompts, n_new=12, seed=6, graph=True, weight_type="q8_0")
 
 
+@pytest.mark.parametrize("weight_type", ["f16", "q8_0"])
+def test_model_file_round_trip_generates_the_same_tokens(M, tmp_path, weight_type):
+    """Seed-generated weights written as a GGUF file, loaded back, same greedy output as the in-memory model."""
+    from llm_infer_b200 import gguf
+    cfg = M.ModelConfig(dim=512, hidden_dim=1024, n_layers=2, n_heads=8, n_kv_heads=2, head_dim=64, vocab_size=600,
+                        max_seq_len=40, norm_eps=1e-5, rope_theta=500000.0)
+    w = M.random_weights(cfg, 9, weight_type=weight_type)
+    path = str(tmp_path / "model.gguf")
+    gguf.write_gguf(path, cfg, w, weight_type)
+    prompts = [[5, 17, 3], [9], [100, 200, 300, 400, 500]]
+    a = M.Llama(cfg, w, batch=3, weight_type=weight_type).generate(prompts, 10)
+    b = M.Llama.from_gguf(path, batch=3).generate(prompts, 10)
+    assert np.array_equal(a.numpy(), b.numpy()) and len(set(a.flatten().tolist())) > 3
+
+
 def test_head_dim_128_gqa4_clip_and_partial_rotary(M, checker):
     cfg = M.ModelConfig(dim=1024, hidden_dim=1536, n_layers=3, n_heads=8, n_kv_heads=2, head_dim=128,
                         vocab_size=777, max_seq_len=96, norm_eps=1e-5, rope_theta=500000.0, rotary_dim=64,
