@@ -213,7 +213,7 @@ def prefill_measure(torch, attention, wl, steps: int, warmup: int, tflops_peak: 
 
 
 # --------------------------------------------------------------------------- our arm, 1 GPU
-def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5):
+def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, prompt_range=(128, 2048)):
     """End-to-end greedy generation with a random-init Llama-3-8B-shaped model stored as Q8_0 (32 layers, 4096,
     32/8 heads of 128, FFN 14336, vocab 128256, theta 5e5): a ragged batch of 8 prompts with lengths uniform in
     [128, 2048] (seeded random token ids), 128 new tokens each, token-at-a-time as the engine does, every step one
@@ -221,7 +221,7 @@ def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5):
     import numpy as np
     from llm_infer_b200 import model as M
     rng = np.random.default_rng(seed)
-    lengths = rng.integers(128, 2049, size=batch).tolist()
+    lengths = rng.integers(prompt_range[0], prompt_range[1] + 1, size=batch).tolist()
     cfg = M.ModelConfig(dim=4096, hidden_dim=14336, n_layers=32, n_heads=32, n_kv_heads=8, head_dim=128,
                         vocab_size=128256, max_seq_len=max(lengths) + n_new, norm_eps=1e-5, rope_theta=500000.0)
     w = M.random_weights(cfg, seed, device="cuda", weight_type="q8_0")
@@ -601,6 +601,8 @@ def main():
                     help="time only the causal-prefill workload (used for profiler captures)")
     ap.add_argument("--generate-only", action="store_true",
                     help="run only the end-to-end greedy generation workload (Q8_0 8B-shaped model) and print it")
+    ap.add_argument("--generate-short", action="store_true",
+                    help="with --generate-only: prompts of 8-16 tokens and 8 new tokens (for profiler launch lists)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the resident-input steps of the 1-GPU workload (used for profiler captures)")
     args = ap.parse_args()
@@ -613,7 +615,8 @@ def main():
     if args.generate_only:
         import torch
         load_package()
-        print(json.dumps({"generate_c5": generate_measure(torch)}), flush=True)
+        kw = {"n_new": 8, "prompt_range": (8, 16)} if args.generate_short else {}
+        print(json.dumps({"generate_c5": generate_measure(torch, **kw)}), flush=True)
         return
     if world == 1 and args.gpus == 1:
         run_single(args)

@@ -153,14 +153,24 @@ typedef struct AttnGemvArgs {
     const float* x;     /* [batch][n] fp32, dense, 16-byte aligned */
     const void* w;      /* [d][n] fp16, n fastest (GGUF dims [n_in, n_out]), 32-byte aligned (attn_gemv_q8_0: blocks) */
     uint64_t out_batch_stride; /* 0 = d */
-    uint32_t n;         /* multiple of 512; when batch*n*4 bytes exceed shared memory the call runs as several launches
-                           over column slices (fp32 out and no clamp only) */
+    uint32_t n;         /* f16: multiple of 512; when batch*n*4 bytes exceed shared memory the call runs as several launches
+                           over column slices (fp32 out and no clamp only). q8_0: multiple of 256 (slices are internal) */
     uint32_t d;
     uint32_t batch;     /* 1 .. 8 */
     float clip;         /* > 0: clamp to [-clip, clip]; 0 = none */
     int32_t out_dtype;  /* ATTN_DTYPE_F32 | ATTN_DTYPE_F16 */
     int32_t accumulate; /* != 0 (fp32 out only): out += result, the residual connection of src/model/block.cpp:169-172 */
     uint32_t* status;   /* optional device word: ATTN_STATUS_WAIT_TIMEOUT is ORed in if a bounded wait ran out (Q8_0) */
+    /* Optional row segments (0 / NULL = unused): rows [0, split1) go to out, [split1, split2) to out2, [split2, d) to
+     * out3, each [batch][segment rows] with its own batch stride (0 = dense). One launch then serves the Q, K and V
+     * projections over a stacked [q rows; k rows; v rows] matrix (src/model/block.cpp:123-125). */
+    void* out2;
+    void* out3;
+    uint64_t out2_batch_stride, out3_batch_stride;
+    uint32_t split1, split2;
+    /* != 0: W holds d gate rows followed by d up rows and out[b][j] = silu(gate_j . x) * (up_j . x), the first half of
+     * the SwiGLU FFN in one launch (src/model/block.cpp:198-210). d a multiple of 16, no segments. */
+    int32_t swiglu;
 } AttnGemvArgs;
 
 int attn_gemv_f16(const AttnGemvArgs* args, void* stream);

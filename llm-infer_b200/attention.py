@@ -222,26 +222,46 @@ def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.floa
     return out
 
 
-def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.float32, clip: float = 0.0,
-              accumulate: bool = False, status=None, stream=None) -> torch.Tensor:
-    """out[b] = clamp(W x[b]) over Q8_0 weights: x [B, n] fp32, w uint8 [d, n/32*34] (GGML blocks: fp16 scale + 32
-    signed bytes) -> out [B, d] fp32 or fp16. Same conventions as gemv_f16."""
+def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=None, out_dtype=torch.float32,
+              clip: float = 0.0, accumulate: bool = False, swiglu: bool = False, status=None,
+              stream=None) -> torch.Tensor:
+    """out[b] = clamp(W x[b]) over Q8_0 weights: x [B, n] fp32, w uint8 [rows, n/32*34] (GGML blocks: fp16 scale + 32
+    signed bytes) -> out [B, rows] fp32 or fp16. Same conventions as gemv_f16, plus:
+    * ``out2`` / ``out3``: the rows are split over out, out2, out3 in that order (stacked Q, K, V projections);
+    * ``swiglu``: w holds d gate rows then d up rows, out [B, d] = silu(gate x) * (up x)."""
     _require_cuda(x, w)
     B, n = x.shape
-    d = w.shape[0]
-    if w.dtype != torch.uint8 or w.shape != (d, n // 32 * 34) or n % 32 or x.dtype != torch.float32:
-        raise ValueError("x must be fp32 [B, n] and w uint8 [d, n/32*34]")
+    rows = w.shape[0]
+    if w.dtype != torch.uint8 or w.shape != (rows, n // 32 * 34) or n % 32 or x.dtype != torch.float32:
+        raise ValueError("x must be fp32 [B, n] and w uint8 [rows, n/32*34]")
+    if swiglu and (rows % 2 or out2 is not None or out3 is not None):
+        raise ValueError("swiglu needs an even number of rows (gate rows, then up rows) and a single output")
     x, w = x.contiguous(), w.contiguous()
+    d = rows // 2 if swiglu else rows
+    segs = [t for t in (out2, out3) if t is not None]
+    if out3 is not None and out2 is None:
+        raise ValueError("out3 without out2")
+    d0 = d - sum(t.shape[1] for t in segs)
     if out is None:
-        out = torch.empty((B, d), dtype=out_dtype, device=x.device)
-    if out.shape != (B, d) or out.stride(1) != 1:
-        raise ValueError("out must be [B, d] with dense rows")
+        out = torch.empty((B, d0), dtype=out_dtype, device=x.device)
+    for t in [out] + segs:
+        if t.shape[0] != B or t.stride(1) != 1 or t.dtype != out.dtype:
+            raise ValueError("outputs must be [B, rows] with dense rows and one dtype")
+    if out.shape[1] != d0 or d0 <= 0:
+        raise ValueError("output widths do not add up to the rows of w")
     a = _b.AttnGemvArgs()
     a.out, a.x, a.w = out.data_ptr(), x.data_ptr(), w.data_ptr()
-    a.out_batch_stride = out.stride(0) if B > 1 else d
+    a.out_batch_stride = out.stride(0) if B > 1 else d0
     a.n, a.d, a.batch, a.clip, a.out_dtype = n, d, B, float(clip), _dtype_code(out)
     a.accumulate = int(accumulate)
+    a.swiglu = int(swiglu)
     a.status = status.data_ptr() if status is not None else None
+    if out2 is not None:
+        a.out2, a.split1 = out2.data_ptr(), d0
+        a.out2_batch_stride = out2.stride(0) if B > 1 else out2.shape[1]
+    if out3 is not None:
+        a.out3, a.split2 = out3.data_ptr(), d0 + out2.shape[1]
+        a.out3_batch_stride = out3.stride(0) if B > 1 else out3.shape[1]
     with torch.cuda.device(x.device):
         _b.check(_b.load().attn_gemv_q8_0(C.byref(a), _stream_ptr(stream)), "attn_gemv_q8_0")
     return out

@@ -148,6 +148,13 @@ class AttnGemvArgs(C.Structure):
         ("out_dtype", C.c_int32),
         ("accumulate", C.c_int32),
         ("status", C.c_void_p),
+        ("out2", C.c_void_p),
+        ("out3", C.c_void_p),
+        ("out2_batch_stride", C.c_uint64),
+        ("out3_batch_stride", C.c_uint64),
+        ("split1", C.c_uint32),
+        ("split2", C.c_uint32),
+        ("swiglu", C.c_int32),
     ]
 
 

@@ -140,6 +140,7 @@ extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
     if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16) return ATTN_ERR_INVALID_ARG;
     if (a->n % 512 != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
     if (a->accumulate && a->out_dtype != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;
+    if (a->split1 || a->split2 || a->swiglu) return ATTN_ERR_UNSUPPORTED;  // row segments / SwiGLU pairing: Q8_0 kernel only
     if ((reinterpret_cast<uintptr_t>(a->x) & 15u) || (reinterpret_cast<uintptr_t>(a->w) & 31u)) return ATTN_ERR_ALIGNMENT;
     DeviceInfo dev{};
     int rc = current_device_info(&dev);

@@ -16,7 +16,13 @@
 // |x| is clamped to the fp16 range, 65504), fp32 accumulation per block, then one fp32 multiply-add by the block's
 // scale per row. The eight warps' partial sums of a row group are added in a fixed order.
 //
-// Algorithmic bytes per call = d * n/32 * 34 + batch * (n*4 + d*sizeof(out)).
+// Three extras serve the transformer block: the output rows may be split into up to three segments with their own
+// buffers (one launch for the Q, K and V projections over a stacked matrix); with `swiglu` the matrix holds gate rows
+// followed by up rows and the kernel writes silu(gate x) * (up x) (one launch for the FFN's first half); and when the
+// activations of all sequences do not fit in shared memory next to the ring (batch 8 x 14336), the inner dimension is
+// staged in equal slices inside the one launch, partial sums carried in shared memory.
+//
+// Algorithmic bytes per call = rows * n/32 * 34 + batch * (n*4 + d*sizeof(out)).
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -37,16 +43,21 @@ constexpr uint32_t kStageBytes = kRows * kSegPitch;         // 4352 = 34 x 128
 constexpr uint32_t kMaxStages = 4;
 
 struct Q8Params {
-    void* out;
+    void* out0;               // rows [0, seg_end0)
+    void* out1;               // rows [seg_end0, seg_end1)
+    void* out2;               // rows [seg_end1, d)
+    uint64_t out_stride0, out_stride1, out_stride2;  // elements between sequences of each output
     const float* x;
     uint32_t* status;
-    uint64_t out_batch_stride;
-    uint32_t x_elem0;         // first 32-bit element of this launch's column slice inside a row of W
     uint64_t x_batch_stride;  // elements between sequences of x
-    uint32_t n_blocks;        // blocks of this launch's column slice (multiple of kChunkBlocks)
-    uint32_t d, batch;
+    uint32_t seg_end0, seg_end1;
+    uint32_t slice_blocks;    // blocks of the inner dimension staged at a time (multiple of kChunkBlocks)
+    uint32_t n_slices;        // slice_blocks * n_slices = blocks per row
+    uint32_t d, batch;        // output rows; with swiglu W has 2 d rows: gate rows, then up rows
     uint32_t stages;
     uint32_t x_col_pitch;     // 32-bit words between sequences of the staged activations
+    uint32_t acc_groups;      // row groups per CTA whose partial sums are carried across slices (0 when n_slices == 1)
+    uint32_t swiglu;
     float clip;
     int32_t out_dtype;
     int32_t accumulate;
@@ -126,19 +137,23 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
                                                                   const __grid_constant__ Q8Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // tile loads want 128-byte alignment
-    // layout: [ring: warps x stages x kStageBytes][red: 2 x warps x 128 floats][bars: warps x kMaxStages][x fragments]
+    // layout: [ring: warps x stages x kStageBytes][red: 2 x 2 x warps x 128 floats][acc: acc_groups x 2 x 128 floats]
+    //         [bars: warps x kMaxStages][x fragments]
     const uint32_t ring_bytes = kQ8Warps * p.stages * kStageBytes;
     float* s_red = reinterpret_cast<float*>(smem + ring_bytes);
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + ring_bytes + 2 * kQ8Warps * 128 * sizeof(float));
-    uint32_t* s_x = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(s_bar) + kQ8Warps * kMaxStages * sizeof(uint64_t));
+    float* s_acc = s_red + 2 * 2 * kQ8Warps * 128;
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_acc + p.acc_groups * 2 * 128);
+    uint32_t* s_x = reinterpret_cast<uint32_t*>(s_bar + kQ8Warps * kMaxStages);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t groups = (p.d + kRows - 1) / kRows;
-    const uint32_t n_chunks = p.n_blocks / kChunkBlocks;
-    const uint32_t cpw = (n_chunks > warp) ? (n_chunks - warp + kQ8Warps - 1) / kQ8Warps : 0;  // chunks per warp and group
+    const uint32_t parts = p.swiglu ? 2u : 1u;  // row groups of W per output row group (gate, up)
+    const uint32_t slice_chunks = p.slice_blocks / kChunkBlocks;
+    // chunks of one slice of one row group that this warp owns: warp, warp + 8, ...
+    const uint32_t cpw = (slice_chunks > warp) ? (slice_chunks - warp + kQ8Warps - 1) / kQ8Warps : 0;
     const uint32_t my_groups = (groups > blockIdx.x) ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const uint32_t total = my_groups * cpw;
+    const uint32_t total = p.n_slices * my_groups * parts * cpw;  // items, in the order slice > group > part > chunk
 
     const uint32_t ring0 = smem_u32(smem) + warp * p.stages * kStageBytes;
     const uint32_t bar0 = smem_u32(s_bar) + warp * kMaxStages * 8;
@@ -151,15 +166,19 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
     __syncwarp();
 
     auto issue = [&](uint32_t item) {
-        const uint32_t rg = blockIdx.x + (item / cpw) * gridDim.x;
-        const uint32_t chunk = warp + (item % cpw) * kQ8Warps;
+        const uint32_t ci = item % cpw, q = item / cpw;
+        const uint32_t part = q % parts, q2 = q / parts;
+        const uint32_t gi = q2 % my_groups, slice = q2 / my_groups;
+        const uint32_t rg = blockIdx.x + gi * gridDim.x;
+        const uint32_t chunk = slice * slice_chunks + warp + ci * kQ8Warps;
         const uint32_t stage = item % p.stages;
         const uint32_t bar = bar0 + 8 * stage;
         if (lane == 0) {
             mbar_arrive_expect_tx(bar, kStageBytes);
-            // x in 32-bit elements (a multiple of 4: 16-byte rule), y = first row of the group
-            tma_load_rows(ring0 + stage * kStageBytes, &tm_w, bar, static_cast<int>(p.x_elem0 + chunk * (kSegBytes / 4)),
-                          static_cast<int>(rg * kRows), policy);
+            // x in 32-bit elements (a multiple of 4: 16-byte rule), y = first row of the group (rows past the
+            // tensor read as zeros)
+            tma_load_rows(ring0 + stage * kStageBytes, &tm_w, bar, static_cast<int>(chunk * (kSegBytes / 4)),
+                          static_cast<int>(part * p.d + rg * kRows), policy);
         }
     };
     // The weights do not depend on the activations (no kernel writes them): start streaming them at once, let the next
@@ -168,97 +187,121 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
     grid_dep_launch_dependents();
     grid_dep_wait();
 
-    // Activations as B fragments: for sequence c, block blk, k-step s, quarter t: four 32-bit words
-    // {hi(x0,x1), hi(x2,x3), lo(x0,x1), lo(x2,x3)} of the elements x[32 blk + 16 s + 4 t .. +4).
-    for (uint32_t i = tid; i < p.batch * p.n_blocks * 8; i += kQ8Threads) {
-        const uint32_t c = i / (p.n_blocks * 8), r = i - c * (p.n_blocks * 8);
-        const uint32_t blk = r >> 3, s = (r >> 2) & 1, tt = r & 3;
-        float4 v = *reinterpret_cast<const float4*>(p.x + c * p.x_batch_stride + 32 * blk + 16 * s + 4 * tt);
-        v.x = fminf(fmaxf(v.x, -65504.f), 65504.f);
-        v.y = fminf(fmaxf(v.y, -65504.f), 65504.f);
-        v.z = fminf(fmaxf(v.z, -65504.f), 65504.f);
-        v.w = fminf(fmaxf(v.w, -65504.f), 65504.f);
-        const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
-        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-        const __half2 l01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y), l23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
-        uint4 o;
-        o.x = *reinterpret_cast<const uint32_t*>(&h01);
-        o.y = *reinterpret_cast<const uint32_t*>(&h23);
-        o.z = *reinterpret_cast<const uint32_t*>(&l01);
-        o.w = *reinterpret_cast<const uint32_t*>(&l23);
-        *reinterpret_cast<uint4*>(s_x + c * p.x_col_pitch + (blk * 2 + s) * 16 + tt * 4) = o;
-    }
-    __syncthreads();
-
     const bool has_col = g < p.batch;  // lanes of the other columns feed zeros
     const uint32_t* my_x = s_x + (has_col ? g : 0) * p.x_col_pitch + t * 4;
     bool timed_out = false;
-    uint32_t item = 0;
-    for (uint32_t gi = 0; gi < my_groups; ++gi) {
-        const uint32_t rg = blockIdx.x + gi * gridDim.x;
-        float tot[4] = {0.f, 0.f, 0.f, 0.f};
-        for (uint32_t ci = 0; ci < cpw; ++ci, ++item) {
-            const uint32_t stage = item % p.stages;
-            if (!mbar_wait(bar0 + 8 * stage, (item / p.stages) & 1)) timed_out = true;
-            const uint32_t chunk = warp + ci * kQ8Warps;
-            const uint32_t seg_lo = ring0 + stage * kStageBytes + g * kSegPitch;
-            const uint32_t seg_hi = seg_lo + 8 * kSegPitch;
-            const uint32_t* xb = my_x + chunk * kChunkBlocks * 32;
-#pragma unroll
-            for (uint32_t bi = 0; bi < kChunkBlocks; ++bi) {
-                uint32_t alo[4], ahi[4];
-                if (bi & 1) {
-                    load_a<false>(alo, seg_lo, bi, t);
-                    load_a<false>(ahi, seg_hi, bi, t);
-                } else {
-                    load_a<true>(alo, seg_lo, bi, t);
-                    load_a<true>(ahi, seg_hi, bi, t);
-                }
-                uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
-                if (has_col) {
-                    x0 = *reinterpret_cast<const uint4*>(xb + bi * 32);
-                    x1 = *reinterpret_cast<const uint4*>(xb + bi * 32 + 16);
-                }
-                float acc[4];
-                mma_f16_first(acc, alo[0], ahi[0], alo[1], ahi[1], x0.z, x0.w);  // k-step 0, residual
-                mma_f16(acc, alo[2], ahi[2], alo[3], ahi[3], x1.z, x1.w);        // k-step 1, residual
-                mma_f16(acc, alo[0], ahi[0], alo[1], ahi[1], x0.x, x0.y);        // k-step 0, value
-                mma_f16(acc, alo[2], ahi[2], alo[3], ahi[3], x1.x, x1.y);        // k-step 1, value
-                const float s_lo = lds_scale(seg_lo + kBlockBytes * bi), s_hi = lds_scale(seg_hi + kBlockBytes * bi);
-                tot[0] = fmaf(s_lo, acc[0], tot[0]);
-                tot[1] = fmaf(s_lo, acc[1], tot[1]);
-                tot[2] = fmaf(s_hi, acc[2], tot[2]);
-                tot[3] = fmaf(s_hi, acc[3], tot[3]);
-            }
-            __syncwarp();
-            if (item + p.stages < total) {
-                // order this warp's reads of the stage before the asynchronous writes that refill it
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                issue(item + p.stages);
-            }
+    uint32_t item = 0, round = 0;
+    for (uint32_t slice = 0; slice < p.n_slices; ++slice) {
+        // Activations of this slice as B fragments: for sequence c, block blk, k-step s, quarter t: four 32-bit words
+        // {hi(x0,x1), hi(x2,x3), lo(x0,x1), lo(x2,x3)} of the elements x[32 blk + 16 s + 4 t .. +4). Every warp has
+        // passed the previous slice's last block-wide barrier, so nobody still reads the old fragments.
+        const float* xs = p.x + static_cast<size_t>(slice) * p.slice_blocks * 32;
+        for (uint32_t i = tid; i < p.batch * p.slice_blocks * 8; i += kQ8Threads) {
+            const uint32_t c = i / (p.slice_blocks * 8), r = i - c * (p.slice_blocks * 8);
+            const uint32_t blk = r >> 3, s = (r >> 2) & 1, tt = r & 3;
+            float4 v = *reinterpret_cast<const float4*>(xs + c * p.x_batch_stride + 32 * blk + 16 * s + 4 * tt);
+            v.x = fminf(fmaxf(v.x, -65504.f), 65504.f);
+            v.y = fminf(fmaxf(v.y, -65504.f), 65504.f);
+            v.z = fminf(fmaxf(v.z, -65504.f), 65504.f);
+            v.w = fminf(fmaxf(v.w, -65504.f), 65504.f);
+            const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const __half2 l01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y), l23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
+            uint4 o;
+            o.x = *reinterpret_cast<const uint32_t*>(&h01);
+            o.y = *reinterpret_cast<const uint32_t*>(&h23);
+            o.z = *reinterpret_cast<const uint32_t*>(&l01);
+            o.w = *reinterpret_cast<const uint32_t*>(&l23);
+            *reinterpret_cast<uint4*>(s_x + c * p.x_col_pitch + (blk * 2 + s) * 16 + tt * 4) = o;
         }
-        // fixed-order sum of the warps' partial sums
-        float* red = s_red + (gi & 1) * kQ8Warps * 128 + warp * 128;
-        red[g * 8 + 2 * t] = tot[0];
-        red[g * 8 + 2 * t + 1] = tot[1];
-        red[(g + 8) * 8 + 2 * t] = tot[2];
-        red[(g + 8) * 8 + 2 * t + 1] = tot[3];
         __syncthreads();
-        if (tid < 128) {
-            const uint32_t r = tid >> 3, c = tid & 7;
-            const float* src = s_red + (gi & 1) * kQ8Warps * 128 + tid;
-            float y = 0.f;
+
+        for (uint32_t gi = 0; gi < my_groups; ++gi, ++round) {
+            const uint32_t rg = blockIdx.x + gi * gridDim.x;
+            float* red = s_red + (round & 1) * 2 * kQ8Warps * 128;
+            for (uint32_t part = 0; part < parts; ++part) {
+                float tot[4] = {0.f, 0.f, 0.f, 0.f};
+                for (uint32_t ci = 0; ci < cpw; ++ci, ++item) {
+                    const uint32_t stage = item % p.stages;
+                    if (!mbar_wait(bar0 + 8 * stage, (item / p.stages) & 1)) timed_out = true;
+                    const uint32_t seg_lo = ring0 + stage * kStageBytes + g * kSegPitch;
+                    const uint32_t seg_hi = seg_lo + 8 * kSegPitch;
+                    const uint32_t* xb = my_x + (warp + ci * kQ8Warps) * kChunkBlocks * 32;
 #pragma unroll
-            for (int w = 0; w < kQ8Warps; ++w) y += src[w * 128];
-            const uint32_t row = rg * kRows + r;
-            if (row < p.d && c < p.batch) {
-                if (p.clip > 0.f) y = fminf(fmaxf(y, -p.clip), p.clip);
-                const size_t o = static_cast<size_t>(c) * p.out_batch_stride + row;
-                if (p.out_dtype == ATTN_DTYPE_F32) {
-                    float* dst = reinterpret_cast<float*>(p.out) + o;
-                    *dst = p.accumulate ? *dst + y : y;
-                } else {
-                    reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(y);
+                    for (uint32_t bi = 0; bi < kChunkBlocks; ++bi) {
+                        uint32_t alo[4], ahi[4];
+                        if (bi & 1) {
+                            load_a<false>(alo, seg_lo, bi, t);
+                            load_a<false>(ahi, seg_hi, bi, t);
+                        } else {
+                            load_a<true>(alo, seg_lo, bi, t);
+                            load_a<true>(ahi, seg_hi, bi, t);
+                        }
+                        uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+                        if (has_col) {
+                            x0 = *reinterpret_cast<const uint4*>(xb + bi * 32);
+                            x1 = *reinterpret_cast<const uint4*>(xb + bi * 32 + 16);
+                        }
+                        float acc[4];
+                        mma_f16_first(acc, alo[0], ahi[0], alo[1], ahi[1], x0.z, x0.w);  // k-step 0, residual
+                        mma_f16(acc, alo[2], ahi[2], alo[3], ahi[3], x1.z, x1.w);        // k-step 1, residual
+                        mma_f16(acc, alo[0], ahi[0], alo[1], ahi[1], x0.x, x0.y);        // k-step 0, value
+                        mma_f16(acc, alo[2], ahi[2], alo[3], ahi[3], x1.x, x1.y);        // k-step 1, value
+                        const float s_lo = lds_scale(seg_lo + kBlockBytes * bi), s_hi = lds_scale(seg_hi + kBlockBytes * bi);
+                        tot[0] = fmaf(s_lo, acc[0], tot[0]);
+                        tot[1] = fmaf(s_lo, acc[1], tot[1]);
+                        tot[2] = fmaf(s_hi, acc[2], tot[2]);
+                        tot[3] = fmaf(s_hi, acc[3], tot[3]);
+                    }
+                    __syncwarp();
+                    if (item + p.stages < total) {
+                        // order this warp's reads of the stage before the asynchronous writes that refill it
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        issue(item + p.stages);
+                    }
+                }
+                float* mine = red + (part * kQ8Warps + warp) * 128;
+                mine[g * 8 + 2 * t] = tot[0];
+                mine[g * 8 + 2 * t + 1] = tot[1];
+                mine[(g + 8) * 8 + 2 * t] = tot[2];
+                mine[(g + 8) * 8 + 2 * t + 1] = tot[3];
+            }
+            __syncthreads();
+            if (tid < 128) {
+                // fixed-order sum of the warps' partial sums; carried across slices in shared memory
+                float y[2] = {0.f, 0.f};
+                for (uint32_t part = 0; part < parts; ++part) {
+                    const float* src = red + part * kQ8Warps * 128 + tid;
+                    float v = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kQ8Warps; ++w) v += src[w * 128];
+                    if (p.n_slices > 1) {
+                        float* carry = s_acc + (gi * 2 + part) * 128 + tid;
+                        if (slice > 0) v += *carry;
+                        if (slice + 1 < p.n_slices) *carry = v;
+                    }
+                    y[part] = v;
+                }
+                const uint32_t row = rg * kRows + (tid >> 3), c = tid & 7;
+                if (slice + 1 == p.n_slices && row < p.d && c < p.batch) {
+                    float v = y[0];
+                    if (p.swiglu) v = __fdiv_rn(v, 1.0f + expf(-v)) * y[1];  // silu(gate) * up, src/model/block.cpp:206-210
+                    if (p.clip > 0.f) v = fminf(fmaxf(v, -p.clip), p.clip);
+                    void* out = p.out0;
+                    uint64_t stride = p.out_stride0;
+                    uint32_t r0 = 0;
+                    if (row >= p.seg_end1) {
+                        out = p.out2, stride = p.out_stride2, r0 = p.seg_end1;
+                    } else if (row >= p.seg_end0) {
+                        out = p.out1, stride = p.out_stride1, r0 = p.seg_end0;
+                    }
+                    const size_t o = static_cast<size_t>(c) * stride + (row - r0);
+                    if (p.out_dtype == ATTN_DTYPE_F32) {
+                        float* dst = reinterpret_cast<float*>(out) + o;
+                        *dst = p.accumulate ? *dst + v : v;
+                    } else {
+                        reinterpret_cast<__half*>(out)[o] = __float2half_rn(v);
+                    }
                 }
             }
         }
@@ -294,36 +337,43 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16) return ATTN_ERR_INVALID_ARG;
     if (a->n % (32 * kChunkBlocks) != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
     if (a->accumulate && a->out_dtype != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;
+    if (a->swiglu && (a->d % kRows != 0 || a->split1 || a->split2)) return ATTN_ERR_UNSUPPORTED;
+    if ((a->split1 && (!a->out2 || a->split1 >= a->d)) || (a->split2 && (!a->out3 || a->split2 <= a->split1 || a->split2 >= a->d)))
+        return ATTN_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(a->x) & 15u) || (reinterpret_cast<uintptr_t>(a->w) & 15u)) return ATTN_ERR_ALIGNMENT;
     DeviceInfo dev{};
     int rc = current_device_info(&dev);
     if (rc != ATTN_OK) return rc;
-    const uint32_t n_blocks = a->n / 32;
-    const size_t fixed = 2 * kQ8Warps * 128 * sizeof(float) + kQ8Warps * kMaxStages * sizeof(uint64_t) + 128;
-    // staged activations: 128 bytes per block and sequence, sequences 64 bytes apart modulo 128 (bank spread)
-    auto x_bytes = [&](uint32_t blocks) { return static_cast<size_t>(a->batch) * (blocks * 128 + 64); };
-    // as many ring stages as fit next to the activations, and column slices when even two do not
-    const size_t budget = static_cast<size_t>(dev.max_smem_optin);
-    if (budget < fixed + 2 * kQ8Warps * kStageBytes + x_bytes(kChunkBlocks)) return ATTN_ERR_UNSUPPORTED;
-    uint32_t slice_blocks = n_blocks;
-    const size_t room = budget - fixed - 2 * kQ8Warps * kStageBytes;
-    if (x_bytes(slice_blocks) > room) {
-        slice_blocks = static_cast<uint32_t>((room / a->batch - 64) / 128) / kChunkBlocks * kChunkBlocks;
-    }
-    const uint32_t slices = (n_blocks + slice_blocks - 1) / slice_blocks;
-    // equal slices (a multiple of the chunk) rather than full ones and a remainder
-    slice_blocks = ((n_blocks + slices - 1) / slices + kChunkBlocks - 1) / kChunkBlocks * kChunkBlocks;
-    if (slices > 1 && (a->clip > 0.f || a->out_dtype != ATTN_DTYPE_F32)) return ATTN_ERR_UNSUPPORTED;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const uint32_t n_blocks = a->n / 32, n_chunks = n_blocks / kChunkBlocks;
     const uint32_t groups = (a->d + kRows - 1) / kRows;
     const uint32_t grid = groups < static_cast<uint32_t>(dev.sm_count) ? groups : static_cast<uint32_t>(dev.sm_count);
-    // W as a 2-D tensor of 32-bit elements [d][row_bytes / 4]; one box = 16 rows x 272 bytes, no swizzle.
+    const uint32_t groups_per_cta = (groups + grid - 1) / grid;
+    const size_t budget = static_cast<size_t>(dev.max_smem_optin);
+    // staged activations: 128 bytes per block and sequence, sequences 64 bytes apart modulo 128 (bank spread)
+    auto x_bytes = [&](uint32_t blocks) { return static_cast<size_t>(a->batch) * (blocks * 128 + 64); };
+    auto fixed_bytes = [&](uint32_t slices) {
+        return 2 * 2 * kQ8Warps * 128 * sizeof(float) + (slices > 1 ? groups_per_cta * 2 * 128 * sizeof(float) : 0) +
+               kQ8Warps * kMaxStages * sizeof(uint64_t) + 128;
+    };
+    // The activations are staged in equal slices of the inner dimension, as few as leave room for a two-stage ring; the
+    // partial sums of the CTA's row groups are carried from slice to slice in shared memory.
+    uint32_t slices = 1;
+    while (slices <= n_chunks &&
+           (n_chunks % slices != 0 || fixed_bytes(slices) + 2 * kQ8Warps * kStageBytes + x_bytes(n_blocks / slices) > budget))
+        ++slices;
+    if (slices > n_chunks) return ATTN_ERR_UNSUPPORTED;
+    const uint32_t slice_blocks = n_blocks / slices;
+    uint32_t stages = kMaxStages;
+    while (stages > 2 && fixed_bytes(slices) + stages * kQ8Warps * kStageBytes + x_bytes(slice_blocks) > budget) --stages;
+    const size_t smem = fixed_bytes(slices) + static_cast<size_t>(stages) * kQ8Warps * kStageBytes + x_bytes(slice_blocks);
+
+    // W as a 2-D tensor of 32-bit elements [rows][row_bytes / 4]; one box = 16 rows x 272 bytes, no swizzle.
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return ATTN_ERR_CUDA;
     CUtensorMap tm_w;
     {
         const cuuint64_t row_bytes = static_cast<cuuint64_t>(n_blocks) * kBlockBytes;
-        const cuuint64_t dims[2] = {row_bytes / 4, a->d};
+        const cuuint64_t dims[2] = {row_bytes / 4, static_cast<cuuint64_t>(a->d) * (a->swiglu ? 2 : 1)};
         const cuuint64_t strides[1] = {row_bytes};
         const cuuint32_t box[2] = {kSegBytes / 4, kRows};
         const cuuint32_t estr[2] = {1, 1};
@@ -335,29 +385,33 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
             return ATTN_ERR_CUDA;
         }
     }
-    for (uint32_t s = 0; s < slices; ++s) {
-        const uint32_t b0 = s * slice_blocks;
-        Q8Params p{};
-        p.out = a->out;
-        p.x = a->x + static_cast<size_t>(b0) * 32;
-        p.x_elem0 = b0 * kBlockBytes / 4;  // b0 is a multiple of 8: 272 bytes per 8 blocks
-        p.status = a->status;
-        p.out_batch_stride = a->out_batch_stride ? a->out_batch_stride : a->d;
-        p.x_batch_stride = a->n;
-        p.n_blocks = (n_blocks - b0 < slice_blocks) ? n_blocks - b0 : slice_blocks;
-        p.d = a->d;
-        p.batch = a->batch;
-        p.x_col_pitch = p.n_blocks * 32 + 16;
-        p.clip = a->clip;
-        p.out_dtype = a->out_dtype;
-        p.accumulate = (s > 0) ? 1 : a->accumulate;
-        uint32_t stages = kMaxStages;
-        while (stages > 2 && fixed + stages * kQ8Warps * kStageBytes + x_bytes(p.n_blocks) > budget) --stages;
-        p.stages = stages;
-        const size_t smem = fixed + static_cast<size_t>(stages) * kQ8Warps * kStageBytes + x_bytes(p.n_blocks);
-        B200_CUDA_TRY(cudaFuncSetAttribute(gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        B200_CUDA_TRY(launch_dependent(gemv_q8_0_kernel, dim3(grid), dim3(kQ8Threads), smem, stream, tm_w, p));
-        g_launch_count.fetch_add(1, std::memory_order_relaxed);
-    }
+    Q8Params p{};
+    const uint64_t stride0 = a->out_batch_stride ? a->out_batch_stride : (a->split1 ? a->split1 : a->d);
+    p.out0 = a->out;
+    p.out_stride0 = stride0;
+    p.seg_end0 = a->split1 ? a->split1 : a->d;
+    p.out1 = a->out2;
+    p.out_stride1 = a->out2_batch_stride ? a->out2_batch_stride : ((a->split2 ? a->split2 : a->d) - p.seg_end0);
+    p.seg_end1 = a->split2 ? a->split2 : a->d;
+    p.out2 = a->out3;
+    p.out_stride2 = a->out3_batch_stride ? a->out3_batch_stride : (a->d - p.seg_end1);
+    p.x = a->x;
+    p.status = a->status;
+    p.x_batch_stride = a->n;
+    p.slice_blocks = slice_blocks;
+    p.n_slices = slices;
+    p.d = a->d;
+    p.batch = a->batch;
+    p.stages = stages;
+    p.x_col_pitch = slice_blocks * 32 + 16;
+    p.acc_groups = slices > 1 ? groups_per_cta : 0;
+    p.swiglu = a->swiglu ? 1u : 0u;
+    p.clip = a->clip;
+    p.out_dtype = a->out_dtype;
+    p.accumulate = a->accumulate;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    B200_CUDA_TRY(cudaFuncSetAttribute(gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    B200_CUDA_TRY(launch_dependent(gemv_q8_0_kernel, dim3(grid), dim3(kQ8Threads), smem, stream, tm_w, p));
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return ATTN_OK;
 }

@@ -4,7 +4,8 @@ The engine's forward is one token of one sequence at a time (``Model::forward``,
 ``Block::block_cpu_``, src/model/block.cpp:105-223); its CUDA block stops after attention
 (src/model/block.cu:235-239). This class runs the same sequence of steps for ``batch`` independent sequences per
 call, each with its own position and KV cache, through the C ABI kernels only (GEMV, RMSNorm, RoPE + cache insert,
-split-KV attention, SwiGLU, argmax): 13 launches per layer, none of them on the host, no CPU fallback.
+split-KV attention, SwiGLU, argmax): 13 launches per layer with fp16 weights, 9 with Q8_0 weights (stacked Q/K/V
+projection, SwiGLU as the epilogue of the stacked gate/up projection), none of them on the host, no CPU fallback.
 
 Weights are the engine's: fp16 ``[d][n]`` matrices (n fastest, GGUF dims ``[n_in, n_out]``), fp32 norm vectors,
 stacked over the layers here. The KV caches keep the engine's ``[row][kv_head][head_dim]`` fp16 layout, one cache
@@ -109,6 +110,11 @@ class Llama:
             if tuple(t.shape) != shape or t.dtype != want:
                 raise ValueError(f"weight {name}: expected {shape} {want}, got {tuple(t.shape)} {t.dtype}")
             self.w[name] = t.to(dev).contiguous()
+        if q8:
+            # The Q8_0 GEMV takes stacked matrices: Q, K and V rows in one launch with three outputs, and gate (w1)
+            # rows followed by up (w3) rows with the SwiGLU product as its epilogue. Only the stacks are kept.
+            self.w["wqkv"] = torch.cat([self.w.pop("wq"), self.w.pop("wk"), self.w.pop("wv")], dim=1).contiguous()
+            self.w["w13"] = torch.cat([self.w.pop("w1"), self.w.pop("w3")], dim=1).contiguous()
         B, f32 = batch, torch.float32
         q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
         z = lambda *s, dtype=f32: torch.zeros(*s, dtype=dtype, device=dev)  # noqa: E731
@@ -162,20 +168,28 @@ class Llama:
         gemv = self._gemv
         self._embed(w["embed"], self.tokens, out=self.x, status=self.status)
         att_flat = self.att.view(B, self._q_dim)
+        q8 = self.weight_type == "q8_0"
         for l in range(c.n_layers):
             A.rmsnorm(self.x, w["rms_att"][l], c.norm_eps, out=self.xb)
-            gemv(self.xb, w["wq"][l], out=self.q.view(B, self._q_dim), clip=c.qkv_clip)
-            gemv(self.xb, w["wk"][l], out=self.k.view(B, self._kv_dim), clip=c.qkv_clip)
-            gemv(self.xb, w["wv"][l], out=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
+            if q8:
+                gemv(self.xb, w["wqkv"][l], out=self.q.view(B, self._q_dim), out2=self.k.view(B, self._kv_dim),
+                     out3=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
+            else:
+                gemv(self.xb, w["wq"][l], out=self.q.view(B, self._q_dim), clip=c.qkv_clip)
+                gemv(self.xb, w["wk"][l], out=self.k.view(B, self._kv_dim), clip=c.qkv_clip)
+                gemv(self.xb, w["wv"][l], out=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
             A.rope_kv_insert(self.q, self.k, self.v, self.k_cache[l], self.v_cache[l], self.pos, self.kv_pos,
                              theta=c.rope_theta, rotary_dim=c.rotary_dim, kv_sink=kv_sink, q_out=self.q)
             A.attn_decode(self.q, self.k_cache[l], self.v_cache[l], self.kv_len, out=self.att,
                           workspace=self.workspace)
             gemv(att_flat, w["wo"][l], out=self.x, accumulate=True)       # x += Wo att
             A.rmsnorm(self.x, w["rms_ffn"][l], c.norm_eps, out=self.xb)
-            gemv(self.xb, w["w1"][l], out=self.hb)
-            gemv(self.xb, w["w3"][l], out=self.hb2)
-            A.swiglu_(self.hb, self.hb2)
+            if q8:
+                gemv(self.xb, w["w13"][l], out=self.hb, swiglu=True)      # hb = silu(W1 xb) * (W3 xb)
+            else:
+                gemv(self.xb, w["w1"][l], out=self.hb)
+                gemv(self.xb, w["w3"][l], out=self.hb2)
+                A.swiglu_(self.hb, self.hb2)
             gemv(self.hb, w["w2"][l], out=self.x, accumulate=True)        # x += W2 (silu(W1 xb) * W3 xb)
         if not want_logits:
             return  # prefill mode: no final norm, no classifier (src/model/model.cpp:74-76)

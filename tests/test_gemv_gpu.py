@@ -158,3 +158,29 @@ def test_q8_0_streams_weights_near_hbm_rate(attention, pkg):
     gbs = (d * n // 32 * 34 + n * 4 + d * 4) / us / 1e3
     print(f"gemv {d}x{n} q8_0: {us:.1f} us, {gbs:.0f} GB/s")
     assert gbs > 3000
+
+
+def test_q8_0_stacked_qkv_and_swiglu_epilogue(attention, port, pkg):
+    """One launch for the Q, K and V projections (three outputs) and one for silu(W1 x) * (W3 x), batch 8."""
+    import torch
+    from llm_infer_b200 import quant
+    rng = np.random.default_rng(77)
+    n, B = 2048, 8
+    x = rng.standard_normal((B, n), dtype=np.float32)
+    wq, wk, wv = (quant.quantize_q8_0(rng.standard_normal((d, n), dtype=np.float32) * 0.03) for d in (512, 128, 128))
+    stacked = torch.from_numpy(np.concatenate([wq, wk, wv])).cuda()
+    q, k, v = (torch.empty(B, d, device="cuda") for d in (512, 128, 128))
+    attention.gemv_q8_0(torch.from_numpy(x).cuda(), stacked, out=q, out2=k, out3=v, clip=0.8)
+    for got, w in ((q, wq), (k, wk), (v, wv)):
+        got = got.cpu().numpy()
+        mag = np.abs(x) @ np.abs(quant.dequantize_q8_0(w)).T
+        for b in range(B):
+            assert (np.abs(got[b] - port.matmul_q8_0(x[b], w, 0.8)) <= 4e-6 * mag[b] + 1e-7).all()
+    hidden = 1040  # 65 row groups: the up rows start at a group boundary that is not a multiple of the grid
+    w1, w3 = (quant.quantize_q8_0(rng.standard_normal((hidden, n), dtype=np.float32) * 0.03) for _ in range(2))
+    got = attention.gemv_q8_0(torch.from_numpy(x).cuda(), torch.from_numpy(np.concatenate([w1, w3])).cuda(),
+                              swiglu=True).cpu().numpy()
+    assert got.shape == (B, hidden)
+    for b in range(B):
+        want = port.swiglu(port.matmul_q8_0(x[b], w1), port.matmul_q8_0(x[b], w3))
+        assert np.abs(got[b] - want).max() <= 2e-5 * np.abs(want).max() + 1e-6
