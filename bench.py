@@ -213,7 +213,7 @@ def prefill_measure(torch, attention, wl, steps: int, warmup: int, tflops_peak: 
 
 
 # --------------------------------------------------------------------------- our arm, 1 GPU
-def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, prompt_range=(128, 2048)):
+def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, prompt_range=(128, 2048), graph=True):
     """End-to-end greedy generation with a random-init Llama-3-8B-shaped model stored as Q8_0 (32 layers, 4096,
     32/8 heads of 128, FFN 14336, vocab 128256, theta 5e5): a ragged batch of 8 prompts with lengths uniform in
     [128, 2048] (seeded random token ids), 128 new tokens each, token-at-a-time as the engine does, every step one
@@ -228,7 +228,8 @@ def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, pro
     weight_bytes = sum(t.numel() * t.element_size() for k, t in w.items() if k != "embed")
     llama = M.Llama(cfg, w, batch, weight_type="q8_0")
     del w
-    llama.capture()
+    if graph:
+        llama.capture()
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lengths]
     llama.generate([p[:4] for p in prompts], 4)  # warm-up
     timing = {}
@@ -246,6 +247,41 @@ def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, pro
     }
     del llama
     torch.cuda.empty_cache()
+    return res
+
+
+def gemv_measure(torch, steps: int, warmup: int, hbm_peak: float, peak_kind: str):
+    """The weight GEMVs of one Llama-3-8B-shaped layer alone (eager launches, rotated weight copies > L2, CUDA events):
+    fp16 and Q8_0, batch 1 and 8. Used for profiler captures and the GEMV roofline figures."""
+    import numpy as np
+    from llm_infer_b200 import attention as A, quant
+    rng = np.random.default_rng(0)
+    d, n = 14336, 4096
+    res = {}
+    base = rng.standard_normal((2048, n), dtype=np.float32)
+    wq8 = torch.from_numpy(quant.quantize_q8_0(base)).cuda().repeat(d // 2048, 1).contiguous()
+    wf16 = torch.from_numpy(base.astype(np.float16)).cuda().repeat(d // 2048, 1).contiguous()
+    for kind, w, fn in (("q8_0", wq8, A.gemv_q8_0), ("f16", wf16, A.gemv_f16)):
+        copies = [w.clone() for _ in range(int(400e6 // (w.numel() * w.element_size())) + 2)]
+        for batch in (1, 8):
+            x = torch.randn(batch, n, device="cuda")
+            out = torch.empty(batch, d, device="cuda")
+            for i in range(max(3, warmup)):
+                fn(x, copies[i % len(copies)], out=out)
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for i in range(steps):
+                fn(x, copies[i % len(copies)], out=out)
+            t1.record()
+            torch.cuda.synchronize()
+            us = t0.elapsed_time(t1) * 1e3 / steps
+            alg = w.numel() * w.element_size() + batch * (n * 4 + d * 4)
+            res[f"{kind}_b{batch}"] = {"us": round(us, 2), "gbs": round(alg / us / 1e3, 1),
+                                       "frac": round(alg / us / 1e3 / hbm_peak, 3), "algorithmic_bytes": alg}
+        del copies
+    res["note"] = (f"{d}x{n} matrix, eager back-to-back launches (host launch cost included when the kernel is "
+                   f"shorter), frac of {peak_kind} HBM peak {hbm_peak:.1f} GB/s")
     return res
 
 
@@ -416,6 +452,10 @@ def run_single(args):
                          "points": sweep}
     del kbig, vbig, flush
     torch.cuda.empty_cache()
+    try:
+        extra["gemv_layer"] = gemv_measure(torch, 60, 6, hbm_peak, peak_kind)
+    except Exception as e:
+        extra["gemv_layer"] = {"error": str(e)[:300]}
     try:
         extra["generate_c5"] = generate_measure(torch)
     except Exception as e:
@@ -599,8 +639,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prefill-only", action="store_true",
                     help="time only the causal-prefill workload (used for profiler captures)")
+    ap.add_argument("--gemv-only", action="store_true",
+                    help="time only the weight GEMVs of one layer (fp16 and Q8_0; used for profiler captures)")
     ap.add_argument("--generate-only", action="store_true",
                     help="run only the end-to-end greedy generation workload (Q8_0 8B-shaped model) and print it")
+    ap.add_argument("--generate-eager", action="store_true",
+                    help="with --generate-only: launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--generate-short", action="store_true",
                     help="with --generate-only: prompts of 8-16 tokens and 8 new tokens (for profiler launch lists)")
     ap.add_argument("--kernel-only", action="store_true",
@@ -612,10 +656,17 @@ def main():
     if args.impl == "reference":
         run_reference(args, max(world, args.gpus), rank)
         return
+    if args.gemv_only:
+        import torch
+        load_package()
+        hbm_peak, _, peak_kind = measured_peaks()
+        print(json.dumps({"gemv_layer": gemv_measure(torch, args.steps, args.warmup, hbm_peak, peak_kind)}), flush=True)
+        return
     if args.generate_only:
         import torch
         load_package()
         kw = {"n_new": 8, "prompt_range": (8, 16)} if args.generate_short else {}
+        kw["graph"] = not args.generate_eager
         print(json.dumps({"generate_c5": generate_measure(torch, **kw)}), flush=True)
         return
     if world == 1 and args.gpus == 1:
