@@ -141,6 +141,8 @@ typedef struct AttnRopeInsertArgs {
     uint32_t kv_sink;      /* number of sink rows to re-rotate (KV_SINK = 4 once the window is full, else 0) */
     float theta;
     int32_t q_out_dtype;   /* ATTN_DTYPE_F32 | F16 | BF16 */
+    int32_t pos_early;     /* != 0: `pos` was in place before the previous kernel of the stream was launched; the kernel
+                              then evaluates its cos/sin table while that kernel may still be running */
 } AttnRopeInsertArgs;
 
 int attn_rope_kv_insert(const AttnRopeInsertArgs* args, void* stream);
@@ -171,6 +173,11 @@ typedef struct AttnGemvArgs {
     /* != 0: W holds d gate rows followed by d up rows and out[b][j] = silu(gate_j . x) * (up_j . x), the first half of
      * the SwiGLU FFN in one launch (src/model/block.cpp:198-210). d a multiple of 16, no segments. */
     int32_t swiglu;
+    /* > 1 (Q8_0 only): the inner dimension is cut into k_split equal slices computed by separate sets of CTAs; out
+     * then receives k_split partial results [k_split][batch][d] (fp32, batch*out_batch_stride floats apart) whose sum
+     * is the product. For the FFN down projection of a batch (8 x 14336 activations do not fit in shared memory at
+     * once); attn_rmsnorm_residual adds the partials into the residual stream. */
+    uint32_t k_split;
 } AttnGemvArgs;
 
 int attn_gemv_f16(const AttnGemvArgs* args, void* stream);
@@ -196,6 +203,13 @@ int attn_embed_q8_0(float* x, const void* table, const uint32_t* tokens, uint32_
 
 /* out[b][i] = x[b][i] / sqrt(mean_i(x[b][i]^2) + eps) * weight[i]; out may be x (include/kernels_cpu.hpp:43-67). */
 int attn_rmsnorm(float* out, const float* x, const float* weight, uint32_t batch, uint32_t dim, float eps, void* stream);
+
+/* The same with the residual connection in front (src/model/block.cpp:219-222 followed by the next norm): first
+ * x[b][i] += partials[0][b][i] + partials[1][b][i] + ... (n_partials arrays [batch][dim], partial_stride floats apart,
+ * added in that order and written back to x), then out = rmsnorm(x). The partial sums are what attn_gemv_q8_0 leaves
+ * with k_split > 1. out must not be x when n_partials > 0. */
+int attn_rmsnorm_residual(float* out, float* x, const float* partials, uint32_t n_partials, uint64_t partial_stride,
+                          const float* weight, uint32_t batch, uint32_t dim, float eps, void* stream);
 
 /* hb[i] = silu(hb[i]) * hb2[i], silu(x) = x / (1 + expf(-x)), over count elements (src/model/block.cpp:206-210). */
 int attn_swiglu(float* hb, const float* hb2, uint64_t count, void* stream);

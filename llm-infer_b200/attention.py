@@ -167,7 +167,8 @@ def attn_prefill_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, ou
 
 
 def rope_kv_insert(q, k, v, k_cache, v_cache, pos, kv_pos, *, theta: float, rotary_dim: int = 0, kv_sink: int = 0,
-                   inv_freq=None, q_out=None, q_out_dtype=torch.float32, stream=None) -> torch.Tensor:
+                   inv_freq=None, q_out=None, q_out_dtype=torch.float32, pos_early: bool = False,
+                   stream=None) -> torch.Tensor:
     """Rotate the current token's q and k, insert k and v (fp16) into the caches, re-rotate the sink rows.
 
     q [B,H,D], k / v [B,Hkv,D] fp32; k_cache / v_cache fp16 [B,T,Hkv,D]; pos, kv_pos int32 CUDA tensors [B].
@@ -193,6 +194,7 @@ def rope_kv_insert(q, k, v, k_cache, v_cache, pos, kv_pos, *, theta: float, rota
     a.batch, a.n_heads, a.n_kv_heads, a.head_dim = B, H, Hkv, D
     a.rotary_dim, a.kv_sink, a.theta = rotary_dim, kv_sink, float(theta)
     a.q_out_dtype = _dtype_code(q_out)
+    a.pos_early = int(pos_early)  # pos was written before the previous kernel of the stream was launched
     with torch.cuda.device(q.device):
         _b.check(_b.load().attn_rope_kv_insert(C.byref(a), _stream_ptr(stream)), "attn_rope_kv_insert")
     return q_out
@@ -223,12 +225,14 @@ def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.floa
 
 
 def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=None, out_dtype=torch.float32,
-              clip: float = 0.0, accumulate: bool = False, swiglu: bool = False, status=None,
+              clip: float = 0.0, accumulate: bool = False, swiglu: bool = False, k_split: int = 1, status=None,
               stream=None) -> torch.Tensor:
     """out[b] = clamp(W x[b]) over Q8_0 weights: x [B, n] fp32, w uint8 [rows, n/32*34] (GGML blocks: fp16 scale + 32
     signed bytes) -> out [B, rows] fp32 or fp16. Same conventions as gemv_f16, plus:
     * ``out2`` / ``out3``: the rows are split over out, out2, out3 in that order (stacked Q, K, V projections);
-    * ``swiglu``: w holds d gate rows then d up rows, out [B, d] = silu(gate x) * (up x)."""
+    * ``swiglu``: w holds d gate rows then d up rows, out [B, d] = silu(gate x) * (up x);
+    * ``k_split`` > 1: out is [k_split, B, rows], the partial products of k_split equal slices of the inner
+      dimension (their sum is the result; ``rmsnorm(..., partials=out)`` adds them into the residual stream)."""
     _require_cuda(x, w)
     B, n = x.shape
     rows = w.shape[0]
@@ -242,19 +246,28 @@ def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=Non
     if out3 is not None and out2 is None:
         raise ValueError("out3 without out2")
     d0 = d - sum(t.shape[1] for t in segs)
-    if out is None:
-        out = torch.empty((B, d0), dtype=out_dtype, device=x.device)
-    for t in [out] + segs:
+    if k_split > 1:
+        if out is None:
+            out = torch.empty((k_split, B, d0), dtype=torch.float32, device=x.device)
+        if out.shape != (k_split, B, d0) or not out.is_contiguous() or segs:
+            raise ValueError("with k_split the output is a dense [k_split, B, rows] fp32 tensor")
+        first = out[0]
+    else:
+        if out is None:
+            out = torch.empty((B, d0), dtype=out_dtype, device=x.device)
+        first = out
+    for t in [first] + segs:
         if t.shape[0] != B or t.stride(1) != 1 or t.dtype != out.dtype:
             raise ValueError("outputs must be [B, rows] with dense rows and one dtype")
-    if out.shape[1] != d0 or d0 <= 0:
+    if first.shape[1] != d0 or d0 <= 0:
         raise ValueError("output widths do not add up to the rows of w")
     a = _b.AttnGemvArgs()
     a.out, a.x, a.w = out.data_ptr(), x.data_ptr(), w.data_ptr()
-    a.out_batch_stride = out.stride(0) if B > 1 else d0
+    a.out_batch_stride = first.stride(0) if B > 1 else d0
     a.n, a.d, a.batch, a.clip, a.out_dtype = n, d, B, float(clip), _dtype_code(out)
     a.accumulate = int(accumulate)
     a.swiglu = int(swiglu)
+    a.k_split = int(k_split)
     a.status = status.data_ptr() if status is not None else None
     if out2 is not None:
         a.out2, a.split1 = out2.data_ptr(), d0
@@ -301,17 +314,24 @@ def embed_q8_0(table: torch.Tensor, tokens: torch.Tensor, *, out=None, status=No
     return out
 
 
-def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, out=None, stream=None) -> torch.Tensor:
-    """out[b] = x[b] / sqrt(mean(x[b]^2) + eps) * weight, fp32 (include/kernels_cpu.hpp:43-67); out may be x."""
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, out=None, partials=None, stream=None) -> torch.Tensor:
+    """out[b] = x[b] / sqrt(mean(x[b]^2) + eps) * weight, fp32 (include/kernels_cpu.hpp:43-67); out may be x.
+    With ``partials`` [k, B, dim] (fp32, dense) the row is first completed, x += partials[0] + partials[1] + ...
+    (written back to x), then normalised into ``out`` (which must then be another tensor)."""
     _require_cuda(x, weight)
     B, dim = x.shape
     if x.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != dim or not x.is_contiguous():
         raise ValueError("x must be dense fp32 [B, dim] and weight fp32 [dim]")
     if out is None:
         out = torch.empty_like(x)
+    n_part, stride, pptr = 0, 0, None
+    if partials is not None:
+        if partials.dtype != torch.float32 or partials.shape[1:] != (B, dim) or not partials.is_contiguous():
+            raise ValueError("partials must be dense fp32 [k, B, dim]")
+        n_part, stride, pptr = partials.shape[0], B * dim, partials.data_ptr()
     with torch.cuda.device(x.device):
-        _b.check(_b.load().attn_rmsnorm(out.data_ptr(), x.data_ptr(), weight.data_ptr(), B, dim, float(eps),
-                                        _stream_ptr(stream)), "attn_rmsnorm")
+        _b.check(_b.load().attn_rmsnorm_residual(out.data_ptr(), x.data_ptr(), pptr, n_part, stride, weight.data_ptr(),
+                                                 B, dim, float(eps), _stream_ptr(stream)), "attn_rmsnorm")
     return out
 
 

@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "attn_embed_f16",
     "attn_embed_q8_0",
     "attn_rmsnorm",
+    "attn_rmsnorm_residual",
     "attn_swiglu",
     "attn_argmax",
     "attn_status_string",
@@ -132,6 +133,7 @@ class AttnRopeInsertArgs(C.Structure):
         ("kv_sink", C.c_uint32),
         ("theta", C.c_float),
         ("q_out_dtype", C.c_int32),
+        ("pos_early", C.c_int32),
     ]
 
 
@@ -155,6 +157,7 @@ class AttnGemvArgs(C.Structure):
         ("split1", C.c_uint32),
         ("split2", C.c_uint32),
         ("swiglu", C.c_int32),
+        ("k_split", C.c_uint32),
     ]
 
 
@@ -217,6 +220,9 @@ def load() -> C.CDLL:
     lib.attn_embed_q8_0.argtypes = lib.attn_embed_f16.argtypes
     lib.attn_rmsnorm.restype = C.c_int
     lib.attn_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p]
+    lib.attn_rmsnorm_residual.restype = C.c_int
+    lib.attn_rmsnorm_residual.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_uint32,
+                                          C.c_uint32, C.c_float, C.c_void_p]
     lib.attn_swiglu.restype = C.c_int
     lib.attn_swiglu.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.attn_argmax.restype = C.c_int

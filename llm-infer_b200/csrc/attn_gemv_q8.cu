@@ -20,7 +20,8 @@
 // buffers (one launch for the Q, K and V projections over a stacked matrix); with `swiglu` the matrix holds gate rows
 // followed by up rows and the kernel writes silu(gate x) * (up x) (one launch for the FFN's first half); and when the
 // activations of all sequences do not fit in shared memory next to the ring (batch 8 x 14336), the inner dimension is
-// staged in equal slices inside the one launch, partial sums carried in shared memory.
+// staged in equal slices inside the one launch, partial sums carried in shared memory - or, with `k_split`, the slices
+// go to separate sets of CTAs that store their partial sums for the consumer (the next RMSNorm) to add.
 //
 // Algorithmic bytes per call = rows * n/32 * 34 + batch * (n*4 + d*sizeof(out)).
 #include <cuda.h>
@@ -58,6 +59,8 @@ struct Q8Params {
     uint32_t x_col_pitch;     // 32-bit words between sequences of the staged activations
     uint32_t acc_groups;      // row groups per CTA whose partial sums are carried across slices (0 when n_slices == 1)
     uint32_t swiglu;
+    uint32_t k_split;         // > 1: the grid is k_split sets of CTAs, set s computes slice s only and stores its partial sums
+    uint64_t partial_stride;  // elements between the partial outputs of consecutive slices
     float clip;
     int32_t out_dtype;
     int32_t accumulate;
@@ -152,8 +155,12 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
     const uint32_t slice_chunks = p.slice_blocks / kChunkBlocks;
     // chunks of one slice of one row group that this warp owns: warp, warp + 8, ...
     const uint32_t cpw = (slice_chunks > warp) ? (slice_chunks - warp + kQ8Warps - 1) / kQ8Warps : 0;
-    const uint32_t my_groups = (groups > blockIdx.x) ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const uint32_t total = p.n_slices * my_groups * parts * cpw;  // items, in the order slice > group > part > chunk
+    // split-k: the grid is k_split sets of CTAs; set s handles slice s of every row group it owns
+    const uint32_t ctas = gridDim.x / p.k_split, cta = blockIdx.x % ctas;
+    const uint32_t slice_begin = p.k_split > 1 ? blockIdx.x / ctas : 0;
+    const uint32_t slice_end = p.k_split > 1 ? slice_begin + 1 : p.n_slices;
+    const uint32_t my_groups = (groups > cta) ? (groups - cta + ctas - 1) / ctas : 0;
+    const uint32_t total = (slice_end - slice_begin) * my_groups * parts * cpw;  // items: slice > group > part > chunk
 
     const uint32_t ring0 = smem_u32(smem) + warp * p.stages * kStageBytes;
     const uint32_t bar0 = smem_u32(s_bar) + warp * kMaxStages * 8;
@@ -168,8 +175,8 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
     auto issue = [&](uint32_t item) {
         const uint32_t ci = item % cpw, q = item / cpw;
         const uint32_t part = q % parts, q2 = q / parts;
-        const uint32_t gi = q2 % my_groups, slice = q2 / my_groups;
-        const uint32_t rg = blockIdx.x + gi * gridDim.x;
+        const uint32_t gi = q2 % my_groups, slice = slice_begin + q2 / my_groups;
+        const uint32_t rg = cta + gi * ctas;
         const uint32_t chunk = slice * slice_chunks + warp + ci * kQ8Warps;
         const uint32_t stage = item % p.stages;
         const uint32_t bar = bar0 + 8 * stage;
@@ -191,7 +198,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
     const uint32_t* my_x = s_x + (has_col ? g : 0) * p.x_col_pitch + t * 4;
     bool timed_out = false;
     uint32_t item = 0, round = 0;
-    for (uint32_t slice = 0; slice < p.n_slices; ++slice) {
+    for (uint32_t slice = slice_begin; slice < slice_end; ++slice) {
         // Activations of this slice as B fragments: for sequence c, block blk, k-step s, quarter t: four 32-bit words
         // {hi(x0,x1), hi(x2,x3), lo(x0,x1), lo(x2,x3)} of the elements x[32 blk + 16 s + 4 t .. +4). Every warp has
         // passed the previous slice's last block-wide barrier, so nobody still reads the old fragments.
@@ -217,7 +224,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
         __syncthreads();
 
         for (uint32_t gi = 0; gi < my_groups; ++gi, ++round) {
-            const uint32_t rg = blockIdx.x + gi * gridDim.x;
+            const uint32_t rg = cta + gi * ctas;
             float* red = s_red + (round & 1) * 2 * kQ8Warps * 128;
             for (uint32_t part = 0; part < parts; ++part) {
                 float tot[4] = {0.f, 0.f, 0.f, 0.f};
@@ -275,15 +282,15 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
                     float v = 0.f;
 #pragma unroll
                     for (int w = 0; w < kQ8Warps; ++w) v += src[w * 128];
-                    if (p.n_slices > 1) {
+                    if (slice_end - slice_begin > 1) {
                         float* carry = s_acc + (gi * 2 + part) * 128 + tid;
-                        if (slice > 0) v += *carry;
-                        if (slice + 1 < p.n_slices) *carry = v;
+                        if (slice > slice_begin) v += *carry;
+                        if (slice + 1 < slice_end) *carry = v;
                     }
                     y[part] = v;
                 }
                 const uint32_t row = rg * kRows + (tid >> 3), c = tid & 7;
-                if (slice + 1 == p.n_slices && row < p.d && c < p.batch) {
+                if (slice + 1 == slice_end && row < p.d && c < p.batch) {
                     float v = y[0];
                     if (p.swiglu) v = __fdiv_rn(v, 1.0f + expf(-v)) * y[1];  // silu(gate) * up, src/model/block.cpp:206-210
                     if (p.clip > 0.f) v = fminf(fmaxf(v, -p.clip), p.clip);
@@ -295,7 +302,8 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
                     } else if (row >= p.seg_end0) {
                         out = p.out1, stride = p.out_stride1, r0 = p.seg_end0;
                     }
-                    const size_t o = static_cast<size_t>(c) * stride + (row - r0);
+                    const size_t o = static_cast<size_t>(c) * stride + (row - r0) +
+                                     (p.k_split > 1 ? slice_begin * p.partial_stride : 0);
                     if (p.out_dtype == ATTN_DTYPE_F32) {
                         float* dst = reinterpret_cast<float*>(out) + o;
                         *dst = p.accumulate ? *dst + v : v;
@@ -338,6 +346,9 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     if (a->n % (32 * kChunkBlocks) != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
     if (a->accumulate && a->out_dtype != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;
     if (a->swiglu && (a->d % kRows != 0 || a->split1 || a->split2)) return ATTN_ERR_UNSUPPORTED;
+    const uint32_t k_split = a->k_split > 1 ? a->k_split : 1;
+    if (k_split > 1 && (a->swiglu || a->split1 || a->accumulate || a->clip > 0.f || a->out_dtype != ATTN_DTYPE_F32))
+        return ATTN_ERR_UNSUPPORTED;
     if ((a->split1 && (!a->out2 || a->split1 >= a->d)) || (a->split2 && (!a->out3 || a->split2 <= a->split1 || a->split2 >= a->d)))
         return ATTN_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(a->x) & 15u) || (reinterpret_cast<uintptr_t>(a->w) & 15u)) return ATTN_ERR_ALIGNMENT;
@@ -346,19 +357,25 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     if (rc != ATTN_OK) return rc;
     const uint32_t n_blocks = a->n / 32, n_chunks = n_blocks / kChunkBlocks;
     const uint32_t groups = (a->d + kRows - 1) / kRows;
-    const uint32_t grid = groups < static_cast<uint32_t>(dev.sm_count) ? groups : static_cast<uint32_t>(dev.sm_count);
-    const uint32_t groups_per_cta = (groups + grid - 1) / grid;
+    const uint32_t set_max = static_cast<uint32_t>(dev.sm_count) / k_split;  // CTAs per k-slice set
+    if (set_max == 0) return ATTN_ERR_UNSUPPORTED;
+    const uint32_t set_ctas = groups < set_max ? groups : set_max;
+    const uint32_t grid = set_ctas * k_split;
+    const uint32_t groups_per_cta = (groups + set_ctas - 1) / set_ctas;
     const size_t budget = static_cast<size_t>(dev.max_smem_optin);
     // staged activations: 128 bytes per block and sequence, sequences 64 bytes apart modulo 128 (bank spread)
     auto x_bytes = [&](uint32_t blocks) { return static_cast<size_t>(a->batch) * (blocks * 128 + 64); };
     auto fixed_bytes = [&](uint32_t slices) {
-        return 2 * 2 * kQ8Warps * 128 * sizeof(float) + (slices > 1 ? groups_per_cta * 2 * 128 * sizeof(float) : 0) +
+        return 2 * 2 * kQ8Warps * 128 * sizeof(float) + ((slices > 1 && k_split == 1) ? groups_per_cta * 2 * 128 * sizeof(float) : 0) +
                kQ8Warps * kMaxStages * sizeof(uint64_t) + 128;
     };
     // The activations are staged in equal slices of the inner dimension, as few as leave room for a two-stage ring; the
     // partial sums of the CTA's row groups are carried from slice to slice in shared memory.
-    uint32_t slices = 1;
-    while (slices <= n_chunks &&
+    uint32_t slices = k_split;
+    if (k_split > 1 && (n_chunks % k_split != 0 ||
+                        fixed_bytes(1) + 2 * kQ8Warps * kStageBytes + x_bytes(n_blocks / k_split) > budget))
+        return ATTN_ERR_UNSUPPORTED;  // the slices must be equal and one must fit next to a two-stage ring
+    while (k_split == 1 && slices <= n_chunks &&
            (n_chunks % slices != 0 || fixed_bytes(slices) + 2 * kQ8Warps * kStageBytes + x_bytes(n_blocks / slices) > budget))
         ++slices;
     if (slices > n_chunks) return ATTN_ERR_UNSUPPORTED;
@@ -404,7 +421,9 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     p.batch = a->batch;
     p.stages = stages;
     p.x_col_pitch = slice_blocks * 32 + 16;
-    p.acc_groups = slices > 1 ? groups_per_cta : 0;
+    p.acc_groups = (slices > 1 && k_split == 1) ? groups_per_cta : 0;
+    p.k_split = k_split;
+    p.partial_stride = static_cast<uint64_t>(a->batch) * stride0;
     p.swiglu = a->swiglu ? 1u : 0u;
     p.clip = a->clip;
     p.out_dtype = a->out_dtype;

@@ -18,19 +18,6 @@ namespace {
 
 constexpr int kOpsThreads = 256;
 
-__device__ __forceinline__ float block_sum(float v, float* s_red) {
-#pragma unroll
-    for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) s_red[warp] = v;
-    __syncthreads();
-    float t = 0.f;
-    // fixed order over the warps: the result does not depend on scheduling
-    for (int w = 0; w < kOpsThreads / 32; ++w) t += s_red[w];
-    __syncthreads();
-    return t;
-}
-
 __global__ void __launch_bounds__(kOpsThreads) embed_kernel(float* x, const __half* table, const uint32_t* tokens,
                                                             uint32_t dim, uint32_t vocab, uint32_t* status) {
     grid_dep_launch_dependents();
@@ -64,20 +51,92 @@ __global__ void __launch_bounds__(kOpsThreads) embed_q8_kernel(float* x, const u
     }
 }
 
-__global__ void __launch_bounds__(kOpsThreads) rmsnorm_kernel(float* out, const float* x, const float* weight,
-                                                              uint32_t dim, float eps) {
-    __shared__ float s_red[kOpsThreads / 32];
+// One CTA of 1024 threads per sequence; each thread keeps its (up to two) float4 of the row in registers, so the row
+// is read once. Optionally the row is first completed with partial sums that a split-k GEMV left behind
+// (x += part[0] + part[1] + ..., added in that order, the residual connection of src/model/block.cpp:219-222) and
+// written back. Rows longer than 8192 or not a multiple of 4 take the plain two-pass form.
+constexpr int kNormThreads = 1024;
+
+struct NormParams {
+    float* out;
+    const float* x;
+    float* x_store;         // where the completed row goes (partials only); may be x
+    const float* partials;  // [n_partials][batch][dim] or null
+    const float* weight;
+    uint64_t partial_stride;
+    uint32_t n_partials, dim;
+    float eps;
+};
+
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const __grid_constant__ NormParams p) {
+    __shared__ float s_red[kNormThreads / 32];
     grid_dep_launch_dependents();
     grid_dep_wait();
-    const size_t base = static_cast<size_t>(blockIdx.x) * dim;
+    const size_t base = static_cast<size_t>(blockIdx.x) * p.dim;
+    const uint32_t tid = threadIdx.x;
+    const bool fast = (p.dim % 4 == 0) && p.dim <= 2 * 4 * kNormThreads;
+    float4 v[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+    float4 wv[2] = {v[0], v[0]};  // the norm weights do not wait for the reduction: fetched with the row
     float ss = 0.f;
-    for (uint32_t i = threadIdx.x; i < dim; i += kOpsThreads) {
-        const float v = x[base + i];
-        ss = fmaf(v, v, ss);
+    auto row_value = [&](size_t i) {
+        float r = p.x[i];
+        for (uint32_t s = 0; s < p.n_partials; ++s) r += p.partials[s * p.partial_stride + i];
+        return r;
+    };
+    if (fast) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t i = (tid + j * kNormThreads) * 4;
+            if (i < p.dim) {
+                v[j] = *reinterpret_cast<const float4*>(p.x + base + i);
+                wv[j] = *reinterpret_cast<const float4*>(p.weight + i);
+                for (uint32_t s = 0; s < p.n_partials; ++s) {
+                    const float4 a = *reinterpret_cast<const float4*>(p.partials + s * p.partial_stride + base + i);
+                    v[j].x += a.x, v[j].y += a.y, v[j].z += a.z, v[j].w += a.w;
+                }
+                if (p.n_partials) *reinterpret_cast<float4*>(p.x_store + base + i) = v[j];
+                ss = fmaf(v[j].x, v[j].x, ss);
+                ss = fmaf(v[j].y, v[j].y, ss);
+                ss = fmaf(v[j].z, v[j].z, ss);
+                ss = fmaf(v[j].w, v[j].w, ss);
+            }
+        }
+    } else {
+        for (uint32_t i = tid; i < p.dim; i += kNormThreads) {
+            const float r = row_value(base + i);
+            ss = fmaf(r, r, ss);
+        }
     }
-    ss = block_sum(ss, s_red);
-    const float rms = sqrtf(ss / static_cast<float>(dim) + eps);
-    for (uint32_t i = threadIdx.x; i < dim; i += kOpsThreads) out[base + i] = __fdiv_rn(x[base + i], rms) * weight[i];
+    // block sum in a fixed order: lanes by shuffle, then the 32 warps' sums one after the other
+#pragma unroll
+    for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if ((tid & 31) == 0) s_red[tid >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kNormThreads / 32; ++w) total += s_red[w];
+    const float rms = sqrtf(total / static_cast<float>(p.dim) + p.eps);
+    if (fast) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t i = (tid + j * kNormThreads) * 4;
+            if (i < p.dim) {
+                const float4 w = wv[j];
+                float4 o;
+                o.x = __fdiv_rn(v[j].x, rms) * w.x;
+                o.y = __fdiv_rn(v[j].y, rms) * w.y;
+                o.z = __fdiv_rn(v[j].z, rms) * w.z;
+                o.w = __fdiv_rn(v[j].w, rms) * w.w;
+                *reinterpret_cast<float4*>(p.out + base + i) = o;
+            }
+        }
+    } else {
+        for (uint32_t i = tid; i < p.dim; i += kNormThreads) {
+            const float r = row_value(base + i);
+            if (p.n_partials) p.x_store[base + i] = r;
+            p.out[base + i] = __fdiv_rn(r, rms) * p.weight[i];
+        }
+    }
 }
 
 __global__ void __launch_bounds__(kOpsThreads) swiglu_kernel(float* hb, const float* hb2, size_t count) {
@@ -161,13 +220,33 @@ extern "C" int attn_embed_q8_0(float* x, const void* table, const uint32_t* toke
     return ATTN_OK;
 }
 
-extern "C" int attn_rmsnorm(float* out, const float* x, const float* weight, uint32_t batch, uint32_t dim, float eps,
-                            void* stream) {
-    if (!out || !x || !weight || batch == 0 || dim == 0) return ATTN_ERR_INVALID_ARG;
-    B200_CUDA_TRY(launch_dependent(rmsnorm_kernel, dim3(batch), dim3(kOpsThreads), 0, static_cast<cudaStream_t>(stream), out, x,
-                                   weight, dim, eps));
+extern "C" int attn_rmsnorm_residual(float* out, float* x, const float* partials, uint32_t n_partials,
+                                     uint64_t partial_stride, const float* weight, uint32_t batch, uint32_t dim, float eps,
+                                     void* stream) {
+    if (!out || !x || !weight || batch == 0 || dim == 0 || (n_partials && !partials)) return ATTN_ERR_INVALID_ARG;
+    if (n_partials && out == x) return ATTN_ERR_INVALID_ARG;  // the completed row and its norm are both kept
+    if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
+         reinterpret_cast<uintptr_t>(partials)) & 15u)
+        return ATTN_ERR_ALIGNMENT;
+    if (n_partials && partial_stride % 4 != 0) return ATTN_ERR_ALIGNMENT;
+    NormParams p{};
+    p.out = out;
+    p.x = x;
+    p.x_store = x;
+    p.partials = partials;
+    p.weight = weight;
+    p.partial_stride = partial_stride;
+    p.n_partials = n_partials;
+    p.dim = dim;
+    p.eps = eps;
+    B200_CUDA_TRY(launch_dependent(rmsnorm_kernel, dim3(batch), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream), p));
     count_launch();
     return ATTN_OK;
+}
+
+extern "C" int attn_rmsnorm(float* out, const float* x, const float* weight, uint32_t batch, uint32_t dim, float eps,
+                            void* stream) {
+    return attn_rmsnorm_residual(out, const_cast<float*>(x), nullptr, 0, 0, weight, batch, dim, eps, stream);
 }
 
 extern "C" int attn_swiglu(float* hb, const float* hb2, uint64_t count, void* stream) {

@@ -34,13 +34,19 @@ struct RopeParams {
     uint32_t batch, n_heads, n_kv_heads, head_dim, rotary_dim, kv_sink;
     float theta;
     int32_t q_out_dtype;
+    int32_t pos_early;
 };
 
-constexpr int kRopeThreads = 256;
+constexpr int kRopeThreads = 1024;
 
 // grid = (batch); each CTA handles one sequence's token: table of cos/sin, then all pairs.
 __global__ void __launch_bounds__(kRopeThreads) rope_kv_insert_kernel(const __grid_constant__ RopeParams p) {
     extern __shared__ float s_tab[];  // [2][rotary_dim/2] cos, sin at `pos`; then [2][rotary_dim/2] at position 1
+    // The cos / sin table depends only on the token's position. When the caller states that the positions were in
+    // place before the previous kernel of the stream was launched (pos_early), the table is computed while that kernel
+    // (the Q/K/V projection) may still be running, and only q, k, v and the caches are read after the wait.
+    grid_dep_launch_dependents();
+    if (!p.pos_early) grid_dep_wait();
     const uint32_t b = blockIdx.x;
     const uint32_t half = p.rotary_dim / 2;
     const uint32_t pos = p.pos[b];
@@ -60,6 +66,7 @@ __global__ void __launch_bounds__(kRopeThreads) rope_kv_insert_kernel(const __gr
         s_tab[2 * half + i] = static_cast<float>(cos(static_cast<double>(deg1)));
         s_tab[3 * half + i] = static_cast<float>(sin(static_cast<double>(deg1)));
     }
+    if (p.pos_early) grid_dep_wait();
     __syncthreads();
 
     const uint32_t D = p.head_dim, hp = D / 2;
@@ -154,8 +161,9 @@ extern "C" int attn_rope_kv_insert(const AttnRopeInsertArgs* a, void* stream_v) 
     p.theta = a->theta;
     p.q_out_dtype = a->q_out_dtype;
     const size_t smem = static_cast<size_t>(p.rotary_dim) * 2 * sizeof(float);
-    rope_kv_insert_kernel<<<a->batch, kRopeThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(p);
-    B200_CUDA_TRY(cudaGetLastError());
+    p.pos_early = a->pos_early;
+    B200_CUDA_TRY(launch_dependent(rope_kv_insert_kernel, dim3(a->batch), dim3(kRopeThreads), smem,
+                                   static_cast<cudaStream_t>(stream_v), p));
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return ATTN_OK;
 }

@@ -133,6 +133,18 @@ class Llama:
         self.v_cache = torch.zeros_like(self.k_cache)
         self.workspace = A.DecodeWorkspace(B, c.n_heads, c.n_kv_heads, c.head_dim, dev)
         self._q_dim, self._kv_dim = q_dim, kv_dim
+        # The Q8_0 down projection of a batch: when the hidden activations of all sequences do not fit in shared memory
+        # next to the weight ring, the inner dimension is split over sets of CTAs and the next RMSNorm adds the
+        # partial products into x (same sum, fixed order).
+        self._k_split = 1
+        if q8:
+            chunks = c.hidden_dim // 256
+            need = B * (c.hidden_dim * 4 + 64)
+            k = max(1, -(-need // (140 * 1024)))
+            while k <= chunks and chunks % k:
+                k += 1
+            self._k_split = k if k <= chunks else 1
+        self.partials = z(self._k_split, B, c.dim) if self._k_split > 1 else None
 
     @classmethod
     def from_gguf(cls, path: str, batch: int, device=None) -> "Llama":
@@ -142,7 +154,7 @@ class Llama:
 
         from . import gguf
         cfg, w, weight_type = gguf.read_gguf(path)
-        weights = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in w.items()}
+        weights = {k: torch.from_numpy(np.array(v)) for k, v in w.items()}  # copies out of the read-only map
         return cls(cfg, weights, batch, device, weight_type=weight_type)
 
     # -- positions: sliding-window arithmetic of src/model/model.cpp:66-68, per sequence --
@@ -169,8 +181,10 @@ class Llama:
         self._embed(w["embed"], self.tokens, out=self.x, status=self.status)
         att_flat = self.att.view(B, self._q_dim)
         q8 = self.weight_type == "q8_0"
+        pending = None  # partial products of the previous layer's down projection, still to be added into x
         for l in range(c.n_layers):
-            A.rmsnorm(self.x, w["rms_att"][l], c.norm_eps, out=self.xb)
+            A.rmsnorm(self.x, w["rms_att"][l], c.norm_eps, out=self.xb, partials=pending)
+            pending = None
             if q8:
                 gemv(self.xb, w["wqkv"][l], out=self.q.view(B, self._q_dim), out2=self.k.view(B, self._kv_dim),
                      out3=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
@@ -179,7 +193,8 @@ class Llama:
                 gemv(self.xb, w["wk"][l], out=self.k.view(B, self._kv_dim), clip=c.qkv_clip)
                 gemv(self.xb, w["wv"][l], out=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
             A.rope_kv_insert(self.q, self.k, self.v, self.k_cache[l], self.v_cache[l], self.pos, self.kv_pos,
-                             theta=c.rope_theta, rotary_dim=c.rotary_dim, kv_sink=kv_sink, q_out=self.q)
+                             theta=c.rope_theta, rotary_dim=c.rotary_dim, kv_sink=kv_sink, q_out=self.q,
+                             pos_early=True)   # positions are copied in before the step's first kernel
             A.attn_decode(self.q, self.k_cache[l], self.v_cache[l], self.kv_len, out=self.att,
                           workspace=self.workspace)
             gemv(att_flat, w["wo"][l], out=self.x, accumulate=True)       # x += Wo att
@@ -190,11 +205,15 @@ class Llama:
                 gemv(self.xb, w["w1"][l], out=self.hb)
                 gemv(self.xb, w["w3"][l], out=self.hb2)
                 A.swiglu_(self.hb, self.hb2)
-            gemv(self.hb, w["w2"][l], out=self.x, accumulate=True)        # x += W2 (silu(W1 xb) * W3 xb)
+            if self._k_split > 1:
+                gemv(self.hb, w["w2"][l], out=self.partials, k_split=self._k_split)
+                pending = self.partials                                    # x += W2 hb, added by the next norm
+            else:
+                gemv(self.hb, w["w2"][l], out=self.x, accumulate=True)    # x += W2 (silu(W1 xb) * W3 xb)
         if not want_logits:
-            return  # prefill mode: no final norm, no classifier (src/model/model.cpp:74-76)
-        A.rmsnorm(self.x, w["rms_final"], c.norm_eps, out=self.x)
-        gemv(self.x, w["wcls"], out=self.logits)
+            return  # prefill mode: no final norm, no classifier (src/model/model.cpp:74-76); x is not read again
+        A.rmsnorm(self.x, w["rms_final"], c.norm_eps, out=self.xb, partials=pending)
+        gemv(self.xb, w["wcls"], out=self.logits)
         A.argmax(self.logits, out=self.next_token)
         self.tokens.copy_(self.next_token)
 

@@ -184,3 +184,33 @@ def test_q8_0_stacked_qkv_and_swiglu_epilogue(attention, port, pkg):
     for b in range(B):
         want = port.swiglu(port.matmul_q8_0(x[b], w1), port.matmul_q8_0(x[b], w3))
         assert np.abs(got[b] - want).max() <= 2e-5 * np.abs(want).max() + 1e-6
+
+
+def test_q8_0_split_k_partials_and_residual_norm(attention, port, pkg):
+    """k_split sets of CTAs each compute one slice of the inner dimension; the partial products sum to the product, and
+    attn_rmsnorm_residual adds them into x before normalising."""
+    import torch
+    from llm_infer_b200 import quant
+    rng = np.random.default_rng(99)
+    n, d, B, K = 14336, 1024, 8, 4
+    x = rng.standard_normal((B, n), dtype=np.float32)
+    blocks = quant.quantize_q8_0(rng.standard_normal((d, n), dtype=np.float32) * 0.02)
+    parts = attention.gemv_q8_0(torch.from_numpy(x).cuda(), torch.from_numpy(blocks).cuda(), k_split=K)
+    assert parts.shape == (K, B, d)
+    got = parts.sum(0).cpu().numpy()
+    mag = np.abs(x) @ np.abs(quant.dequantize_q8_0(blocks)).T
+    want = np.stack([port.matmul_q8_0(x[b], blocks) for b in range(B)])
+    assert (np.abs(got - want) <= 4e-6 * mag + 1e-7).all()
+    assert (parts[0].abs().sum() > 0) and (parts[K - 1].abs().sum() > 0)
+    # residual + norm
+    resid = rng.standard_normal((B, d), dtype=np.float32)
+    wt = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    xg = torch.from_numpy(resid.copy()).cuda()
+    normed = attention.rmsnorm(xg, torch.from_numpy(wt).cuda(), 1e-5, out=torch.empty_like(xg), partials=parts)
+    full = resid.copy()
+    for s_ in range(K):
+        full += parts[s_].cpu().numpy()
+    assert np.array_equal(xg.cpu().numpy(), full)  # same order of additions: bit-equal
+    for b in range(B):
+        ref = port.rmsnorm(full[b], wt, 1e-5)
+        assert np.abs(normed[b].cpu().numpy() - ref).max() <= 4e-6 * np.abs(ref).max()

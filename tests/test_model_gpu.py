@@ -77,6 +77,18 @@ def test_q8_0_model_token_equality(M, port):
     _run_case(M, port, cfg, prompts, n_new=12, seed=6, graph=True, weight_type="q8_0")
 
 
+def test_q8_0_model_with_split_k_down_projection(M, port):
+    """Batch 8 with an FFN wide enough (8 x 8192 activations) that the down projection runs split over the inner
+    dimension and the next RMSNorm adds the partial products into the residual stream."""
+    cfg = M.ModelConfig(dim=512, hidden_dim=8192, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=128, vocab_size=400,
+                        max_seq_len=32, norm_eps=1e-5, rope_theta=10000.0)
+    rng = np.random.default_rng(41)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (3, 8, 5, 1, 2, 6, 4, 7)]
+    w = M.random_weights(cfg, 8, weight_type="q8_0")
+    assert M.Llama(cfg, w, batch=8, weight_type="q8_0")._k_split == 2
+    _run_case(M, port, cfg, prompts, n_new=8, seed=8, graph=True, weight_type="q8_0")
+
+
 @pytest.mark.parametrize("weight_type", ["f16", "q8_0"])
 def test_model_file_round_trip_generates_the_same_tokens(M, tmp_path, weight_type):
     """Seed-generated weights written as a GGUF file, loaded back, same greedy output as the in-memory model."""
