@@ -21,12 +21,9 @@ int launch_one(const DecodeParams& p, uint32_t grid, size_t smem_bytes, cudaStre
     auto kernel = decode_split_kernel<D, HPC, QSPLIT, BF16, FUSED>;
     B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem_bytes)));
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = stream;
-    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
+    // launched as a programmatic dependent: the launch overlaps the previous kernel's tail; the kernel waits for that
+    // kernel before it reads anything
+    B200_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(kThreads), smem_bytes, stream, p));
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return ATTN_OK;
 }

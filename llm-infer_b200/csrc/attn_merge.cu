@@ -36,7 +36,9 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
     const int lane = tid & 31;
     const int warp = tid >> 5;
     const uint32_t row = blockIdx.x;
-    // Wait for the grid that produced the partials (no-op without a programmatic dependency).
+    // Let the next kernel of the stream be scheduled (a weight GEMV starts prefetching), then wait for the grid that
+    // produced the partials (no-op without a programmatic dependency).
+    grid_dep_launch_dependents();
     grid_dep_wait();
 
     const float* po;

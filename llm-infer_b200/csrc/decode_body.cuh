@@ -115,8 +115,10 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     const uint32_t tiles_u32 = smem_u32(tiles);
 
     // The merge pass may be scheduled as soon as every CTA got here; it waits for
-    // this grid to finish before reading the partials.
+    // this grid to finish before reading the partials. This grid in turn waits for
+    // the kernel before it (which wrote q and the newest cache row) before reading.
     grid_dep_launch_dependents();
+    grid_dep_wait();
 
     if (tid == 0) {
         for (uint32_t s = 0; s < nst; ++s) {
