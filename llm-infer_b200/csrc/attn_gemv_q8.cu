@@ -36,12 +36,13 @@ namespace {
 constexpr int kQ8Warps = 8;
 constexpr int kQ8Threads = kQ8Warps * 32;
 constexpr uint32_t kBlockBytes = 34;                        // fp16 scale + 32 int8
-constexpr uint32_t kChunkBlocks = 8;                        // blocks of one row per stage
-constexpr uint32_t kSegBytes = kChunkBlocks * kBlockBytes;  // 272: one row's share of a stage (multiple of 16)
-constexpr uint32_t kSegPitch = kSegBytes;                   // 68 words = 4 mod 32: the 8 rows x 4 lanes of one load hit 32 banks
+// Blocks of one row per stage (CB): 8 (272-byte row segments, up to four stages per warp) or 16 (544-byte segments,
+// two stages: ~10 % faster streaming, used when the activations leave room). A row segment is 68 or 136 words long
+// (4 or 8 mod 32), so the 8 rows x 4 lanes of one shared-memory load never share a bank.
 constexpr uint32_t kRows = 16;                              // rows of a group = M of the MMA
-constexpr uint32_t kStageBytes = kRows * kSegPitch;         // 4352 = 34 x 128
-constexpr uint32_t kMaxStages = 4;
+constexpr uint32_t kMaxStages = 4;                          // barrier slots per warp
+constexpr uint32_t seg_bytes(uint32_t cb) { return cb * kBlockBytes; }          // one row's share of a stage
+constexpr uint32_t stage_bytes(uint32_t cb) { return kRows * seg_bytes(cb); }   // 4352 or 8704, multiples of 128
 
 struct Q8Params {
     void* out0;               // rows [0, seg_end0)
@@ -52,7 +53,7 @@ struct Q8Params {
     uint32_t* status;
     uint64_t x_batch_stride;  // elements between sequences of x
     uint32_t seg_end0, seg_end1;
-    uint32_t slice_blocks;    // blocks of the inner dimension staged at a time (multiple of kChunkBlocks)
+    uint32_t slice_blocks;    // blocks of the inner dimension staged at a time (multiple of the chunk)
     uint32_t n_slices;        // slice_blocks * n_slices = blocks per row
     uint32_t d, batch;        // output rows; with swiglu W has 2 d rows: gate rows, then up rows
     uint32_t stages;
@@ -136,8 +137,10 @@ __device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* m
         : "memory");
 }
 
+template <uint32_t CB>
 __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                   const __grid_constant__ Q8Params p) {
+    constexpr uint32_t kChunkBlocks = CB, kSegBytes = seg_bytes(CB), kSegPitch = kSegBytes, kStageBytes = stage_bytes(CB);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // tile loads want 128-byte alignment
     // layout: [ring: warps x stages x kStageBytes][red: 2 x 2 x warps x 128 floats][acc: acc_groups x 2 x 128 floats]
@@ -343,7 +346,7 @@ using namespace b200;
 extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     if (!a || !a->out || !a->x || !a->w || a->n == 0 || a->d == 0 || a->batch == 0) return ATTN_ERR_INVALID_ARG;
     if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16) return ATTN_ERR_INVALID_ARG;
-    if (a->n % (32 * kChunkBlocks) != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
+    if (a->n % 256 != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
     if (a->accumulate && a->out_dtype != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;
     if (a->swiglu && (a->d % kRows != 0 || a->split1 || a->split2)) return ATTN_ERR_UNSUPPORTED;
     const uint32_t k_split = a->k_split > 1 ? a->k_split : 1;
@@ -355,7 +358,7 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     DeviceInfo dev{};
     int rc = current_device_info(&dev);
     if (rc != ATTN_OK) return rc;
-    const uint32_t n_blocks = a->n / 32, n_chunks = n_blocks / kChunkBlocks;
+    const uint32_t n_blocks = a->n / 32;
     const uint32_t groups = (a->d + kRows - 1) / kRows;
     const uint32_t set_max = static_cast<uint32_t>(dev.sm_count) / k_split;  // CTAs per k-slice set
     if (set_max == 0) return ATTN_ERR_UNSUPPORTED;
@@ -370,19 +373,36 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
                kQ8Warps * kMaxStages * sizeof(uint64_t) + 128;
     };
     // The activations are staged in equal slices of the inner dimension, as few as leave room for a two-stage ring; the
-    // partial sums of the CTA's row groups are carried from slice to slice in shared memory.
-    uint32_t slices = k_split;
-    if (k_split > 1 && (n_chunks % k_split != 0 ||
-                        fixed_bytes(1) + 2 * kQ8Warps * kStageBytes + x_bytes(n_blocks / k_split) > budget))
-        return ATTN_ERR_UNSUPPORTED;  // the slices must be equal and one must fit next to a two-stage ring
-    while (k_split == 1 && slices <= n_chunks &&
-           (n_chunks % slices != 0 || fixed_bytes(slices) + 2 * kQ8Warps * kStageBytes + x_bytes(n_blocks / slices) > budget))
-        ++slices;
-    if (slices > n_chunks) return ATTN_ERR_UNSUPPORTED;
-    const uint32_t slice_blocks = n_blocks / slices;
-    uint32_t stages = kMaxStages;
-    while (stages > 2 && fixed_bytes(slices) + stages * kQ8Warps * kStageBytes + x_bytes(slice_blocks) > budget) --stages;
-    const size_t smem = fixed_bytes(slices) + static_cast<size_t>(stages) * kQ8Warps * kStageBytes + x_bytes(slice_blocks);
+    // partial sums of the CTA's row groups are carried from slice to slice in shared memory (or, with k_split, the
+    // slices go to separate sets of CTAs). 16-block chunks are used when everything fits in one slice with them.
+    struct Plan {
+        uint32_t cb, slices, stages;
+        size_t smem;
+    };
+    auto make_plan = [&](uint32_t cb, Plan* out) {
+        if (n_blocks % cb != 0) return false;
+        const uint32_t n_chunks = n_blocks / cb;
+        const size_t ring2 = 2 * static_cast<size_t>(kQ8Warps) * stage_bytes(cb);
+        uint32_t slices = k_split;
+        if (k_split > 1) {
+            if (n_chunks % k_split != 0 || fixed_bytes(1) + ring2 + x_bytes(n_blocks / k_split) > budget) return false;
+        } else {
+            while (slices <= n_chunks && (n_chunks % slices != 0 || fixed_bytes(slices) + ring2 + x_bytes(n_blocks / slices) > budget))
+                ++slices;
+            if (slices > n_chunks) return false;
+        }
+        uint32_t stages = cb == 8 ? 4 : 2;
+        while (stages > 2 && fixed_bytes(slices) + stages * kQ8Warps * stage_bytes(cb) + x_bytes(n_blocks / slices) > budget) --stages;
+        *out = Plan{cb, slices, stages,
+                    fixed_bytes(slices) + static_cast<size_t>(stages) * kQ8Warps * stage_bytes(cb) + x_bytes(n_blocks / slices)};
+        return true;
+    };
+    Plan plan{};
+    Plan wide{};
+    if (!make_plan(8, &plan)) return ATTN_ERR_UNSUPPORTED;  // (the slices must be equal and one must fit next to the ring)
+    if (k_split == 1 && make_plan(16, &wide) && wide.slices == 1) plan = wide;
+    const uint32_t slices = plan.slices, stages = plan.stages, slice_blocks = n_blocks / slices;
+    const size_t smem = plan.smem;
 
     // W as a 2-D tensor of 32-bit elements [rows][row_bytes / 4]; one box = 16 rows x 272 bytes, no swizzle.
     EncodeTiledFn enc = encode_tiled_fn();
@@ -392,7 +412,7 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
         const cuuint64_t row_bytes = static_cast<cuuint64_t>(n_blocks) * kBlockBytes;
         const cuuint64_t dims[2] = {row_bytes / 4, static_cast<cuuint64_t>(a->d) * (a->swiglu ? 2 : 1)};
         const cuuint64_t strides[1] = {row_bytes};
-        const cuuint32_t box[2] = {kSegBytes / 4, kRows};
+        const cuuint32_t box[2] = {seg_bytes(plan.cb) / 4, kRows};
         const cuuint32_t estr[2] = {1, 1};
         CUresult r = enc(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a->w), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -429,8 +449,9 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     p.out_dtype = a->out_dtype;
     p.accumulate = a->accumulate;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    B200_CUDA_TRY(cudaFuncSetAttribute(gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    B200_CUDA_TRY(launch_dependent(gemv_q8_0_kernel, dim3(grid), dim3(kQ8Threads), smem, stream, tm_w, p));
+    auto kernel = plan.cb == 16 ? gemv_q8_0_kernel<16> : gemv_q8_0_kernel<8>;
+    B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    B200_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(kQ8Threads), smem, stream, tm_w, p));
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return ATTN_OK;
 }
