@@ -297,6 +297,11 @@ int attn_last_cuda_error(void);
 /* Number of kernels this library has launched from this process (for accounting in benchmarks). */
 uint64_t attn_kernel_launch_count(void);
 
+/* sizeof() of an argument structure as this library was compiled, so that a foreign-function binding can check its own
+ * mirror of the layout: 0 AttnDecodeArgs, 1 AttnDecodeShardedArgs, 2 AttnPrefillArgs, 3 AttnRopeInsertArgs,
+ * 4 AttnGemvArgs, 5 AttnMergeArgs; 0 for any other index. */
+size_t attn_abi_struct_size(int which);
+
 #ifdef __cplusplus
 }
 #endif

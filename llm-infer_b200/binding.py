@@ -39,6 +39,7 @@ EXPORTED_SYMBOLS = (
     "attn_status_string",
     "attn_last_cuda_error",
     "attn_kernel_launch_count",
+    "attn_abi_struct_size",
 )
 # include/kernels_b200.cuh
 SYMBOL_HELPERS = (
@@ -235,6 +236,13 @@ def load() -> C.CDLL:
     lib.attn_status_string.argtypes = [C.c_int]
     lib.attn_last_cuda_error.restype = C.c_int
     lib.attn_kernel_launch_count.restype = C.c_uint64
+    lib.attn_abi_struct_size.restype = C.c_size_t
+    lib.attn_abi_struct_size.argtypes = [C.c_int]
+    mirrors = (AttnDecodeArgs, AttnDecodeShardedArgs, AttnPrefillArgs, AttnRopeInsertArgs, AttnGemvArgs, AttnMergeArgs)
+    for index, mirror in enumerate(mirrors):
+        if lib.attn_abi_struct_size(index) != C.sizeof(mirror):
+            raise RuntimeError(f"{mirror.__name__}: the ctypes mirror ({C.sizeof(mirror)} bytes) does not match the "
+                               f"library ({lib.attn_abi_struct_size(index)} bytes)")
     # include/kernels_b200.cuh: the engine's kernel symbol and its helpers
     lib.attention_workspace_bytes.restype = C.c_size_t
     lib.attention_workspace_bytes.argtypes = [C.c_uint32] * 3

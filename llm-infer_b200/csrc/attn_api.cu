@@ -242,4 +242,16 @@ int attn_last_cuda_error(void) { return g_last_cuda_error; }
 
 uint64_t attn_kernel_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
 
+size_t attn_abi_struct_size(int which) {
+    switch (which) {
+        case 0: return sizeof(AttnDecodeArgs);
+        case 1: return sizeof(AttnDecodeShardedArgs);
+        case 2: return sizeof(AttnPrefillArgs);
+        case 3: return sizeof(AttnRopeInsertArgs);
+        case 4: return sizeof(AttnGemvArgs);
+        case 5: return sizeof(AttnMergeArgs);
+        default: return 0;
+    }
+}
+
 }  // extern "C"

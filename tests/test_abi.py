@@ -82,3 +82,12 @@ def test_work_split_arithmetic_matches_between_passes():
         for t in range(nt):
             c = ((t + 1) * a - 1) // nt
             assert starts[c] <= t < starts[c + 1], (nt, a, t, c)
+
+
+def test_ctypes_mirrors_have_the_library_struct_sizes(built_lib, pkg):
+    b = pkg.binding
+    mirrors = (b.AttnDecodeArgs, b.AttnDecodeShardedArgs, b.AttnPrefillArgs, b.AttnRopeInsertArgs, b.AttnGemvArgs,
+               b.AttnMergeArgs)
+    for index, mirror in enumerate(mirrors):
+        assert built_lib.attn_abi_struct_size(index) == C.sizeof(mirror), mirror.__name__
+    assert built_lib.attn_abi_struct_size(99) == 0
