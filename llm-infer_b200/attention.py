@@ -200,6 +200,62 @@ def rope_kv_insert(q, k, v, k_cache, v_cache, pos, kv_pos, *, theta: float, rota
     return q_out
 
 
+class HostDecodeStep:
+    """One decode step of the attention block driven from host buffers, as ONE CUDA-graph launch: the token's fp32
+    q, k, v are copied from pinned host memory (one copy), ``attn_rope_kv_insert`` rotates q and k and appends k, v to
+    the resident fp16 caches, ``attn_decode`` attends over them, and the output is copied back to pinned host memory.
+    The engine drives its CUDA step the same way (a captured graph per step, include/model/device.hpp:161-262).
+    Calling the object replays the graph and waits for the result.
+
+    host_in   pinned fp32 [B*H*D + 2*B*Hkv*D]: q, then k, then v of the current token
+    k_cache, v_cache  fp16 [B, T, Hkv, D] on the device; pos, kv_pos int32 [B] on the device
+    out_host  pinned fp32 [B, H, D]
+    """
+
+    def __init__(self, host_in, k_cache, v_cache, pos, kv_pos, out_host, *, n_heads: int, theta: float,
+                 rotary_dim: int = 0, kv_len=None, workspace: DecodeWorkspace | None = None):
+        if not (host_in.is_pinned() and out_host.is_pinned()):
+            raise ValueError("host_in and out_host must be pinned host tensors")
+        B, T, Hkv, D = k_cache.shape
+        H = n_heads
+        n_q, n_kv = B * H * D, B * Hkv * D
+        if host_in.numel() != n_q + 2 * n_kv or host_in.dtype != torch.float32 or out_host.shape != (B, H, D):
+            raise ValueError("host_in must hold q, k, v of one token per sequence (fp32) and out_host be [B, H, D]")
+        dev = k_cache.device
+        self.host_in, self.out_host = host_in, out_host
+        self._dev_in = torch.empty(n_q + 2 * n_kv, dtype=torch.float32, device=dev)
+        q32 = self._dev_in[:n_q].view(B, H, D)
+        k32 = self._dev_in[n_q:n_q + n_kv].view(B, Hkv, D)
+        v32 = self._dev_in[n_q + n_kv:].view(B, Hkv, D)
+        self._q_rot = torch.empty((B, H, D), dtype=torch.float16, device=dev)
+        self._out = torch.empty((B, H, D), dtype=torch.float32, device=dev)
+        self.workspace = workspace if workspace is not None else DecodeWorkspace(B, H, Hkv, D, dev)
+
+        def launches():
+            self._dev_in.copy_(host_in, non_blocking=True)
+            rope_kv_insert(q32, k32, v32, k_cache, v_cache, pos, kv_pos, theta=theta, rotary_dim=rotary_dim,
+                           q_out=self._q_rot)
+            attn_decode(self._q_rot, k_cache, v_cache, kv_len, out=self._out, workspace=self.workspace)
+            out_host.copy_(self._out, non_blocking=True)
+
+        with torch.cuda.device(dev):
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                launches()  # lazy set-up of every kernel happens outside the capture
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize(dev)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                launches()
+        self._device = dev
+
+    def __call__(self) -> torch.Tensor:
+        self.graph.replay()
+        torch.cuda.current_stream(self._device).synchronize()  # the caller reads out_host before the next token
+        return self.out_host
+
+
 def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.float32, clip: float = 0.0,
              accumulate: bool = False, stream=None) -> torch.Tensor:
     """out[b] = clamp(W x[b]): x [B, n] fp32, w [d, n] fp16 (n fastest) -> out [B, d] fp32 or fp16 (may be a strided

@@ -178,6 +178,31 @@ def test_merge_entry_point(attention, wl, port):
     assert torch.equal(z, torch.zeros_like(z))
 
 
+@pytest.mark.parametrize("n_parts", [1, 7, 24, 25, 49, 97, 148, 301])
+@pytest.mark.parametrize("D", [64, 128])
+def test_merge_of_many_partials(attention, port, n_parts, D):
+    """From one to a few hundred partials per row (a single long sequence leaves one per split-pass CTA): same result
+    as the restated LSE merge, empty partials (lse = -inf) included."""
+    import torch
+    rng = np.random.default_rng(n_parts * 7 + D)
+    rows = 5
+    part_o = rng.standard_normal((n_parts, rows, D), dtype=np.float32)
+    part_lse = (rng.standard_normal((n_parts, rows), dtype=np.float32) * 3).astype(np.float32)
+    part_lse[rng.random((n_parts, rows)) < 0.2] = -np.inf
+    part_lse[:, 4] = -np.inf  # a row with nothing at all
+    lse = torch.empty(rows, dtype=torch.float32, device="cuda")
+    got = attention.attn_merge(torch.from_numpy(part_o).cuda(), torch.from_numpy(part_lse).cuda(), lse=lse)
+    torch.cuda.synchronize()
+    got, lse = got.cpu().numpy(), lse.cpu().numpy()
+    for r in range(rows):
+        want, want_lse = port.lse_merge(part_o[:, r], part_lse[:, r])
+        if np.isinf(part_lse[:, r]).all():
+            assert (got[r] == 0).all() and lse[r] == -np.inf
+        else:
+            np.testing.assert_allclose(got[r], want, rtol=0, atol=2e-5)
+            assert abs(lse[r] - want_lse) <= 1e-5 * max(1.0, abs(want_lse))
+
+
 def _sharded_single_gpu(attention, q, k, v, world, rank, bufs, out, status_ws, step=0, poll_limit=0):
     import torch
     return attention.attn_decode_sharded(q, k, v, peer_buffers=[b.data_ptr() for b in bufs], world_size=world,

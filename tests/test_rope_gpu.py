@@ -115,3 +115,32 @@ def test_rotated_q_feeds_decode_attention(attention, checker, pkg):
     want = checker.attn_decode(q_ref[None], kc_ref[None], vc_ref[None], np.array([pos + 1], np.uint32))
     max_abs, max_rel = wl.error_metrics(out.cpu().numpy(), want)
     assert max_abs <= wl.ABS_TOL and max_rel <= wl.REL_TOL, (max_abs, max_rel)
+
+
+def test_host_decode_step_graph_matches_the_eager_calls(built_lib, pkg):
+    """attention.HostDecodeStep (copy in, rope + insert, decode, copy out as one graph launch) against the same calls
+    made one by one; the pinned input is rewritten between replays, so the graph must re-read it every time."""
+    import torch
+    from llm_infer_b200 import attention as A
+    B, H, Hkv, D, T = 3, 8, 2, 128, 96
+    g = torch.Generator().manual_seed(5)
+    k_cache = torch.randn(B, T, Hkv, D, generator=g).half().cuda()
+    v_cache = torch.randn(B, T, Hkv, D, generator=g).half().cuda()
+    k_ref, v_ref = k_cache.clone(), v_cache.clone()
+    pos = torch.tensor([40, 95, 7], dtype=torch.int32).cuda()
+    kv_len = (pos + 1).to(torch.int32)
+    host_in = torch.zeros(B * H * D + 2 * B * Hkv * D).pin_memory()
+    out_host = torch.zeros(B, H, D).pin_memory()
+    step = A.HostDecodeStep(host_in, k_cache, v_cache, pos, pos, out_host, n_heads=H, theta=10000.0, kv_len=kv_len)
+    for trial in range(2):
+        fresh = torch.randn(host_in.numel(), generator=g)
+        host_in.copy_(fresh)
+        got = step().clone()
+        dev = fresh.cuda()
+        n_q, n_kv = B * H * D, B * Hkv * D
+        q = A.rope_kv_insert(dev[:n_q].view(B, H, D), dev[n_q:n_q + n_kv].view(B, Hkv, D),
+                             dev[n_q + n_kv:].view(B, Hkv, D), k_ref, v_ref, pos, pos, theta=10000.0,
+                             q_out_dtype=torch.float16)
+        want = A.attn_decode(q, k_ref, v_ref, kv_len).cpu()
+        assert torch.equal(got, want), trial
+        assert torch.equal(k_cache, k_ref) and torch.equal(v_cache, v_ref)
