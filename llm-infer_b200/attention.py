@@ -256,51 +256,17 @@ class HostDecodeStep:
         return self.out_host
 
 
-def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out_dtype=torch.float32, clip: float = 0.0,
-             accumulate: bool = False, stream=None) -> torch.Tensor:
-    """out[b] = clamp(W x[b]): x [B, n] fp32, w [d, n] fp16 (n fastest) -> out [B, d] fp32 or fp16 (may be a strided
-    view, e.g. a KV-cache row per sequence). Mirrors matmul() of include/kernels_cpu.hpp:69-80 for a batch."""
-    _require_cuda(x, w)
-    B, n = x.shape
-    d = w.shape[0]
-    if w.shape != (d, n) or w.dtype != torch.float16 or x.dtype != torch.float32:
-        raise ValueError("x must be fp32 [B, n] and w fp16 [d, n]")
-    x, w = x.contiguous(), w.contiguous()
-    if out is None:
-        out = torch.empty((B, d), dtype=out_dtype, device=x.device)
-    if out.shape != (B, d) or out.stride(1) != 1:
-        raise ValueError("out must be [B, d] with dense rows")
-    a = _b.AttnGemvArgs()
-    a.out, a.x, a.w = out.data_ptr(), x.data_ptr(), w.data_ptr()
-    a.out_batch_stride = out.stride(0) if B > 1 else d
-    a.n, a.d, a.batch, a.clip, a.out_dtype = n, d, B, float(clip), _dtype_code(out)
-    a.accumulate = int(accumulate)  # out += W x (residual connection); fp32 out only
-    with torch.cuda.device(x.device):
-        _b.check(_b.load().attn_gemv_f16(C.byref(a), _stream_ptr(stream)), "attn_gemv_f16")
-    return out
-
-
-def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=None, out_dtype=torch.float32,
-              clip: float = 0.0, accumulate: bool = False, swiglu: bool = False, k_split: int = 1, status=None,
-              stream=None) -> torch.Tensor:
-    """out[b] = clamp(W x[b]) over Q8_0 weights: x [B, n] fp32, w uint8 [rows, n/32*34] (GGML blocks: fp16 scale + 32
-    signed bytes) -> out [B, rows] fp32 or fp16. Same conventions as gemv_f16, plus:
-    * ``out2`` / ``out3``: the rows are split over out, out2, out3 in that order (stacked Q, K, V projections);
-    * ``swiglu``: w holds d gate rows then d up rows, out [B, d] = silu(gate x) * (up x);
-    * ``k_split`` > 1: out is [k_split, B, rows], the partial products of k_split equal slices of the inner
-      dimension (their sum is the result; ``rmsnorm(..., partials=out)`` adds them into the residual stream)."""
-    _require_cuda(x, w)
-    B, n = x.shape
+def _gemv(entry: str, x, w, n: int, out, out2, out3, out_dtype, clip, accumulate, swiglu, k_split, status, stream):
+    """Common part of gemv_f16 / gemv_q8_0: output shapes, the argument structure, the call."""
+    B = x.shape[0]
     rows = w.shape[0]
-    if w.dtype != torch.uint8 or w.shape != (rows, n // 32 * 34) or n % 32 or x.dtype != torch.float32:
-        raise ValueError("x must be fp32 [B, n] and w uint8 [rows, n/32*34]")
     if swiglu and (rows % 2 or out2 is not None or out3 is not None):
         raise ValueError("swiglu needs an even number of rows (gate rows, then up rows) and a single output")
+    if out3 is not None and out2 is None:
+        raise ValueError("out3 without out2")
     x, w = x.contiguous(), w.contiguous()
     d = rows // 2 if swiglu else rows
     segs = [t for t in (out2, out3) if t is not None]
-    if out3 is not None and out2 is None:
-        raise ValueError("out3 without out2")
     d0 = d - sum(t.shape[1] for t in segs)
     if k_split > 1:
         if out is None:
@@ -332,8 +298,37 @@ def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=Non
         a.out3, a.split2 = out3.data_ptr(), d0 + out2.shape[1]
         a.out3_batch_stride = out3.stride(0) if B > 1 else out3.shape[1]
     with torch.cuda.device(x.device):
-        _b.check(_b.load().attn_gemv_q8_0(C.byref(a), _stream_ptr(stream)), "attn_gemv_q8_0")
+        _b.check(getattr(_b.load(), entry)(C.byref(a), _stream_ptr(stream)), entry)
     return out
+
+
+def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=None, out_dtype=torch.float32,
+             clip: float = 0.0, accumulate: bool = False, swiglu: bool = False, k_split: int = 1,
+             stream=None) -> torch.Tensor:
+    """out[b] = clamp(W x[b]): x [B, n] fp32, w [rows, n] fp16 (n fastest) -> out [B, rows] fp32 or fp16 (may be a
+    strided view, e.g. a KV-cache row per sequence). Mirrors matmul() of include/kernels_cpu.hpp:69-80 for a batch;
+    ``accumulate`` adds into out (residual connection). Fused forms (they and any batch > 1 run on the tensor cores):
+    * ``out2`` / ``out3``: the rows are split over out, out2, out3 in that order (stacked Q, K, V projections);
+    * ``swiglu``: w holds d gate rows then d up rows, out [B, d] = silu(gate x) * (up x);
+    * ``k_split`` > 1: out is [k_split, B, rows], the partial products of k_split equal slices of the inner
+      dimension (their sum is the result; ``rmsnorm(..., partials=out)`` adds them into the residual stream)."""
+    _require_cuda(x, w)
+    B, n = x.shape
+    if w.dim() != 2 or w.shape[1] != n or w.dtype != torch.float16 or x.dtype != torch.float32:
+        raise ValueError("x must be fp32 [B, n] and w fp16 [rows, n]")
+    return _gemv("attn_gemv_f16", x, w, n, out, out2, out3, out_dtype, clip, accumulate, swiglu, k_split, None, stream)
+
+
+def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=None, out_dtype=torch.float32,
+              clip: float = 0.0, accumulate: bool = False, swiglu: bool = False, k_split: int = 1, status=None,
+              stream=None) -> torch.Tensor:
+    """The same over Q8_0 weights: w uint8 [rows, n/32*34] (GGML blocks: fp16 scale + 32 signed bytes). Same
+    conventions and fused forms as gemv_f16."""
+    _require_cuda(x, w)
+    B, n = x.shape
+    if w.dim() != 2 or w.dtype != torch.uint8 or w.shape[1] != n // 32 * 34 or n % 32 or x.dtype != torch.float32:
+        raise ValueError("x must be fp32 [B, n] and w uint8 [rows, n/32*34]")
+    return _gemv("attn_gemv_q8_0", x, w, n, out, out2, out3, out_dtype, clip, accumulate, swiglu, k_split, status, stream)
 
 
 def embed_f16(table: torch.Tensor, tokens: torch.Tensor, *, out=None, status=None, stream=None) -> torch.Tensor:

@@ -155,6 +155,8 @@ int current_device_info(DeviceInfo* out);
 int launch_decode_split(const DecodeParams& p, uint32_t head_dim, uint32_t hpc, bool qsplit, bool kv_bf16, bool fused,
                         uint32_t grid, size_t smem_bytes, cudaStream_t stream);
 int launch_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch);
+// fp16-weight GEMV on the tensor cores (attn_gemv_f16mma.cu): batches and the fused forms of attn_gemv_f16.
+int launch_gemv_f16_mma(const AttnGemvArgs* a, cudaStream_t stream);
 
 // Geometry of the decode split for given dimensions.
 struct DecodePlan {

@@ -4,8 +4,8 @@ The engine's forward is one token of one sequence at a time (``Model::forward``,
 ``Block::block_cpu_``, src/model/block.cpp:105-223); its CUDA block stops after attention
 (src/model/block.cu:235-239). This class runs the same sequence of steps for ``batch`` independent sequences per
 call, each with its own position and KV cache, through the C ABI kernels only (GEMV, RMSNorm, RoPE + cache insert,
-split-KV attention, SwiGLU, argmax): 13 launches per layer with fp16 weights, 9 with Q8_0 weights (stacked Q/K/V
-projection, SwiGLU as the epilogue of the stacked gate/up projection), none of them on the host, no CPU fallback.
+split-KV attention, SwiGLU, argmax): 9 launches per layer (stacked Q/K/V projection, SwiGLU as the epilogue of the
+stacked gate/up projection, residual added by the next norm), none of them on the host, no CPU fallback.
 
 Weights are the engine's: fp16 ``[d][n]`` matrices (n fastest, GGUF dims ``[n_in, n_out]``), fp32 norm vectors,
 stacked over the layers here. The KV caches keep the engine's ``[row][kv_head][head_dim]`` fp16 layout, one cache
@@ -110,18 +110,17 @@ class Llama:
             if tuple(t.shape) != shape or t.dtype != want:
                 raise ValueError(f"weight {name}: expected {shape} {want}, got {tuple(t.shape)} {t.dtype}")
             self.w[name] = t.to(dev).contiguous()
-        if q8:
-            # The Q8_0 GEMV takes stacked matrices: Q, K and V rows in one launch with three outputs, and gate (w1)
-            # rows followed by up (w3) rows with the SwiGLU product as its epilogue. Only the stacks are kept.
-            self.w["wqkv"] = torch.cat([self.w.pop("wq"), self.w.pop("wk"), self.w.pop("wv")], dim=1).contiguous()
-            self.w["w13"] = torch.cat([self.w.pop("w1"), self.w.pop("w3")], dim=1).contiguous()
+        # The GEMVs take stacked matrices: Q, K and V rows in one launch with three outputs, and gate (w1) rows
+        # followed by up (w3) rows with the SwiGLU product as its epilogue. Only the stacks are kept.
+        self.w["wqkv"] = torch.cat([self.w.pop("wq"), self.w.pop("wk"), self.w.pop("wv")], dim=1).contiguous()
+        self.w["w13"] = torch.cat([self.w.pop("w1"), self.w.pop("w3")], dim=1).contiguous()
         B, f32 = batch, torch.float32
         q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
         z = lambda *s, dtype=f32: torch.zeros(*s, dtype=dtype, device=dev)  # noqa: E731
         self.x, self.xb = z(B, c.dim), z(B, c.dim)
         self.q, self.k, self.v = z(B, c.n_heads, c.head_dim), z(B, c.n_kv_heads, c.head_dim), z(B, c.n_kv_heads, c.head_dim)
         self.att = z(B, c.n_heads, c.head_dim)
-        self.hb, self.hb2 = z(B, c.hidden_dim), z(B, c.hidden_dim)
+        self.hb = z(B, c.hidden_dim)
         self.logits = z(B, c.vocab_size)
         self.next_token = z(B, dtype=torch.int32)
         self.tokens = z(B, dtype=torch.int32)   # the step's input tokens; a decode step writes its picks back here
@@ -133,17 +132,15 @@ class Llama:
         self.v_cache = torch.zeros_like(self.k_cache)
         self.workspace = A.DecodeWorkspace(B, c.n_heads, c.n_kv_heads, c.head_dim, dev)
         self._q_dim, self._kv_dim = q_dim, kv_dim
-        # The Q8_0 down projection of a batch: when the hidden activations of all sequences do not fit in shared memory
-        # next to the weight ring, the inner dimension is split over sets of CTAs and the next RMSNorm adds the
-        # partial products into x (same sum, fixed order).
-        self._k_split = 1
-        if q8:
-            chunks = c.hidden_dim // 256
-            need = B * (c.hidden_dim * 4 + 64)
-            k = max(1, -(-need // (140 * 1024)))
-            while k <= chunks and chunks % k:
-                k += 1
-            self._k_split = k if k <= chunks else 1
+        # The down projection of a batch: when the hidden activations of all sequences do not fit in shared memory next
+        # to the weight ring, the inner dimension is split over sets of CTAs and the next RMSNorm adds the partial
+        # products into x (same sum, fixed order).
+        chunks = c.hidden_dim // 256
+        need = B * (c.hidden_dim * 4 + 64)
+        k = max(1, -(-need // (140 * 1024)))
+        while k <= chunks and chunks % k:
+            k += 1
+        self._k_split = k if k <= chunks else 1
         self.partials = z(self._k_split, B, c.dim) if self._k_split > 1 else None
 
     @classmethod
@@ -180,18 +177,12 @@ class Llama:
         gemv = self._gemv
         self._embed(w["embed"], self.tokens, out=self.x, status=self.status)
         att_flat = self.att.view(B, self._q_dim)
-        q8 = self.weight_type == "q8_0"
         pending = None  # partial products of the previous layer's down projection, still to be added into x
         for l in range(c.n_layers):
             A.rmsnorm(self.x, w["rms_att"][l], c.norm_eps, out=self.xb, partials=pending)
             pending = None
-            if q8:
-                gemv(self.xb, w["wqkv"][l], out=self.q.view(B, self._q_dim), out2=self.k.view(B, self._kv_dim),
-                     out3=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
-            else:
-                gemv(self.xb, w["wq"][l], out=self.q.view(B, self._q_dim), clip=c.qkv_clip)
-                gemv(self.xb, w["wk"][l], out=self.k.view(B, self._kv_dim), clip=c.qkv_clip)
-                gemv(self.xb, w["wv"][l], out=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
+            gemv(self.xb, w["wqkv"][l], out=self.q.view(B, self._q_dim), out2=self.k.view(B, self._kv_dim),
+                 out3=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
             A.rope_kv_insert(self.q, self.k, self.v, self.k_cache[l], self.v_cache[l], self.pos, self.kv_pos,
                              theta=c.rope_theta, rotary_dim=c.rotary_dim, kv_sink=kv_sink, q_out=self.q,
                              pos_early=True)   # positions are copied in before the step's first kernel
@@ -199,12 +190,7 @@ class Llama:
                           workspace=self.workspace)
             gemv(att_flat, w["wo"][l], out=self.x, accumulate=True)       # x += Wo att
             A.rmsnorm(self.x, w["rms_ffn"][l], c.norm_eps, out=self.xb)
-            if q8:
-                gemv(self.xb, w["w13"][l], out=self.hb, swiglu=True)      # hb = silu(W1 xb) * (W3 xb)
-            else:
-                gemv(self.xb, w["w1"][l], out=self.hb)
-                gemv(self.xb, w["w3"][l], out=self.hb2)
-                A.swiglu_(self.hb, self.hb2)
+            gemv(self.xb, w["w13"][l], out=self.hb, swiglu=True)          # hb = silu(W1 xb) * (W3 xb)
             if self._k_split > 1:
                 gemv(self.hb, w["w2"][l], out=self.partials, k_split=self._k_split)
                 pending = self.partials                                    # x += W2 hb, added by the next norm
@@ -220,7 +206,7 @@ class Llama:
     def capture(self) -> None:
         """Record the step once per mode (prefill: no classifier; decode: classifier + greedy pick + feedback) as CUDA
         graphs, the way the engine drives its CUDA step (include/model/device.hpp:161-262): a step then costs one
-        graph launch instead of 13 launches per layer. Positions inside the sliding window only (kv_sink = 0)."""
+        graph launch instead of 9 launches per layer. Positions inside the sliding window only (kv_sink = 0)."""
         if self._graphs is not None:
             return
         side = torch.cuda.Stream(self.device)

@@ -42,9 +42,12 @@ def test_fp16_result_into_a_strided_cache_row(attention, checker):
     torch.cuda.synchronize()
     got = cache.cpu().numpy()
     for b in range(B):
-        want = checker.matmul_clip(x[b], w).astype(np.float16)
+        want32 = checker.matmul_clip(x[b], w)
+        want = want32.astype(np.float16)
+        # one fp16 step of the rounded reference, or (results near zero, where fp16 steps are tiny) the fp32 bound
         steps = np.abs(got[b, row].view(np.int16).astype(np.int32) - want.view(np.int16).astype(np.int32))
-        assert steps.max() <= 1
+        near = np.abs(got[b, row].astype(np.float32) - want32) <= 4e-6 * (np.abs(x[b]) @ np.abs(w.astype(np.float32)).T) + 1e-3 * np.abs(want32)
+        assert ((steps <= 1) | near).all() and (np.abs(got[b, row].astype(np.float32) - want32) <= 2e-3 * np.abs(want32) + 1e-3).all()
         assert not got[b, row - 1].any() and not got[b, row + 1].any()  # neighbours untouched
 
 
@@ -160,46 +163,59 @@ def test_q8_0_streams_weights_near_hbm_rate(attention, pkg):
     assert gbs > 3000
 
 
-def test_q8_0_stacked_qkv_and_swiglu_epilogue(attention, port, pkg):
-    """One launch for the Q, K and V projections (three outputs) and one for silu(W1 x) * (W3 x), batch 8."""
+def _weights(kind, w32, port, checker):
+    """(device tensor, gemv wrapper name, per-sequence CPU product, fp32 view of the stored weights)."""
     import torch
     from llm_infer_b200 import quant
+    if kind == "q8_0":
+        blocks = quant.quantize_q8_0(w32)
+        return torch.from_numpy(blocks).cuda(), "gemv_q8_0", (lambda x, clip=0.0: port.matmul_q8_0(x, blocks, clip)), \
+            quant.dequantize_q8_0(blocks)
+    w16 = w32.astype(np.float16)
+    return torch.from_numpy(w16).cuda(), "gemv_f16", (lambda x, clip=0.0: checker.matmul_clip(x, w16, clip)), \
+        w16.astype(np.float32)
+
+
+@pytest.mark.parametrize("kind", ["q8_0", "f16"])
+def test_stacked_qkv_and_swiglu_epilogue(attention, port, checker, pkg, kind):
+    """One launch for the Q, K and V projections (three outputs) and one for silu(W1 x) * (W3 x), batch 8."""
+    import torch
     rng = np.random.default_rng(77)
     n, B = 2048, 8
     x = rng.standard_normal((B, n), dtype=np.float32)
-    wq, wk, wv = (quant.quantize_q8_0(rng.standard_normal((d, n), dtype=np.float32) * 0.03) for d in (512, 128, 128))
-    stacked = torch.from_numpy(np.concatenate([wq, wk, wv])).cuda()
+    mats = [_weights(kind, rng.standard_normal((d, n), dtype=np.float32) * 0.03, port, checker) for d in (512, 128, 128)]
+    stacked = torch.cat([m[0] for m in mats])
+    gemv = getattr(attention, mats[0][1])
     q, k, v = (torch.empty(B, d, device="cuda") for d in (512, 128, 128))
-    attention.gemv_q8_0(torch.from_numpy(x).cuda(), stacked, out=q, out2=k, out3=v, clip=0.8)
-    for got, w in ((q, wq), (k, wk), (v, wv)):
+    gemv(torch.from_numpy(x).cuda(), stacked, out=q, out2=k, out3=v, clip=0.8)
+    for got, m in ((q, mats[0]), (k, mats[1]), (v, mats[2])):
         got = got.cpu().numpy()
-        mag = np.abs(x) @ np.abs(quant.dequantize_q8_0(w)).T
+        mag = np.abs(x) @ np.abs(m[3]).T
         for b in range(B):
-            assert (np.abs(got[b] - port.matmul_q8_0(x[b], w, 0.8)) <= 4e-6 * mag[b] + 1e-7).all()
+            assert (np.abs(got[b] - m[2](x[b], 0.8)) <= 4e-6 * mag[b] + 1e-7).all()
     hidden = 1040  # 65 row groups: the up rows start at a group boundary that is not a multiple of the grid
-    w1, w3 = (quant.quantize_q8_0(rng.standard_normal((hidden, n), dtype=np.float32) * 0.03) for _ in range(2))
-    got = attention.gemv_q8_0(torch.from_numpy(x).cuda(), torch.from_numpy(np.concatenate([w1, w3])).cuda(),
-                              swiglu=True).cpu().numpy()
+    g1, g3 = (_weights(kind, rng.standard_normal((hidden, n), dtype=np.float32) * 0.03, port, checker) for _ in range(2))
+    got = gemv(torch.from_numpy(x).cuda(), torch.cat([g1[0], g3[0]]), swiglu=True).cpu().numpy()
     assert got.shape == (B, hidden)
     for b in range(B):
-        want = port.swiglu(port.matmul_q8_0(x[b], w1), port.matmul_q8_0(x[b], w3))
+        want = port.swiglu(g1[2](x[b]), g3[2](x[b]))
         assert np.abs(got[b] - want).max() <= 2e-5 * np.abs(want).max() + 1e-6
 
 
-def test_q8_0_split_k_partials_and_residual_norm(attention, port, pkg):
+@pytest.mark.parametrize("kind", ["q8_0", "f16"])
+def test_split_k_partials_and_residual_norm(attention, port, checker, pkg, kind):
     """k_split sets of CTAs each compute one slice of the inner dimension; the partial products sum to the product, and
     attn_rmsnorm_residual adds them into x before normalising."""
     import torch
-    from llm_infer_b200 import quant
     rng = np.random.default_rng(99)
     n, d, B, K = 14336, 1024, 8, 4
     x = rng.standard_normal((B, n), dtype=np.float32)
-    blocks = quant.quantize_q8_0(rng.standard_normal((d, n), dtype=np.float32) * 0.02)
-    parts = attention.gemv_q8_0(torch.from_numpy(x).cuda(), torch.from_numpy(blocks).cuda(), k_split=K)
+    w_dev, name, product, w_f32 = _weights(kind, rng.standard_normal((d, n), dtype=np.float32) * 0.02, port, checker)
+    parts = getattr(attention, name)(torch.from_numpy(x).cuda(), w_dev, k_split=K)
     assert parts.shape == (K, B, d)
     got = parts.sum(0).cpu().numpy()
-    mag = np.abs(x) @ np.abs(quant.dequantize_q8_0(blocks)).T
-    want = np.stack([port.matmul_q8_0(x[b], blocks) for b in range(B)])
+    mag = np.abs(x) @ np.abs(w_f32).T
+    want = np.stack([product(x[b]) for b in range(B)])
     assert (np.abs(got - want) <= 4e-6 * mag + 1e-7).all()
     assert (parts[0].abs().sum() > 0) and (parts[K - 1].abs().sum() > 0)
     # residual + norm
@@ -214,3 +230,16 @@ def test_q8_0_split_k_partials_and_residual_norm(attention, port, pkg):
     for b in range(B):
         ref = port.rmsnorm(full[b], wt, 1e-5)
         assert np.abs(normed[b].cpu().numpy() - ref).max() <= 4e-6 * np.abs(ref).max()
+
+
+def test_f16_batch_8_streams_weights_near_hbm_rate(attention):
+    """The batched fp16 form on the tensor cores: 14336 x 4096, batch 8."""
+    import torch
+    n, d = 4096, 14336
+    ws = [torch.randn(d, n, device="cuda").half() for _ in range(3)]  # 352 MB > L2, rotated
+    x = torch.randn(8, n, device="cuda")
+    out = torch.empty(8, d, device="cuda")
+    us = _graph_time_us(lambda i: attention.gemv_f16(x, ws[i], out=out), 3)
+    gbs = (d * n * 2 + 8 * (n * 4 + d * 4)) / us / 1e3
+    print(f"gemv 14336x4096 fp16 batch 8: {us:.1f} us, {gbs:.0f} GB/s")
+    assert gbs > 3000
