@@ -24,65 +24,20 @@
 // go to separate sets of CTAs that store their partial sums for the consumer (the next RMSNorm) to add.
 //
 // Algorithmic bytes per call = rows * n/32 * 34 + batch * (n*4 + d*sizeof(out)).
-#include <cuda.h>
-#include <cuda_fp16.h>
-
-#include "attn_internal.cuh"
-#include "ptx_sm100.cuh"
+#include "gemv_mma_common.cuh"
 
 namespace b200 {
 namespace {
 
-constexpr int kQ8Warps = 8;
-constexpr int kQ8Threads = kQ8Warps * 32;
+using namespace gemv_mma;
+
 constexpr uint32_t kBlockBytes = 34;                        // fp16 scale + 32 int8
 // Blocks of one row per stage (CB): 8 (272-byte row segments, up to four stages per warp) or 16 (544-byte segments,
 // two stages: ~10 % faster streaming, used when the activations leave room). A row segment is 68 or 136 words long
 // (4 or 8 mod 32), so the 8 rows x 4 lanes of one shared-memory load never share a bank.
-constexpr uint32_t kRows = 16;                              // rows of a group = M of the MMA
 constexpr uint32_t kMaxStages = 4;                          // barrier slots per warp
 constexpr uint32_t seg_bytes(uint32_t cb) { return cb * kBlockBytes; }          // one row's share of a stage
 constexpr uint32_t stage_bytes(uint32_t cb) { return kRows * seg_bytes(cb); }   // 4352 or 8704, multiples of 128
-
-struct Q8Params {
-    void* out0;               // rows [0, seg_end0)
-    void* out1;               // rows [seg_end0, seg_end1)
-    void* out2;               // rows [seg_end1, d)
-    uint64_t out_stride0, out_stride1, out_stride2;  // elements between sequences of each output
-    const float* x;
-    uint32_t* status;
-    uint64_t x_batch_stride;  // elements between sequences of x
-    uint32_t seg_end0, seg_end1;
-    uint32_t slice_blocks;    // blocks of the inner dimension staged at a time (multiple of the chunk)
-    uint32_t n_slices;        // slice_blocks * n_slices = blocks per row
-    uint32_t d, batch;        // output rows; with swiglu W has 2 d rows: gate rows, then up rows
-    uint32_t stages;
-    uint32_t x_col_pitch;     // 32-bit words between sequences of the staged activations
-    uint32_t acc_groups;      // row groups per CTA whose partial sums are carried across slices (0 when n_slices == 1)
-    uint32_t swiglu;
-    uint32_t k_split;         // > 1: the grid is k_split sets of CTAs, set s computes slice s only and stores its partial sums
-    uint64_t partial_stride;  // elements between the partial outputs of consecutive slices
-    float clip;
-    int32_t out_dtype;
-    int32_t accumulate;
-};
-
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                        uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// The first MMA of a block: accumulates onto zero (constant inputs, no registers to clear).
-__device__ __forceinline__ void mma_f16_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-}
 
 // Two bytes of w (already XORed with 0x80, i.e. q + 128) -> half2 (q_lo, q_hi): 0x6400 | u is the fp16 number
 // 1024 + u, and 1024 + u - 1152 = q exactly.
@@ -128,36 +83,27 @@ __device__ __forceinline__ void load_a(uint32_t (&r)[4], uint32_t seg_addr, uint
     r[3] = bytes_to_half2<2>(v1);
 }
 
-// Tile load through the TMA engine: 16 rows x 272 bytes of W in one request (rows beyond d read as zeros).
-__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y,
-                                              uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy)
-        : "memory");
-}
-
 template <uint32_t CB>
-__global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_constant__ CUtensorMap tm_w,
-                                                                  const __grid_constant__ Q8Params p) {
+__global__ void __launch_bounds__(kThreads, 1) gemv_q8_0_kernel(const __grid_constant__ CUtensorMap tm_w,
+                                                                  const __grid_constant__ Params p) {
     constexpr uint32_t kChunkBlocks = CB, kSegBytes = seg_bytes(CB), kSegPitch = kSegBytes, kStageBytes = stage_bytes(CB);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // tile loads want 128-byte alignment
     // layout: [ring: warps x stages x kStageBytes][red: 2 x 2 x warps x 128 floats][acc: acc_groups x 2 x 128 floats]
     //         [bars: warps x kMaxStages][x fragments]
-    const uint32_t ring_bytes = kQ8Warps * p.stages * kStageBytes;
+    const uint32_t ring_bytes = kWarps * p.stages * kStageBytes;
     float* s_red = reinterpret_cast<float*>(smem + ring_bytes);
-    float* s_acc = s_red + 2 * 2 * kQ8Warps * 128;
+    float* s_acc = s_red + 2 * 2 * kWarps * 128;
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_acc + p.acc_groups * 2 * 128);
-    uint32_t* s_x = reinterpret_cast<uint32_t*>(s_bar + kQ8Warps * kMaxStages);
+    uint32_t* s_x = reinterpret_cast<uint32_t*>(s_bar + kWarps * kMaxStages);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t groups = (p.d + kRows - 1) / kRows;
     const uint32_t parts = p.swiglu ? 2u : 1u;  // row groups of W per output row group (gate, up)
-    const uint32_t slice_chunks = p.slice_blocks / kChunkBlocks;
+    const uint32_t slice_chunks = p.slice_units / kChunkBlocks;
     // chunks of one slice of one row group that this warp owns: warp, warp + 8, ...
-    const uint32_t cpw = (slice_chunks > warp) ? (slice_chunks - warp + kQ8Warps - 1) / kQ8Warps : 0;
+    const uint32_t cpw = (slice_chunks > warp) ? (slice_chunks - warp + kWarps - 1) / kWarps : 0;
     // split-k: the grid is k_split sets of CTAs; set s handles slice s of every row group it owns
     const uint32_t ctas = gridDim.x / p.k_split, cta = blockIdx.x % ctas;
     const uint32_t slice_begin = p.k_split > 1 ? blockIdx.x / ctas : 0;
@@ -180,7 +126,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
         const uint32_t part = q % parts, q2 = q / parts;
         const uint32_t gi = q2 % my_groups, slice = slice_begin + q2 / my_groups;
         const uint32_t rg = cta + gi * ctas;
-        const uint32_t chunk = slice * slice_chunks + warp + ci * kQ8Warps;
+        const uint32_t chunk = slice * slice_chunks + warp + ci * kWarps;
         const uint32_t stage = item % p.stages;
         const uint32_t bar = bar0 + 8 * stage;
         if (lane == 0) {
@@ -205,30 +151,19 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
         // Activations of this slice as B fragments: for sequence c, block blk, k-step s, quarter t: four 32-bit words
         // {hi(x0,x1), hi(x2,x3), lo(x0,x1), lo(x2,x3)} of the elements x[32 blk + 16 s + 4 t .. +4). Every warp has
         // passed the previous slice's last block-wide barrier, so nobody still reads the old fragments.
-        const float* xs = p.x + static_cast<size_t>(slice) * p.slice_blocks * 32;
-        for (uint32_t i = tid; i < p.batch * p.slice_blocks * 8; i += kQ8Threads) {
-            const uint32_t c = i / (p.slice_blocks * 8), r = i - c * (p.slice_blocks * 8);
+        const float* xs = p.x + static_cast<size_t>(slice) * p.slice_units * 32;
+        for (uint32_t i = tid; i < p.batch * p.slice_units * 8; i += kThreads) {
+            const uint32_t c = i / (p.slice_units * 8), r = i - c * (p.slice_units * 8);
             const uint32_t blk = r >> 3, s = (r >> 2) & 1, tt = r & 3;
-            float4 v = *reinterpret_cast<const float4*>(xs + c * p.x_batch_stride + 32 * blk + 16 * s + 4 * tt);
-            v.x = fminf(fmaxf(v.x, -65504.f), 65504.f);
-            v.y = fminf(fmaxf(v.y, -65504.f), 65504.f);
-            v.z = fminf(fmaxf(v.z, -65504.f), 65504.f);
-            v.w = fminf(fmaxf(v.w, -65504.f), 65504.f);
-            const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
-            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-            const __half2 l01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y), l23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
-            uint4 o;
-            o.x = *reinterpret_cast<const uint32_t*>(&h01);
-            o.y = *reinterpret_cast<const uint32_t*>(&h23);
-            o.z = *reinterpret_cast<const uint32_t*>(&l01);
-            o.w = *reinterpret_cast<const uint32_t*>(&l23);
+            const float4 v = *reinterpret_cast<const float4*>(xs + c * p.x_batch_stride + 32 * blk + 16 * s + 4 * tt);
+            const uint4 o = split_activations(v.x, v.y, v.z, v.w);
             *reinterpret_cast<uint4*>(s_x + c * p.x_col_pitch + (blk * 2 + s) * 16 + tt * 4) = o;
         }
         __syncthreads();
 
         for (uint32_t gi = 0; gi < my_groups; ++gi, ++round) {
             const uint32_t rg = cta + gi * ctas;
-            float* red = s_red + (round & 1) * 2 * kQ8Warps * 128;
+            float* red = s_red + (round & 1) * 2 * kWarps * 128;
             for (uint32_t part = 0; part < parts; ++part) {
                 float tot[4] = {0.f, 0.f, 0.f, 0.f};
                 for (uint32_t ci = 0; ci < cpw; ++ci, ++item) {
@@ -236,7 +171,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
                     if (!mbar_wait(bar0 + 8 * stage, (item / p.stages) & 1)) timed_out = true;
                     const uint32_t seg_lo = ring0 + stage * kStageBytes + g * kSegPitch;
                     const uint32_t seg_hi = seg_lo + 8 * kSegPitch;
-                    const uint32_t* xb = my_x + (warp + ci * kQ8Warps) * kChunkBlocks * 32;
+                    const uint32_t* xb = my_x + (warp + ci * kWarps) * kChunkBlocks * 32;
 #pragma unroll
                     for (uint32_t bi = 0; bi < kChunkBlocks; ++bi) {
                         uint32_t alo[4], ahi[4];
@@ -270,72 +205,13 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_0_kernel(const __grid_c
                         issue(item + p.stages);
                     }
                 }
-                float* mine = red + (part * kQ8Warps + warp) * 128;
-                mine[g * 8 + 2 * t] = tot[0];
-                mine[g * 8 + 2 * t + 1] = tot[1];
-                mine[(g + 8) * 8 + 2 * t] = tot[2];
-                mine[(g + 8) * 8 + 2 * t + 1] = tot[3];
+                store_partial(red, part, warp, g, t, tot);
             }
             __syncthreads();
-            if (tid < 128) {
-                // fixed-order sum of the warps' partial sums; carried across slices in shared memory
-                float y[2] = {0.f, 0.f};
-                for (uint32_t part = 0; part < parts; ++part) {
-                    const float* src = red + part * kQ8Warps * 128 + tid;
-                    float v = 0.f;
-#pragma unroll
-                    for (int w = 0; w < kQ8Warps; ++w) v += src[w * 128];
-                    if (slice_end - slice_begin > 1) {
-                        float* carry = s_acc + (gi * 2 + part) * 128 + tid;
-                        if (slice > slice_begin) v += *carry;
-                        if (slice + 1 < slice_end) *carry = v;
-                    }
-                    y[part] = v;
-                }
-                const uint32_t row = rg * kRows + (tid >> 3), c = tid & 7;
-                if (slice + 1 == slice_end && row < p.d && c < p.batch) {
-                    float v = y[0];
-                    if (p.swiglu) v = __fdiv_rn(v, 1.0f + expf(-v)) * y[1];  // silu(gate) * up, src/model/block.cpp:206-210
-                    if (p.clip > 0.f) v = fminf(fmaxf(v, -p.clip), p.clip);
-                    void* out = p.out0;
-                    uint64_t stride = p.out_stride0;
-                    uint32_t r0 = 0;
-                    if (row >= p.seg_end1) {
-                        out = p.out2, stride = p.out_stride2, r0 = p.seg_end1;
-                    } else if (row >= p.seg_end0) {
-                        out = p.out1, stride = p.out_stride1, r0 = p.seg_end0;
-                    }
-                    const size_t o = static_cast<size_t>(c) * stride + (row - r0) +
-                                     (p.k_split > 1 ? slice_begin * p.partial_stride : 0);
-                    if (p.out_dtype == ATTN_DTYPE_F32) {
-                        float* dst = reinterpret_cast<float*>(out) + o;
-                        *dst = p.accumulate ? *dst + v : v;
-                    } else {
-                        reinterpret_cast<__half*>(out)[o] = __float2half_rn(v);
-                    }
-                }
-            }
+            reduce_and_store(p, red, s_acc, tid, parts, gi, rg, slice, slice_begin, slice_end);
         }
     }
     if (timed_out && lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
-}
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// The driver's tensor-map encoder, looked up once (a host-side computation; nothing is allocated).
-EncodeTiledFn encode_tiled_fn() {
-    static std::atomic<void*> cached{nullptr};
-    void* fn = cached.load(std::memory_order_acquire);
-    if (!fn) {
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
-            qres != cudaDriverEntryPointSuccess)
-            return nullptr;
-        cached.store(fn, std::memory_order_release);
-    }
-    return reinterpret_cast<EncodeTiledFn>(fn);
 }
 
 }  // namespace
@@ -347,13 +223,8 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     if (!a || !a->out || !a->x || !a->w || a->n == 0 || a->d == 0 || a->batch == 0) return ATTN_ERR_INVALID_ARG;
     if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16) return ATTN_ERR_INVALID_ARG;
     if (a->n % 256 != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
-    if (a->accumulate && a->out_dtype != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;
-    if (a->swiglu && (a->d % kRows != 0 || a->split1 || a->split2)) return ATTN_ERR_UNSUPPORTED;
-    const uint32_t k_split = a->k_split > 1 ? a->k_split : 1;
-    if (k_split > 1 && (a->swiglu || a->split1 || a->accumulate || a->clip > 0.f || a->out_dtype != ATTN_DTYPE_F32))
-        return ATTN_ERR_UNSUPPORTED;
-    if ((a->split1 && (!a->out2 || a->split1 >= a->d)) || (a->split2 && (!a->out3 || a->split2 <= a->split1 || a->split2 >= a->d)))
-        return ATTN_ERR_INVALID_ARG;
+    uint32_t k_split = 1;
+    if (int rc0 = check_fused_args(a, &k_split); rc0 != ATTN_OK) return rc0;
     if ((reinterpret_cast<uintptr_t>(a->x) & 15u) || (reinterpret_cast<uintptr_t>(a->w) & 15u)) return ATTN_ERR_ALIGNMENT;
     DeviceInfo dev{};
     int rc = current_device_info(&dev);
@@ -369,8 +240,8 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     // staged activations: 128 bytes per block and sequence, sequences 64 bytes apart modulo 128 (bank spread)
     auto x_bytes = [&](uint32_t blocks) { return static_cast<size_t>(a->batch) * (blocks * 128 + 64); };
     auto fixed_bytes = [&](uint32_t slices) {
-        return 2 * 2 * kQ8Warps * 128 * sizeof(float) + ((slices > 1 && k_split == 1) ? groups_per_cta * 2 * 128 * sizeof(float) : 0) +
-               kQ8Warps * kMaxStages * sizeof(uint64_t) + 128;
+        return 2 * 2 * kWarps * 128 * sizeof(float) + ((slices > 1 && k_split == 1) ? groups_per_cta * 2 * 128 * sizeof(float) : 0) +
+               kWarps * kMaxStages * sizeof(uint64_t) + 128;
     };
     // The activations are staged in equal slices of the inner dimension, as few as leave room for a two-stage ring; the
     // partial sums of the CTA's row groups are carried from slice to slice in shared memory (or, with k_split, the
@@ -382,7 +253,7 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     auto make_plan = [&](uint32_t cb, Plan* out) {
         if (n_blocks % cb != 0) return false;
         const uint32_t n_chunks = n_blocks / cb;
-        const size_t ring2 = 2 * static_cast<size_t>(kQ8Warps) * stage_bytes(cb);
+        const size_t ring2 = 2 * static_cast<size_t>(kWarps) * stage_bytes(cb);
         uint32_t slices = k_split;
         if (k_split > 1) {
             if (n_chunks % k_split != 0 || fixed_bytes(1) + ring2 + x_bytes(n_blocks / k_split) > budget) return false;
@@ -392,9 +263,9 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
             if (slices > n_chunks) return false;
         }
         uint32_t stages = cb == 8 ? 4 : 2;
-        while (stages > 2 && fixed_bytes(slices) + stages * kQ8Warps * stage_bytes(cb) + x_bytes(n_blocks / slices) > budget) --stages;
+        while (stages > 2 && fixed_bytes(slices) + stages * kWarps * stage_bytes(cb) + x_bytes(n_blocks / slices) > budget) --stages;
         *out = Plan{cb, slices, stages,
-                    fixed_bytes(slices) + static_cast<size_t>(stages) * kQ8Warps * stage_bytes(cb) + x_bytes(n_blocks / slices)};
+                    fixed_bytes(slices) + static_cast<size_t>(stages) * kWarps * stage_bytes(cb) + x_bytes(n_blocks / slices)};
         return true;
     };
     Plan plan{};
@@ -422,36 +293,17 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
             return ATTN_ERR_CUDA;
         }
     }
-    Q8Params p{};
-    const uint64_t stride0 = a->out_batch_stride ? a->out_batch_stride : (a->split1 ? a->split1 : a->d);
-    p.out0 = a->out;
-    p.out_stride0 = stride0;
-    p.seg_end0 = a->split1 ? a->split1 : a->d;
-    p.out1 = a->out2;
-    p.out_stride1 = a->out2_batch_stride ? a->out2_batch_stride : ((a->split2 ? a->split2 : a->d) - p.seg_end0);
-    p.seg_end1 = a->split2 ? a->split2 : a->d;
-    p.out2 = a->out3;
-    p.out_stride2 = a->out3_batch_stride ? a->out3_batch_stride : (a->d - p.seg_end1);
-    p.x = a->x;
-    p.status = a->status;
-    p.x_batch_stride = a->n;
-    p.slice_blocks = slice_blocks;
+    Params p{};
+    fill_common(p, a, k_split);
+    p.slice_units = slice_blocks;
     p.n_slices = slices;
-    p.d = a->d;
-    p.batch = a->batch;
     p.stages = stages;
     p.x_col_pitch = slice_blocks * 32 + 16;
     p.acc_groups = (slices > 1 && k_split == 1) ? groups_per_cta : 0;
-    p.k_split = k_split;
-    p.partial_stride = static_cast<uint64_t>(a->batch) * stride0;
-    p.swiglu = a->swiglu ? 1u : 0u;
-    p.clip = a->clip;
-    p.out_dtype = a->out_dtype;
-    p.accumulate = a->accumulate;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     auto kernel = plan.cb == 16 ? gemv_q8_0_kernel<16> : gemv_q8_0_kernel<8>;
     B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    B200_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(kQ8Threads), smem, stream, tm_w, p));
+    B200_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(kThreads), smem, stream, tm_w, p));
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return ATTN_OK;
 }

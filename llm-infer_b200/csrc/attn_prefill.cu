@@ -33,6 +33,7 @@
 
 #include "attn_internal.cuh"
 #include "ptx_sm100.cuh"
+#include "tma_tile.cuh"
 
 namespace b200 {
 namespace {
@@ -543,23 +544,6 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 }
 
 // ------------------------------------------------------------------------------------------------ host
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static std::atomic<void*> cached{nullptr};
-    void* fn = cached.load(std::memory_order_acquire);
-    if (!fn) {
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
-            qres != cudaDriverEntryPointSuccess)
-            return nullptr;
-        cached.store(fn, std::memory_order_release);
-    }
-    return reinterpret_cast<EncodeTiledFn>(fn);
-}
-
 // [B][S][heads][128] tensor viewed as (dim, row, head, batch); box = 128 bytes of 128 rows, 128-byte swizzle.
 int make_map(CUtensorMap* map, const void* ptr, int32_t dtype, uint32_t batch, uint32_t seq, uint32_t heads) {
     EncodeTiledFn enc = encode_tiled_fn();
