@@ -48,7 +48,18 @@ enum {
     ATTN_ERR_DEVICE = -6        /* not an sm_100 device */
 };
 
-enum { ATTN_DTYPE_F32 = 0, ATTN_DTYPE_F16 = 1, ATTN_DTYPE_BF16 = 2 };
+enum {
+    ATTN_DTYPE_F32 = 0,
+    ATTN_DTYPE_F16 = 1,
+    ATTN_DTYPE_BF16 = 2,
+    /* Activations prepared for the tensor-core GEMV (attn_gemv_q8_0 with x_format = ATTN_DTYPE_SPLIT16): one 32-bit word
+     * per element; elements 4r .. 4r+3 of a vector occupy words 4r .. 4r+3 as {fp16(x0) | fp16(x1) << 16,
+     * fp16(x2) | fp16(x3) << 16, fp16(x0 - fp16(x0)) | ... << 16, fp16(x2 - fp16(x2)) | ... << 16}: an fp16 value and an
+     * fp16 residual per element (~ 22 significant bits), |x| clamped to 65504. A producer that writes its result in
+     * this form (attn_decode o_dtype, attn_gemv_q8_0 out_dtype, attn_rmsnorm_residual out_split) saves the consumer
+     * the conversion that every CTA of the GEMV would otherwise repeat. */
+    ATTN_DTYPE_SPLIT16 = 3
+};
 
 /* Bits of the optional device status word (AttnDecodeArgs.status etc.). A kernel
  * ORs a bit in and returns early instead of spinning for ever or trapping. */
@@ -67,7 +78,7 @@ typedef struct AttnDecodeArgs {
     const void* v; /* in : same geometry as k */
     float* lse;    /* optional out: [batch][n_heads] natural-log sum-exp of the scaled scores
                       (-inf for an empty sequence); NULL to skip */
-    int32_t o_dtype;  /* ATTN_DTYPE_F32 | F16 | BF16 */
+    int32_t o_dtype;  /* ATTN_DTYPE_F32 | F16 | BF16 | SPLIT16 (32-bit words, n_heads*head_dim a multiple of 4) */
     int32_t q_dtype;  /* ATTN_DTYPE_F32 | F16 | BF16 */
     int32_t kv_dtype; /* ATTN_DTYPE_F16 | BF16 */
     uint32_t batch;
@@ -160,7 +171,7 @@ typedef struct AttnGemvArgs {
     uint32_t d;
     uint32_t batch;     /* 1 .. 8 */
     float clip;         /* > 0: clamp to [-clip, clip]; 0 = none */
-    int32_t out_dtype;  /* ATTN_DTYPE_F32 | ATTN_DTYPE_F16 */
+    int32_t out_dtype;  /* ATTN_DTYPE_F32 | ATTN_DTYPE_F16 | (q8_0 only) ATTN_DTYPE_SPLIT16, segment widths multiples of 4 */
     int32_t accumulate; /* != 0 (fp32 out only): out += result, the residual connection of src/model/block.cpp:169-172 */
     uint32_t* status;   /* optional device word: ATTN_STATUS_WAIT_TIMEOUT is ORed in if a bounded wait ran out (Q8_0) */
     /* Optional row segments (0 / NULL = unused): rows [0, split1) go to out, [split1, split2) to out2, [split2, d) to
@@ -178,6 +189,9 @@ typedef struct AttnGemvArgs {
      * is the product. For the FFN down projection of a batch (8 x 14336 activations do not fit in shared memory at
      * once); attn_rmsnorm_residual adds the partials into the residual stream. */
     uint32_t k_split;
+    /* ATTN_DTYPE_F32 (0): x is fp32. ATTN_DTYPE_SPLIT16 (q8_0 only): x points at prepared activations, 32-bit words
+     * [batch][n] dense, which the kernel copies into shared memory as they are. */
+    int32_t x_format;
 } AttnGemvArgs;
 
 int attn_gemv_f16(const AttnGemvArgs* args, void* stream);
@@ -210,6 +224,12 @@ int attn_rmsnorm(float* out, const float* x, const float* weight, uint32_t batch
  * with k_split > 1. out must not be x when n_partials > 0. */
 int attn_rmsnorm_residual(float* out, float* x, const float* partials, uint32_t n_partials, uint64_t partial_stride,
                           const float* weight, uint32_t batch, uint32_t dim, float eps, void* stream);
+
+/* The same, with the normalised row written as prepared activations (ATTN_DTYPE_SPLIT16 words [batch][dim], dim a
+ * multiple of 4) instead of fp32. */
+int attn_rmsnorm_residual_split(uint32_t* out_split, float* x, const float* partials, uint32_t n_partials,
+                                uint64_t partial_stride, const float* weight, uint32_t batch, uint32_t dim, float eps,
+                                void* stream);
 
 /* hb[i] = silu(hb[i]) * hb2[i], silu(x) = x / (1 + expf(-x)), over count elements (src/model/block.cpp:206-210). */
 int attn_swiglu(float* hb, const float* hb2, uint64_t count, void* stream);

@@ -16,7 +16,9 @@ import torch
 
 from . import binding as _b
 
-_DTYPES = {torch.float32: _b.DTYPE_F32, torch.float16: _b.DTYPE_F16, torch.bfloat16: _b.DTYPE_BF16}
+_DTYPES = {torch.float32: _b.DTYPE_F32, torch.float16: _b.DTYPE_F16, torch.bfloat16: _b.DTYPE_BF16,
+           # int32 tensors stand for prepared activations (ATTN_DTYPE_SPLIT16: one 32-bit word per element)
+           torch.int32: 3}
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -290,6 +292,7 @@ def _gemv(entry: str, x, w, n: int, out, out2, out3, out_dtype, clip, accumulate
     a.accumulate = int(accumulate)
     a.swiglu = int(swiglu)
     a.k_split = int(k_split)
+    a.x_format = _dtype_code(x)  # fp32, or int32 = prepared activations
     a.status = status.data_ptr() if status is not None else None
     if out2 is not None:
         a.out2, a.split1 = out2.data_ptr(), d0
@@ -323,11 +326,14 @@ def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=Non
               clip: float = 0.0, accumulate: bool = False, swiglu: bool = False, k_split: int = 1, status=None,
               stream=None) -> torch.Tensor:
     """The same over Q8_0 weights: w uint8 [rows, n/32*34] (GGML blocks: fp16 scale + 32 signed bytes). Same
-    conventions and fused forms as gemv_f16."""
+    conventions and fused forms as gemv_f16. x and out may also be int32 tensors, which stand for prepared activations
+    (one word per element: fp16 value and fp16 residual, written by rmsnorm(out=int32), attn_decode(out=int32) or
+    this function itself): the kernel then copies x into shared memory as it is instead of converting it in every CTA."""
     _require_cuda(x, w)
     B, n = x.shape
-    if w.dim() != 2 or w.dtype != torch.uint8 or w.shape[1] != n // 32 * 34 or n % 32 or x.dtype != torch.float32:
-        raise ValueError("x must be fp32 [B, n] and w uint8 [rows, n/32*34]")
+    if w.dim() != 2 or w.dtype != torch.uint8 or w.shape[1] != n // 32 * 34 or n % 32 or \
+            x.dtype not in (torch.float32, torch.int32):
+        raise ValueError("x must be fp32 (or int32 = prepared activations) [B, n] and w uint8 [rows, n/32*34]")
     return _gemv("attn_gemv_q8_0", x, w, n, out, out2, out3, out_dtype, clip, accumulate, swiglu, k_split, status, stream)
 
 
@@ -366,7 +372,8 @@ def embed_q8_0(table: torch.Tensor, tokens: torch.Tensor, *, out=None, status=No
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, out=None, partials=None, stream=None) -> torch.Tensor:
-    """out[b] = x[b] / sqrt(mean(x[b]^2) + eps) * weight, fp32 (include/kernels_cpu.hpp:43-67); out may be x.
+    """out[b] = x[b] / sqrt(mean(x[b]^2) + eps) * weight, fp32 (include/kernels_cpu.hpp:43-67); out may be x, or an
+    int32 tensor [B, dim] to receive the result as prepared activations for gemv_q8_0.
     With ``partials`` [k, B, dim] (fp32, dense) the row is first completed, x += partials[0] + partials[1] + ...
     (written back to x), then normalised into ``out`` (which must then be another tensor)."""
     _require_cuda(x, weight)
@@ -380,9 +387,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, out=None, part
         if partials.dtype != torch.float32 or partials.shape[1:] != (B, dim) or not partials.is_contiguous():
             raise ValueError("partials must be dense fp32 [k, B, dim]")
         n_part, stride, pptr = partials.shape[0], B * dim, partials.data_ptr()
+    fn = _b.load().attn_rmsnorm_residual_split if out.dtype == torch.int32 else _b.load().attn_rmsnorm_residual
     with torch.cuda.device(x.device):
-        _b.check(_b.load().attn_rmsnorm_residual(out.data_ptr(), x.data_ptr(), pptr, n_part, stride, weight.data_ptr(),
-                                                 B, dim, float(eps), _stream_ptr(stream)), "attn_rmsnorm")
+        _b.check(fn(out.data_ptr(), x.data_ptr(), pptr, n_part, stride, weight.data_ptr(), B, dim, float(eps),
+                    _stream_ptr(stream)), "attn_rmsnorm")
     return out
 
 

@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "attn_embed_q8_0",
     "attn_rmsnorm",
     "attn_rmsnorm_residual",
+    "attn_rmsnorm_residual_split",
     "attn_swiglu",
     "attn_argmax",
     "attn_status_string",
@@ -159,6 +160,7 @@ class AttnGemvArgs(C.Structure):
         ("split2", C.c_uint32),
         ("swiglu", C.c_int32),
         ("k_split", C.c_uint32),
+        ("x_format", C.c_int32),
     ]
 
 
@@ -224,6 +226,8 @@ def load() -> C.CDLL:
     lib.attn_rmsnorm_residual.restype = C.c_int
     lib.attn_rmsnorm_residual.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_uint32,
                                           C.c_uint32, C.c_float, C.c_void_p]
+    lib.attn_rmsnorm_residual_split.restype = C.c_int
+    lib.attn_rmsnorm_residual_split.argtypes = lib.attn_rmsnorm_residual.argtypes
     lib.attn_swiglu.restype = C.c_int
     lib.attn_swiglu.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.attn_argmax.restype = C.c_int

@@ -49,6 +49,7 @@ namespace {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 bool valid_dtype(int32_t d) { return d == ATTN_DTYPE_F32 || d == ATTN_DTYPE_F16 || d == ATTN_DTYPE_BF16; }
+bool valid_out_dtype(int32_t d) { return valid_dtype(d) || d == ATTN_DTYPE_SPLIT16; }
 
 // Rows each CTA should own at least before another CTA is brought in: below
 // this the per-CTA fixed cost (Q load, partial write, merge work) outweighs the
@@ -82,7 +83,8 @@ struct Exchange {
 
 int decode_impl(const AttnDecodeArgs* a, void* stream_v, const Exchange* xchg) {
     if (!a || !a->o || !a->q || !a->k || !a->v) return ATTN_ERR_INVALID_ARG;
-    if (!valid_dtype(a->o_dtype) || !valid_dtype(a->q_dtype)) return ATTN_ERR_INVALID_ARG;
+    if (!valid_out_dtype(a->o_dtype) || !valid_dtype(a->q_dtype)) return ATTN_ERR_INVALID_ARG;
+    if (a->o_dtype == ATTN_DTYPE_SPLIT16 && (a->n_heads * a->head_dim) % 4 != 0) return ATTN_ERR_UNSUPPORTED;
     if (a->kv_dtype != ATTN_DTYPE_F16 && a->kv_dtype != ATTN_DTYPE_BF16) return ATTN_ERR_UNSUPPORTED;
     if (a->batch == 0 || a->n_heads == 0 || a->n_kv_heads == 0 || a->head_dim == 0) return ATTN_ERR_INVALID_ARG;
     if (a->n_heads % a->n_kv_heads != 0) return ATTN_ERR_INVALID_ARG;
@@ -206,7 +208,7 @@ int attn_decode_sharded(const AttnDecodeShardedArgs* s, void* stream_v) {
 
 int attn_merge(const AttnMergeArgs* a, void* stream_v) {
     if (!a || !a->o || !a->part_o || !a->part_lse) return ATTN_ERR_INVALID_ARG;
-    if (!valid_dtype(a->o_dtype)) return ATTN_ERR_INVALID_ARG;
+    if (!valid_out_dtype(a->o_dtype)) return ATTN_ERR_INVALID_ARG;
     if (a->n_parts == 0 || a->rows == 0) return ATTN_ERR_INVALID_ARG;
     if (a->head_dim != 32 && a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return ATTN_ERR_UNSUPPORTED;
     if (!aligned16(a->part_o) || a->o_part_stride % 4 != 0) return ATTN_ERR_ALIGNMENT;

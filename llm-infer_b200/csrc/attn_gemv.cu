@@ -139,6 +139,7 @@ extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
     if (!a || !a->out || !a->x || !a->w || a->n == 0 || a->d == 0 || a->batch == 0) return ATTN_ERR_INVALID_ARG;
     if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16) return ATTN_ERR_INVALID_ARG;
     if (a->accumulate && a->out_dtype != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;
+    if (a->x_format != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;  // prepared activations: Q8_0 kernel only
     if ((reinterpret_cast<uintptr_t>(a->x) & 15u) || (reinterpret_cast<uintptr_t>(a->w) & 31u)) return ATTN_ERR_ALIGNMENT;
     // Batches and the fused forms (row segments, SwiGLU, k_split) run on the tensor cores; one sequence with a plain
     // output stays on the streaming kernel below (same bandwidth, no staging of fragments).

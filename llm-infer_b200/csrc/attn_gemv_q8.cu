@@ -95,7 +95,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q8_0_kernel(const __grid_con
     float* s_red = reinterpret_cast<float*>(smem + ring_bytes);
     float* s_acc = s_red + 2 * 2 * kWarps * 128;
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_acc + p.acc_groups * 2 * 128);
-    uint32_t* s_x = reinterpret_cast<uint32_t*>(s_bar + kWarps * kMaxStages);
+    uint32_t* s_x = reinterpret_cast<uint32_t*>(s_bar + kWarps * kMaxStages + 2);  // + the activations' barrier (padded to 16 bytes)
+    const uint32_t bar_x = smem_u32(s_bar + kWarps * kMaxStages);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
@@ -117,6 +118,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q8_0_kernel(const __grid_con
 
     if (lane == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) mbar_init(bar0 + 8 * s, 1);
+        if (warp == 0) mbar_init(bar_x, 1);
         mbar_init_fence();
     }
     __syncwarp();
@@ -151,15 +153,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q8_0_kernel(const __grid_con
         // Activations of this slice as B fragments: for sequence c, block blk, k-step s, quarter t: four 32-bit words
         // {hi(x0,x1), hi(x2,x3), lo(x0,x1), lo(x2,x3)} of the elements x[32 blk + 16 s + 4 t .. +4). Every warp has
         // passed the previous slice's last block-wide barrier, so nobody still reads the old fragments.
-        const float* xs = p.x + static_cast<size_t>(slice) * p.slice_units * 32;
-        for (uint32_t i = tid; i < p.batch * p.slice_units * 8; i += kThreads) {
-            const uint32_t c = i / (p.slice_units * 8), r = i - c * (p.slice_units * 8);
-            const uint32_t blk = r >> 3, s = (r >> 2) & 1, tt = r & 3;
-            const float4 v = *reinterpret_cast<const float4*>(xs + c * p.x_batch_stride + 32 * blk + 16 * s + 4 * tt);
-            const uint4 o = split_activations(v.x, v.y, v.z, v.w);
-            *reinterpret_cast<uint4*>(s_x + c * p.x_col_pitch + (blk * 2 + s) * 16 + tt * 4) = o;
+        if (p.x_split) {
+            // prepared activations: one bulk copy per sequence, as they are; the barrier's phase counts the slices
+            __syncthreads();  // (barrier initialised; with more than one slice: the old fragments are no longer read)
+            if (tid == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                const uint32_t bytes = p.slice_units * 32 * 4;
+                mbar_arrive_expect_tx(bar_x, bytes * p.batch);
+                const uint32_t* xw = reinterpret_cast<const uint32_t*>(p.x) + static_cast<size_t>(slice) * p.slice_units * 32;
+                for (uint32_t c = 0; c < p.batch; ++c) {
+                    bulk_g2s(smem_u32(s_x + c * p.x_col_pitch), xw + c * p.x_batch_stride, bytes, bar_x, l2_policy_evict_last());
+                }
+            }
+            if (!mbar_wait(bar_x, (slice - slice_begin) & 1)) timed_out = true;
+        } else {
+            const float* xs = p.x + static_cast<size_t>(slice) * p.slice_units * 32;
+            for (uint32_t i = tid; i < p.batch * p.slice_units * 8; i += kThreads) {
+                const uint32_t c = i / (p.slice_units * 8), r = i - c * (p.slice_units * 8);
+                const uint32_t blk = r >> 3, s = (r >> 2) & 1, tt = r & 3;
+                const float4 v = *reinterpret_cast<const float4*>(xs + c * p.x_batch_stride + 32 * blk + 16 * s + 4 * tt);
+                const uint4 o = split_activations(v.x, v.y, v.z, v.w);
+                *reinterpret_cast<uint4*>(s_x + c * p.x_col_pitch + (blk * 2 + s) * 16 + tt * 4) = o;
+            }
+            __syncthreads();
         }
-        __syncthreads();
 
         for (uint32_t gi = 0; gi < my_groups; ++gi, ++round) {
             const uint32_t rg = cta + gi * ctas;
@@ -221,7 +238,8 @@ using namespace b200;
 
 extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     if (!a || !a->out || !a->x || !a->w || a->n == 0 || a->d == 0 || a->batch == 0) return ATTN_ERR_INVALID_ARG;
-    if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16) return ATTN_ERR_INVALID_ARG;
+    if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16 && a->out_dtype != ATTN_DTYPE_SPLIT16)
+        return ATTN_ERR_INVALID_ARG;
     if (a->n % 256 != 0 || a->batch > 8) return ATTN_ERR_UNSUPPORTED;
     uint32_t k_split = 1;
     if (int rc0 = check_fused_args(a, &k_split); rc0 != ATTN_OK) return rc0;
@@ -241,7 +259,7 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     auto x_bytes = [&](uint32_t blocks) { return static_cast<size_t>(a->batch) * (blocks * 128 + 64); };
     auto fixed_bytes = [&](uint32_t slices) {
         return 2 * 2 * kWarps * 128 * sizeof(float) + ((slices > 1 && k_split == 1) ? groups_per_cta * 2 * 128 * sizeof(float) : 0) +
-               kWarps * kMaxStages * sizeof(uint64_t) + 128;
+               (kWarps * kMaxStages + 2) * sizeof(uint64_t) + 128;
     };
     // The activations are staged in equal slices of the inner dimension, as few as leave room for a two-stage ring; the
     // partial sums of the CTA's row groups are carried from slice to slice in shared memory (or, with k_split, the

@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 
 #include "attn_internal.cuh"
+#include "gemv_mma_common.cuh"
 #include "ptx_sm100.cuh"
 
 namespace b200 {
@@ -58,7 +59,8 @@ __global__ void __launch_bounds__(kOpsThreads) embed_q8_kernel(float* x, const u
 constexpr int kNormThreads = 1024;
 
 struct NormParams {
-    float* out;
+    float* out;             // fp32 result, or null when out_split is given
+    uint32_t* out_split;    // the result as prepared activations (ATTN_DTYPE_SPLIT16 words), or null
     const float* x;
     float* x_store;         // where the completed row goes (partials only); may be x
     const float* partials;  // [n_partials][batch][dim] or null
@@ -127,14 +129,20 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const __grid_cons
                 o.y = __fdiv_rn(v[j].y, rms) * w.y;
                 o.z = __fdiv_rn(v[j].z, rms) * w.z;
                 o.w = __fdiv_rn(v[j].w, rms) * w.w;
-                *reinterpret_cast<float4*>(p.out + base + i) = o;
+                if (p.out_split) {
+                    *reinterpret_cast<uint4*>(p.out_split + base + i) = gemv_mma::split_activations(o.x, o.y, o.z, o.w);
+                } else {
+                    *reinterpret_cast<float4*>(p.out + base + i) = o;
+                }
             }
         }
     } else {
         for (uint32_t i = tid; i < p.dim; i += kNormThreads) {
             const float r = row_value(base + i);
             if (p.n_partials) p.x_store[base + i] = r;
-            p.out[base + i] = __fdiv_rn(r, rms) * p.weight[i];
+            const float o = __fdiv_rn(r, rms) * p.weight[i];
+            if (p.out_split) store_split16(p.out_split + base, i, o);
+            else p.out[base + i] = o;
         }
     }
 }
@@ -220,17 +228,19 @@ extern "C" int attn_embed_q8_0(float* x, const void* table, const uint32_t* toke
     return ATTN_OK;
 }
 
-extern "C" int attn_rmsnorm_residual(float* out, float* x, const float* partials, uint32_t n_partials,
-                                     uint64_t partial_stride, const float* weight, uint32_t batch, uint32_t dim, float eps,
-                                     void* stream) {
-    if (!out || !x || !weight || batch == 0 || dim == 0 || (n_partials && !partials)) return ATTN_ERR_INVALID_ARG;
+namespace {
+int launch_rmsnorm(float* out, uint32_t* out_split, float* x, const float* partials, uint32_t n_partials,
+                   uint64_t partial_stride, const float* weight, uint32_t batch, uint32_t dim, float eps, void* stream) {
+    if ((!out && !out_split) || !x || !weight || batch == 0 || dim == 0 || (n_partials && !partials)) return ATTN_ERR_INVALID_ARG;
     if (n_partials && out == x) return ATTN_ERR_INVALID_ARG;  // the completed row and its norm are both kept
-    if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
-         reinterpret_cast<uintptr_t>(partials)) & 15u)
+    if (out_split && dim % 4 != 0) return ATTN_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out_split) | reinterpret_cast<uintptr_t>(x) |
+         reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(partials)) & 15u)
         return ATTN_ERR_ALIGNMENT;
     if (n_partials && partial_stride % 4 != 0) return ATTN_ERR_ALIGNMENT;
     NormParams p{};
     p.out = out;
+    p.out_split = out_split;
     p.x = x;
     p.x_store = x;
     p.partials = partials;
@@ -242,6 +252,19 @@ extern "C" int attn_rmsnorm_residual(float* out, float* x, const float* partials
     B200_CUDA_TRY(launch_dependent(rmsnorm_kernel, dim3(batch), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream), p));
     count_launch();
     return ATTN_OK;
+}
+}  // namespace
+
+extern "C" int attn_rmsnorm_residual(float* out, float* x, const float* partials, uint32_t n_partials,
+                                     uint64_t partial_stride, const float* weight, uint32_t batch, uint32_t dim, float eps,
+                                     void* stream) {
+    return launch_rmsnorm(out, nullptr, x, partials, n_partials, partial_stride, weight, batch, dim, eps, stream);
+}
+
+extern "C" int attn_rmsnorm_residual_split(uint32_t* out_split, float* x, const float* partials, uint32_t n_partials,
+                                           uint64_t partial_stride, const float* weight, uint32_t batch, uint32_t dim,
+                                           float eps, void* stream) {
+    return launch_rmsnorm(nullptr, out_split, x, partials, n_partials, partial_stride, weight, batch, dim, eps, stream);
 }
 
 extern "C" int attn_rmsnorm(float* out, const float* x, const float* weight, uint32_t batch, uint32_t dim, float eps,

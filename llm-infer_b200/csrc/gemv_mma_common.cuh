@@ -8,6 +8,7 @@
 #include <cuda_fp16.h>
 
 #include "attn_internal.cuh"
+#include "merge_device.cuh"
 #include "ptx_sm100.cuh"
 #include "tma_tile.cuh"
 
@@ -39,6 +40,7 @@ struct Params {
     float clip;
     int32_t out_dtype;
     int32_t accumulate;
+    int32_t x_split;          // x holds prepared activations (ATTN_DTYPE_SPLIT16 words) instead of fp32
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -132,6 +134,9 @@ __device__ __forceinline__ void reduce_and_store(const Params& p, const float* r
     if (p.out_dtype == ATTN_DTYPE_F32) {
         float* dst = reinterpret_cast<float*>(out) + o;
         *dst = p.accumulate ? *dst + v : v;
+    } else if (p.out_dtype == ATTN_DTYPE_SPLIT16) {
+        // a sequence's segment is a vector of its own: the group of four is counted from the segment's first row
+        store_split16(reinterpret_cast<uint32_t*>(out) + static_cast<size_t>(c) * stride, row - r0, v);
     } else {
         reinterpret_cast<__half*>(out)[o] = __float2half_rn(v);
     }
@@ -141,6 +146,8 @@ __device__ __forceinline__ void reduce_and_store(const Params& p, const float* r
 inline int check_fused_args(const AttnGemvArgs* a, uint32_t* k_split_out) {
     if (a->batch > 8) return ATTN_ERR_UNSUPPORTED;
     if (a->accumulate && a->out_dtype != ATTN_DTYPE_F32) return ATTN_ERR_UNSUPPORTED;
+    if (a->x_format != ATTN_DTYPE_F32 && a->x_format != ATTN_DTYPE_SPLIT16) return ATTN_ERR_INVALID_ARG;
+    if (a->out_dtype == ATTN_DTYPE_SPLIT16 && (a->d % 4 || a->split1 % 4 || a->split2 % 4 || a->k_split > 1)) return ATTN_ERR_UNSUPPORTED;
     if (a->swiglu && (a->d % kRows != 0 || a->split1 || a->split2)) return ATTN_ERR_UNSUPPORTED;
     const uint32_t k_split = a->k_split > 1 ? a->k_split : 1;
     if (k_split > 1 && (a->swiglu || a->split1 || a->accumulate || a->clip > 0.f || a->out_dtype != ATTN_DTYPE_F32))
@@ -173,6 +180,7 @@ inline void fill_common(Params& p, const AttnGemvArgs* a, uint32_t k_split) {
     p.clip = a->clip;
     p.out_dtype = a->out_dtype;
     p.accumulate = a->accumulate;
+    p.x_split = a->x_format == ATTN_DTYPE_SPLIT16;
 }
 
 }  // namespace gemv_mma

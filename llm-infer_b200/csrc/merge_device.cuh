@@ -16,9 +16,22 @@ struct MergeVec<2> { using type = float2; };
 template <>
 struct MergeVec<4> { using type = float4; };
 
+// One element of a vector in the prepared-activation form (ATTN_DTYPE_SPLIT16): element idx = 4r + e lives in the
+// 16-bit half (e & 1) of word 4r + (e >> 1) (fp16 value) and of word 4r + 2 + (e >> 1) (fp16 residual).
+__device__ __forceinline__ void store_split16(void* o, size_t idx, float x) {
+    x = fminf(fmaxf(x, -65504.f), 65504.f);
+    const __half hi = __float2half_rn(x);
+    const __half lo = __float2half_rn(x - __half2float(hi));
+    __half* words = reinterpret_cast<__half*>(o) + (idx & ~static_cast<size_t>(3)) * 2;  // 8 halves per group of 4
+    const size_t e = idx & 3;
+    words[(e >> 1) * 2 + (e & 1)] = hi;
+    words[4 + (e >> 1) * 2 + (e & 1)] = lo;
+}
+
 __device__ __forceinline__ void store_out(void* o, int32_t dtype, size_t idx, float x) {
     if (dtype == ATTN_DTYPE_F32) reinterpret_cast<float*>(o)[idx] = x;
     else if (dtype == ATTN_DTYPE_F16) reinterpret_cast<__half*>(o)[idx] = __float2half_rn(x);
+    else if (dtype == ATTN_DTYPE_SPLIT16) store_split16(o, idx, x);
     else reinterpret_cast<__nv_bfloat16*>(o)[idx] = __float2bfloat16_rn(x);
 }
 

@@ -69,6 +69,12 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     return pol;
 }
 
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
 // Untiled bulk copy global -> this CTA's shared memory, completion counted in
 // bytes on an mbarrier. Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,

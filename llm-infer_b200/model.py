@@ -117,10 +117,14 @@ class Llama:
         B, f32 = batch, torch.float32
         q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
         z = lambda *s, dtype=f32: torch.zeros(*s, dtype=dtype, device=dev)  # noqa: E731
-        self.x, self.xb = z(B, c.dim), z(B, c.dim)
+        self.x = z(B, c.dim)
+        # Activations that feed a GEMV: fp32, or with Q8_0 weights the prepared form (int32 words: fp16 value + fp16
+        # residual), written by the producing kernel so that no GEMV CTA has to convert them again
+        act = torch.int32 if q8 else f32
+        self.xb = z(B, c.dim, dtype=act)
         self.q, self.k, self.v = z(B, c.n_heads, c.head_dim), z(B, c.n_kv_heads, c.head_dim), z(B, c.n_kv_heads, c.head_dim)
-        self.att = z(B, c.n_heads, c.head_dim)
-        self.hb = z(B, c.hidden_dim)
+        self.att = z(B, c.n_heads, c.head_dim, dtype=act)
+        self.hb = z(B, c.hidden_dim, dtype=act)
         self.logits = z(B, c.vocab_size)
         self.next_token = z(B, dtype=torch.int32)
         self.tokens = z(B, dtype=torch.int32)   # the step's input tokens; a decode step writes its picks back here

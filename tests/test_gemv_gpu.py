@@ -243,3 +243,55 @@ def test_f16_batch_8_streams_weights_near_hbm_rate(attention):
     gbs = (d * n * 2 + 8 * (n * 4 + d * 4)) / us / 1e3
     print(f"gemv 14336x4096 fp16 batch 8: {us:.1f} us, {gbs:.0f} GB/s")
     assert gbs > 3000
+
+
+def _split16_words(x):
+    """numpy restatement of the prepared-activation form (ATTN_DTYPE_SPLIT16): per group of four elements the words
+    {hi(x0,x1), hi(x2,x3), lo(x0,x1), lo(x2,x3)}, hi = fp16(x), lo = fp16(x - hi)."""
+    x = np.clip(np.asarray(x, dtype=np.float32), -65504.0, 65504.0)
+    hi = x.astype(np.float16)
+    lo = (x - hi.astype(np.float32)).astype(np.float16)
+    h = hi.view(np.uint16).astype(np.uint32).reshape(*x.shape[:-1], -1, 4)
+    l = lo.view(np.uint16).astype(np.uint32).reshape(*x.shape[:-1], -1, 4)
+    words = np.stack([h[..., 0] | (h[..., 1] << 16), h[..., 2] | (h[..., 3] << 16),
+                      l[..., 0] | (l[..., 1] << 16), l[..., 2] | (l[..., 3] << 16)], axis=-1)
+    return words.reshape(x.shape).astype(np.uint32)
+
+
+def test_prepared_activations_from_every_producer(attention, pkg):
+    """RMSNorm, the Q8_0 GEMV (SwiGLU epilogue, row segments) and decode attention can write their result as prepared
+    activations (int32 tensors); the words are exactly the split of the fp32 result, and a GEMV fed with them gives
+    bit for bit what it gives when it converts the fp32 activations itself."""
+    import torch
+    from llm_infer_b200 import quant
+    rng = np.random.default_rng(123)
+    B, n, hidden = 8, 2048, 1024
+    x = torch.from_numpy(rng.standard_normal((B, n), dtype=np.float32) * 3).cuda()
+    wt = torch.from_numpy((1 + 0.1 * rng.standard_normal(n)).astype(np.float32)).cuda()
+    w13 = torch.from_numpy(quant.quantize_q8_0(rng.standard_normal((2 * hidden, n), dtype=np.float32) * 0.03)).cuda()
+    w2 = torch.from_numpy(quant.quantize_q8_0(rng.standard_normal((512, hidden), dtype=np.float32) * 0.03)).cuda()
+    # 1. RMSNorm
+    xb32 = attention.rmsnorm(x, wt, 1e-5, out=torch.empty_like(x))
+    xbw = attention.rmsnorm(x, wt, 1e-5, out=torch.empty((B, n), dtype=torch.int32, device="cuda"))
+    assert np.array_equal(xbw.cpu().numpy().view(np.uint32), _split16_words(xb32.cpu().numpy()))
+    # 2. GEMV reading prepared activations, writing fp32 and prepared activations (SwiGLU epilogue)
+    hb32 = attention.gemv_q8_0(xb32, w13, swiglu=True)
+    assert torch.equal(attention.gemv_q8_0(xbw, w13, swiglu=True), hb32)
+    hbw = attention.gemv_q8_0(xbw, w13, swiglu=True, out=torch.empty((B, hidden), dtype=torch.int32, device="cuda"))
+    assert np.array_equal(hbw.cpu().numpy().view(np.uint32), _split16_words(hb32.cpu().numpy()))
+    assert torch.equal(attention.gemv_q8_0(hbw, w2), attention.gemv_q8_0(hb32, w2))
+    # 3. row segments in prepared form
+    q32, k32 = torch.empty(B, 768, device="cuda"), torch.empty(B, 256, device="cuda")
+    qw, kw = (torch.empty(B, d, dtype=torch.int32, device="cuda") for d in (768, 256))
+    attention.gemv_q8_0(xbw, w13[:1024], out=q32, out2=k32)
+    attention.gemv_q8_0(xbw, w13[:1024], out=qw, out2=kw)
+    assert np.array_equal(qw.cpu().numpy().view(np.uint32), _split16_words(q32.cpu().numpy()))
+    assert np.array_equal(kw.cpu().numpy().view(np.uint32), _split16_words(k32.cpu().numpy()))
+    # 4. decode attention
+    H, Hkv, D, T = 8, 2, 128, 300
+    q = torch.randn(B, H, D, device="cuda")
+    kc, vc = torch.randn(B, T, Hkv, D, device="cuda").half(), torch.randn(B, T, Hkv, D, device="cuda").half()
+    o32 = attention.attn_decode(q, kc, vc)
+    ow = attention.attn_decode(q, kc, vc, out=torch.empty((B, H, D), dtype=torch.int32, device="cuda"))
+    assert np.array_equal(ow.cpu().numpy().view(np.uint32).reshape(B, H * D),
+                          _split16_words(o32.cpu().numpy().reshape(B, H * D)))
