@@ -88,9 +88,10 @@ __device__ __forceinline__ uint4 split_activations(float x0, float x1, float x2,
 }
 
 // This warp's four partial sums of a row group (rows g, g + 8; columns 2t, 2t + 1) into the reduction buffer.
+template <int WARPS = kWarps>
 __device__ __forceinline__ void store_partial(float* red, uint32_t part, uint32_t warp, uint32_t g, uint32_t t,
                                               const float (&tot)[4]) {
-    float* mine = red + (part * kWarps + warp) * 128;
+    float* mine = red + (part * WARPS + warp) * 128;
     mine[g * 8 + 2 * t] = tot[0];
     mine[g * 8 + 2 * t + 1] = tot[1];
     mine[(g + 8) * 8 + 2 * t] = tot[2];
@@ -100,16 +101,17 @@ __device__ __forceinline__ void store_partial(float* red, uint32_t part, uint32_
 // After the block-wide barrier that follows store_partial: threads 0..127 add the warps' partial sums of one row
 // group in a fixed order, carry them across slices in shared memory, and on the last slice apply the epilogue (SwiGLU
 // over the gate / up parts, clamp, row segment, accumulate or split-k partial output).
+template <int WARPS = kWarps>
 __device__ __forceinline__ void reduce_and_store(const Params& p, const float* red, float* s_acc, uint32_t tid,
                                                  uint32_t parts, uint32_t gi, uint32_t rg, uint32_t slice,
                                                  uint32_t slice_begin, uint32_t slice_end) {
     if (tid >= 128) return;
     float y[2] = {0.f, 0.f};
     for (uint32_t part = 0; part < parts; ++part) {
-        const float* src = red + part * kWarps * 128 + tid;
+        const float* src = red + part * WARPS * 128 + tid;
         float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) v += src[w * 128];
+        for (int w = 0; w < WARPS; ++w) v += src[w * 128];
         if (slice_end - slice_begin > 1) {
             float* carry = s_acc + (gi * 2 + part) * 128 + tid;
             if (slice > slice_begin) v += *carry;
