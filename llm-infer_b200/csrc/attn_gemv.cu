@@ -8,8 +8,9 @@
 // src/model/block.cpp:130-138 (both sides; the engine's GPU kernel clamps only from above, src/kernels.cu:218-227,
 // which the CPU path - the model of record - does not).
 //
-// HBM-bound: every weight byte is read exactly once per call, whatever the batch. One persistent CTA per SM, 16
-// warps; the activations of all sequences of the batch are staged once in shared memory (fp32); each warp owns
+// This file holds the kernel for ONE sequence with a plain output; batches and the fused forms (row segments, SwiGLU,
+// k_split) run on the tensor cores (attn_gemv_f16mma.cu). HBM-bound: every weight byte is read exactly once per call.
+// One persistent CTA per SM, 16 warps; the activations are staged once in shared memory (fp32); each warp owns
 // output rows j, j + #warps, ... and streams a row with 256-bit loads, eight in flight per lane (128 KB in flight per
 // SM), streaming (no-allocate) cache policy. Algorithmic bytes per call = d*n*2 + batch*(n*4 + d*sizeof(out)).
 #include "attn_internal.cuh"
@@ -150,9 +151,9 @@ extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
     DeviceInfo dev{};
     int rc = current_device_info(&dev);
     if (rc != ATTN_OK) return rc;
-    // The activations of one launch must fit in shared memory. A longer inner dimension (batch 8 x 14336 for the
-    // FFN's down projection) is covered by several launches over column slices of W, each adding to the output: the
-    // sums of the slices are added in a fixed order, so the result does not depend on scheduling.
+    // The activations of one launch must fit in shared memory. A longer inner dimension (beyond ~ 58 000 elements) is
+    // covered by several launches over column slices of W, each adding to the output: the sums of the slices are
+    // added in a fixed order, so the result does not depend on scheduling.
     const uint32_t slice_max = static_cast<uint32_t>(static_cast<size_t>(dev.max_smem_optin) / (a->batch * sizeof(float))) & ~511u;
     if (slice_max == 0) return ATTN_ERR_UNSUPPORTED;
     const uint32_t slices = (a->n + slice_max - 1) / slice_max;
@@ -174,16 +175,7 @@ extern "C" int attn_gemv_f16(const AttnGemvArgs* a, void* stream_v) {
         p.out_dtype = a->out_dtype;
         p.accumulate = (s > 0) ? 1 : a->accumulate;
         const size_t smem = static_cast<size_t>(a->batch) * p.n * sizeof(float);
-        switch (a->batch) {
-            case 1: rc = launch_gemv<1>(p, dev.sm_count, smem, stream); break;
-            case 2: rc = launch_gemv<2>(p, dev.sm_count, smem, stream); break;
-            case 3: rc = launch_gemv<3>(p, dev.sm_count, smem, stream); break;
-            case 4: rc = launch_gemv<4>(p, dev.sm_count, smem, stream); break;
-            case 5: rc = launch_gemv<5>(p, dev.sm_count, smem, stream); break;
-            case 6: rc = launch_gemv<6>(p, dev.sm_count, smem, stream); break;
-            case 7: rc = launch_gemv<7>(p, dev.sm_count, smem, stream); break;
-            default: rc = launch_gemv<8>(p, dev.sm_count, smem, stream); break;
-        }
+        rc = launch_gemv<1>(p, dev.sm_count, smem, stream);  // batches go to the tensor-core kernel above
         if (rc != ATTN_OK) return rc;
     }
     return ATTN_OK;
