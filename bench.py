@@ -562,7 +562,11 @@ def run_multi(args, world: int, rank: int, local_rank: int):
         if agree(ok):
             def graph_step(i):
                 graphs[i % n_sets].replay()
-            step, launch_mode = graph_step, "fused peer-store exchange, CUDA-graph replay"
+            paths["fused_peer_store_graph_ms"] = timed(graph_step, args.steps)
+            # Both are the product path; consecutive eager steps overlap through the dependent-launch chain, separate
+            # graph launches do not, so the faster one (the same on every rank: the times are maxima over ranks) is timed.
+            if paths["fused_peer_store_graph_ms"] <= paths["fused_peer_store_eager_ms"]:
+                step, launch_mode = graph_step, "fused peer-store exchange, CUDA-graph replay"
         else:
             graphs = None
     if step is None:
@@ -578,7 +582,7 @@ def run_multi(args, world: int, rank: int, local_rank: int):
         dist.barrier()
         ms = time_steps(torch, step, args.steps)
     launches = attention.kernel_launch_count() - launches0
-    if graphs is not None:
+    if graphs is not None and "graph" in launch_mode:
         launches = 2 * args.steps  # split pass + merge/exchange pass per replay (replays bypass the host-side counter)
     t = torch.tensor([ms], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
