@@ -29,9 +29,22 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one split-pass launch on the N=1 workload, from the ncu
-# capture summarised in profiles/ (None until a capture has been taken for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 272_322_304  # 268.65 MB read + 3.67 MB write, profiles/decode_split_c2_b16_kv4096.md
+
+def ncu_traffic_bytes():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one split-pass launch on the N=1 workload, recorded from a
+    profiler capture together with a hash of the kernel's sources; None when the sources have changed since."""
+    import hashlib
+    path = os.path.join(ROOT, "profiles", "decode_split_traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)
+        h = hashlib.sha256()
+        for rel in rec["kernel_sources"]:
+            with open(os.path.join(ROOT, rel), "rb") as f:
+                h.update(f.read())
+        return int(rec["traffic_bytes_per_launch"]) if h.hexdigest() == rec["sha256"] else None
+    except Exception:
+        return None
 
 
 def load_package():
@@ -117,12 +130,14 @@ class ClockSampler:
 # --------------------------------------------------------------------------- CPU baseline
 def cpu_reference_arm(wl, shape, steps: int, warmup: int, seconds_budget: float = 25.0):
     """Times the engine's CPU attention on a bounded sample of `shape` (whole sequences, or the first rows of one
-    long sequence). Returns (GB/s, description dict)."""
+    long sequence) on every core this process may use. Returns (GB/s, description dict, steps timed)."""
     import numpy as np
     import oracle
 
     chk = oracle.best()
     kind = "reference" if chk.kind == "reference" else "port"
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers: ask for the host's cores explicitly
+    cores = chk.set_num_threads(None)
     # sample: one sequence of the batch; long sequences are cut to 8192 rows so that one step stays well under 0.2 s
     rows = min(shape.kv_len, 8192)
     sample = wl.DecodeShape(shape.name + "-cpu-sample", shape.seed, 1, shape.n_heads, shape.n_kv_heads,
@@ -130,18 +145,24 @@ def cpu_reference_arm(wl, shape, steps: int, warmup: int, seconds_budget: float 
     q, k, v = wl.decode_inputs(sample)
     q32 = wl.widen(q, sample.q_dtype)
     k16, v16 = wl.as_f16_for_oracle(k, sample.kv_dtype), wl.as_f16_for_oracle(v, sample.kv_dtype)
-    for _ in range(max(1, warmup)):
+    # warm-up: at least `warmup` calls and half a second (thread pool spin-up, page faults, clock ramp)
+    t0 = time.perf_counter()
+    n = 0
+    while n < max(3, warmup) or time.perf_counter() - t0 < 0.5:
         chk.attn_decode(q32, k16, v16)
+        n += 1
+    # timed: at least `steps` calls and one second, at most the budget
     t0 = time.perf_counter()
     done = 0
-    for _ in range(steps):
+    while True:
         chk.attn_decode(q32, k16, v16)
         done += 1
-        if time.perf_counter() - t0 > seconds_budget:
+        el = time.perf_counter() - t0
+        if el > seconds_budget or (done >= steps and el >= 1.0):
             break
     dt = (time.perf_counter() - t0) / done
     gbs = sample.algorithmic_bytes() / dt / 1e9
-    desc = {"value": gbs, "unit": "GB/s", "cores": chk.num_threads(), "kind": kind,
+    desc = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
             "sample": f"1 sequence x {rows} KV rows of the workload per step, {done} steps, "
                       f"{dt * 1e3:.2f} ms/step; OpenMP over the {shape.n_heads} query heads as the engine does",
             "ms_per_step": dt * 1e3}
@@ -194,10 +215,10 @@ def prefill_measure(torch, attention, wl, steps: int, warmup: int, tflops_peak: 
         sets.append((q, k, v, torch.empty_like(q)))
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     res = {}
-    for name, fast in (("precise", False), ("fast", True)):
-        def step(i, fast=fast):
+    for name, mode in (("precise", 0), ("fast", 1)):
+        def step(i, mode=mode):
             q, k, v, o = sets[i % 2]
-            attention.attn_prefill_causal(q, k, v, out=o, fast=fast, status=status)
+            attention.attn_prefill_causal(q, k, v, out=o, p_mode=mode, status=status)
         for i in range(max(3, warmup)):
             step(i)
         ms = time_steps(torch, step, steps) / steps
@@ -208,26 +229,49 @@ def prefill_measure(torch, attention, wl, steps: int, warmup: int, tflops_peak: 
     return {"workload": shape.name, "dtype": "bf16 in, f32 accumulate, bf16 out", "causal_flops": shape.causal_flops,
             "peak_tflops": tflops_peak, "peak_kind": f"of {peak_kind} (cuBLAS bf16 burst)",
             "modes": res,
-            "note": "precise = probabilities as 16-bit value + residual (two PV MMAs), the mode that meets the "
-                    "parity tolerance; fast = one rounded 16-bit probability (outside the tolerance for bf16)"}
+            "note": "precise (the default) = probabilities as 16-bit value + residual (two PV MMAs), the mode that meets "
+                    "the parity tolerance on every row; fast = one probability rounded to bf16 (one PV MMA, outside "
+                    "the tolerance)"}
 
 
 # --------------------------------------------------------------------------- our arm, 1 GPU
 def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, prompt_range=(128, 2048), graph=True):
-    """End-to-end greedy generation with a random-init Llama-3-8B-shaped model stored as Q8_0 (32 layers, 4096,
-    32/8 heads of 128, FFN 14336, vocab 128256, theta 5e5): a ragged batch of 8 prompts with lengths uniform in
-    [128, 2048] (seeded random token ids), 128 new tokens each, token-at-a-time as the engine does, every step one
-    CUDA-graph launch. Weights are generated on the device from a seed (no checkpoint, no file)."""
+    """End-to-end greedy generation with a random-init Llama-3-8B-shaped model stored as a seed-generated Q8_0 GGUF
+    file (32 layers, 4096, 32/8 heads of 128, FFN 14336, vocab 128256, theta 5e5): the weights are generated on the
+    device from a seed, quantised, written as a GGUF v3 file the engine's parser accepts, and the model that runs is
+    loaded back from that file. A ragged batch of 8 prompts with lengths uniform in [128, 2048] (seeded random token
+    ids), 128 new tokens each, token-at-a-time as the engine does, every step one CUDA-graph launch."""
+    import shutil
+    import tempfile
+
     import numpy as np
+    from llm_infer_b200 import gguf
     from llm_infer_b200 import model as M
     rng = np.random.default_rng(seed)
     lengths = rng.integers(prompt_range[0], prompt_range[1] + 1, size=batch).tolist()
     cfg = M.ModelConfig(dim=4096, hidden_dim=14336, n_layers=32, n_heads=32, n_kv_heads=8, head_dim=128,
                         vocab_size=128256, max_seq_len=max(lengths) + n_new, norm_eps=1e-5, rope_theta=500000.0)
     w = M.random_weights(cfg, seed, device="cuda", weight_type="q8_0")
-    weight_bytes = sum(t.numel() * t.element_size() for k, t in w.items() if k != "embed")
-    llama = M.Llama(cfg, w, batch, weight_type="q8_0")
-    del w
+    # the file goes to memory-backed storage when there is room for it (9 GB), else to the temporary directory
+    roots = [d for d in ("/dev/shm", tempfile.gettempdir()) if os.path.isdir(d) and shutil.disk_usage(d).free > 12e9]
+    if not roots:
+        raise RuntimeError("no room for the 9 GB model file")
+    workdir = tempfile.mkdtemp(prefix="llm_infer_b200_", dir=roots[0])
+    path = os.path.join(workdir, "llama3-8b-shaped-seed%d.q8_0.gguf" % seed)
+    try:
+        t0 = time.perf_counter()
+        gguf.write_gguf(path, cfg, w, "q8_0")
+        write_s = time.perf_counter() - t0
+        file_bytes = os.path.getsize(path)
+        del w
+        torch.cuda.empty_cache()
+        t0 = time.perf_counter()
+        llama = M.Llama.from_gguf(path, batch)
+        torch.cuda.synchronize()
+        load_s = time.perf_counter() - t0
+    finally:
+        shutil.rmtree(workdir, ignore_errors=True)
+    weight_bytes = sum(t.numel() * t.element_size() for k, t in llama.w.items() if k != "embed")
     if graph:
         llama.capture()
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lengths]
@@ -236,11 +280,12 @@ def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, pro
     tokens = llama.generate(prompts, n_new, timing=timing)
     gen_ms = timing["generate_ms"] / max(1, timing["generate_steps"])
     res = {
-        "workload": "Llama-3-8B-shaped random-init model, Q8_0 weights (8.5 GB incl. embedding), batch 8, prompts "
-                    f"{lengths}, {n_new} new tokens each, greedy, token-at-a-time, one CUDA graph launch per step",
+        "workload": "Llama-3-8B-shaped random-init model loaded from a seed-generated Q8_0 GGUF file, batch 8, prompts "
+                    f"{lengths}, {n_new} new tokens each, greedy, one CUDA graph launch per step",
+        "gguf_file_bytes": file_bytes, "gguf_write_s": round(write_s, 2), "gguf_load_s": round(load_s, 2),
         "generate_tok_per_s": batch * 1e3 / gen_ms, "generate_ms_per_step": gen_ms,
         "prompt_tok_per_s": sum(lengths) * 1e3 / timing["prompt_ms"],
-        "prompt_ms_per_step": timing["prompt_ms"] / timing["prompt_steps"],
+        "prompt_ms": timing["prompt_ms"], "prompt_mode": timing.get("prompt_mode", "token-at-a-time"),
         "weight_bytes_per_decode_step": weight_bytes,
         "weight_stream_gbs": weight_bytes / (gen_ms * 1e-3) / 1e9,
         "distinct_tokens_generated": int(len(set(tokens.flatten().tolist()))),
@@ -283,6 +328,132 @@ def gemv_measure(torch, steps: int, warmup: int, hbm_peak: float, peak_kind: str
     res["note"] = (f"{d}x{n} matrix, eager back-to-back launches (host launch cost included when the kernel is "
                    f"shorter), frac of {peak_kind} HBM peak {hbm_peak:.1f} GB/s")
     return res
+
+
+def decode_trace(torch):
+    """Where the time of one attn_decode call goes. Needs the profiling build of the library (python
+    llm-infer_b200/build.py --trace, loaded through LLM_INFER_ATTN_LIB): its kernels store the GPU's nanosecond timer
+    at a few points per CTA. For each shape one flushed call is traced five times; printed are, in microseconds after
+    the first CTA of the split pass started, the median and the maximum over CTAs of every point, for the run with the
+    median total."""
+    import ctypes as C
+    from llm_infer_b200 import attention, binding
+    lib = binding.load()
+    if not hasattr(lib, "attn_trace_set_buffers"):
+        raise SystemExit("--decode-trace needs the profiling build: python llm-infer_b200/build.py --trace && "
+                         "LLM_INFER_ATTN_LIB=llm-infer_b200/libllm_infer_attn_trace.so python bench.py --decode-trace")
+    lib.attn_trace_set_buffers.argtypes = [C.c_void_p, C.c_void_p]
+    lib.attn_trace_set_buffers.restype = None
+    dev = torch.device("cuda", 0)
+    H, Hkv, D = 32, 8, 128
+    split_names = ["entry", "previous kernel done", "set-up done", "q in registers", "first K tile landed",
+                   "last tile computed", "partials written", "producer issued last copy"]
+    merge_names = ["entry", "split pass done, addresses ready", "partials folded", "row stored"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    tr_split = torch.zeros(1024 * 8, dtype=torch.int64, device=dev)
+    tr_merge = torch.zeros(4096 * 8, dtype=torch.int64, device=dev)
+    out = {}
+    # what the bracketing events cost by themselves: nothing between them, and one trivial kernel between them
+    floors = {"nothing": [], "one_trivial_kernel": []}
+    one = torch.zeros(32, device=dev)
+    for name in floors:
+        for _ in range(7):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if name != "nothing":
+                one.add_(1.0)
+            e1.record()
+            torch.cuda.synchronize()
+            floors[name].append(e0.elapsed_time(e1) * 1e3)
+        floors[name] = round(sorted(floors[name])[3], 2)
+    out["event_floor_us"] = floors
+    for b, t in ((1, 64), (1, 4096), (16, 4096), (1, 16384), (1, 32768), (1, 131072)):
+        q = torch.randn((b, H, D), device=dev).half()
+        k = torch.randn((b, t, Hkv, D), device=dev, dtype=torch.float16)
+        v = torch.randn((b, t, Hkv, D), device=dev, dtype=torch.float16)
+        o = torch.empty((b, H, D), device=dev)
+        ws = attention.DecodeWorkspace(b, H, Hkv, D, dev)
+        lib.attn_trace_set_buffers(None, None)
+        for _ in range(3):
+            attention.attn_decode(q, k, v, out=o, workspace=ws)
+        runs = []
+        for _ in range(5):
+            flush.zero_()
+            tr_split.zero_()
+            tr_merge.zero_()
+            torch.cuda.synchronize()
+            lib.attn_trace_set_buffers(tr_split.data_ptr(), tr_merge.data_ptr())
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            flush.zero_()
+            e0.record()
+            attention.attn_decode(q, k, v, out=o, workspace=ws)
+            e1.record()
+            torch.cuda.synchronize()
+            lib.attn_trace_set_buffers(None, None)
+            sp = tr_split.view(-1, 8).cpu().numpy().astype("int64")
+            mg = tr_merge.view(-1, 8).cpu().numpy().astype("int64")
+            sp = sp[sp[:, 0] > 0]
+            mg = mg[mg[:, 0] > 0]
+            t0 = int(sp[:, 0].min())
+            rec = {"event_us": round(e0.elapsed_time(e1) * 1e3, 2), "split_ctas": int(len(sp)),
+                   "split_ctas_with_tiles": int((sp[:, 5] > 0).sum()), "merge_ctas": int(len(mg)), "split": {}, "merge": {}}
+            for i, name in enumerate(split_names):
+                col = sp[:, i][sp[:, i] > 0]
+                if len(col):
+                    rel = (col - t0) / 1e3
+                    rec["split"][name] = [round(float(sorted(rel)[len(rel) // 2]), 2), round(float(rel.max()), 2)]
+            for i, name in enumerate(merge_names):
+                col = mg[:, i][mg[:, i] > 0]
+                if len(col):
+                    rel = (col - t0) / 1e3
+                    rec["merge"][name] = [round(float(rel.min()), 2), round(float(sorted(rel)[len(rel) // 2]), 2),
+                                          round(float(rel.max()), 2)]
+            rec["total_us_first_entry_to_last_store"] = round((int(mg[:, 3].max()) - t0) / 1e3, 2)
+            runs.append(rec)
+        runs.sort(key=lambda r: r["event_us"])
+        out[f"b{b}_kv{t}"] = runs[len(runs) // 2]
+        del q, k, v, o, ws
+    # The same stamps for the LAST of four back-to-back steps on rotated inputs (no flush, no events in between): how
+    # consecutive calls overlap through the programmatic-launch chain, with and without early K/V streaming.
+    b, t = 16, 4096
+    sets = [(torch.randn((b, H, D), device=dev).half(), torch.randn((b, t, Hkv, D), device=dev, dtype=torch.float16),
+             torch.randn((b, t, Hkv, D), device=dev, dtype=torch.float16)) for _ in range(3)]
+    o = torch.empty((b, H, D), device=dev)
+    ws = attention.DecodeWorkspace(b, H, Hkv, D, dev)
+    for early in (False, True):
+        runs = []
+        for _ in range(5):
+            tr_split.zero_()
+            tr_merge.zero_()
+            torch.cuda.synchronize()
+            lib.attn_trace_set_buffers(tr_split.data_ptr(), tr_merge.data_ptr())
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(4):
+                q, k, v = sets[i % 3]
+                attention.attn_decode(q, k, v, out=o, workspace=ws, kv_early=early)
+            e1.record()
+            torch.cuda.synchronize()
+            lib.attn_trace_set_buffers(None, None)
+            sp = tr_split.view(-1, 8).cpu().numpy().astype("int64")
+            mg = tr_merge.view(-1, 8).cpu().numpy().astype("int64")
+            sp, mg = sp[sp[:, 0] > 0], mg[mg[:, 0] > 0]
+            t0 = int(sp[:, 0].min())
+            rec = {"four_steps_event_us": round(e0.elapsed_time(e1) * 1e3, 2), "split": {}, "merge": {}}
+            for i, name in enumerate(split_names):
+                col = sp[:, i][sp[:, i] > 0]
+                rel = (col - t0) / 1e3
+                rec["split"][name] = [round(float(rel.min()), 2), round(float(sorted(rel)[len(rel) // 2]), 2), round(float(rel.max()), 2)]
+            for i, name in enumerate(merge_names):
+                col = mg[:, i][mg[:, i] > 0]
+                rel = (col - t0) / 1e3
+                rec["merge"][name] = [round(float(rel.min()), 2), round(float(sorted(rel)[len(rel) // 2]), 2), round(float(rel.max()), 2)]
+            runs.append(rec)
+        runs.sort(key=lambda r: r["four_steps_event_us"])
+        out[f"loop_b16_kv4096_last_of_4_steps_kv_early={early}"] = runs[len(runs) // 2]
+    print(json.dumps({"decode_trace": out, "legend": {"split": "[median, max] over CTAs, us after the first CTA's entry",
+                                                        "merge": "[min, median, max] over CTAs, same origin"}}), flush=True)
 
 
 def time_steps(torch, fn, steps: int):
@@ -466,11 +637,11 @@ def run_single(args):
         "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
-        "config": {**workload_config(shape, 1),
-                   "l2": f"inputs {shape.kv_bytes >> 20} MiB per step > 126 MB L2, {n_sets} input copies rotated"},
+        "config": workload_config(shape, 1),
+        "l2": f"inputs {shape.kv_bytes >> 20} MiB per step > 126 MB L2, {n_sets} input copies rotated",
         "tok_per_s": B / (ms_per_step * 1e-3),
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"of {peak_kind}",
+                     "traffic": ncu_traffic_bytes(), "peak_kind": f"of {peak_kind}",
                      "frac_of_nominal_8tbs": gbs / 8000.0, "algorithmic_bytes_per_launch": alg_bytes,
                      "note": "duration = CUDA-event time of one step (split pass + merge pass) / steps"},
         "cpu_baseline": cpu_baseline,
@@ -484,6 +655,7 @@ def run_single(args):
 
 # --------------------------------------------------------------------------- our arm, N GPUs
 def run_multi(args, world: int, rank: int, local_rank: int):
+    import numpy as np
     import torch
     import torch.distributed as dist
 
@@ -500,14 +672,21 @@ def run_multi(args, world: int, rank: int, local_rank: int):
     r0, r1 = shard_rows(T, world, rank)
     rows = r1 - r0
 
+    # The workload's own seeded inputs, generated on the host by every rank (so the CPU checker on rank 0 sees exactly
+    # the rows the GPUs hold); each rank keeps rows [r0, r1). Further copies of the shard (device-generated noise of
+    # the same shape) are rotated through so that a timed step never finds its rows in L2; copy 0 is the real one.
+    q_np, k_np, v_np = wl.decode_inputs(shape)
+    q = torch.from_numpy(q_np).to(dev)
     gen = torch.Generator(device=dev)
-    gen.manual_seed(shape.seed)  # same seed on every rank: Q is replicated
-    q = torch.randn((1, H, D), generator=gen, device=dev, dtype=torch.float32).half()
     gen.manual_seed(shape.seed * 1000 + rank + 1)
-    # rotate over enough copies of the shard that a step never finds its rows in L2
     n_sets = max(2, min(8, int(400e6 // (2 * rows * Hkv * D * 2)) + 1))
-    ks = [torch.randn((1, rows, Hkv, D), generator=gen, device=dev, dtype=torch.float16) for _ in range(n_sets)]
-    vs = [torch.randn((1, rows, Hkv, D), generator=gen, device=dev, dtype=torch.float16) for _ in range(n_sets)]
+    ks = [torch.from_numpy(np.ascontiguousarray(k_np[:, r0:r1])).to(dev)]
+    vs = [torch.from_numpy(np.ascontiguousarray(v_np[:, r0:r1])).to(dev)]
+    for _ in range(n_sets - 1):
+        ks.append(torch.randn((1, rows, Hkv, D), generator=gen, device=dev, dtype=torch.float16))
+        vs.append(torch.randn((1, rows, Hkv, D), generator=gen, device=dev, dtype=torch.float16))
+    if rank != 0:
+        del k_np, v_np
     out = torch.empty((1, H, D), dtype=torch.float32, device=dev)
 
     def agree(ok: bool) -> bool:
@@ -527,7 +706,8 @@ def run_multi(args, world: int, rank: int, local_rank: int):
 
     # ---- path A: NCCL all-gather between the local decode and the merge (three launches + one collective)
     nccl = ShardedDecode(H, D, device=dev)
-    nccl.use_workspace(attention.DecodeWorkspace(1, H, Hkv, D, dev))
+    ws_local = attention.DecodeWorkspace(1, H, Hkv, D, dev)
+    nccl.use_workspace(ws_local)
     out_a = out.view(H, D)
     for i in range(max(3, args.warmup)):
         nccl(q, ks[i % n_sets], vs[i % n_sets], out=out_a)
@@ -569,6 +749,8 @@ def run_multi(args, world: int, rank: int, local_rank: int):
                 step, launch_mode = graph_step, "fused peer-store exchange, CUDA-graph replay"
         else:
             graphs = None
+    else:
+        fused = None
     if step is None:
         def step(i):
             nccl(q, ks[i % n_sets], vs[i % n_sets], out=out_a)
@@ -589,35 +771,84 @@ def run_multi(args, world: int, rank: int, local_rank: int):
     ms_per_step = float(t.item()) / args.steps
     status_ok = fused is None or int(fused.workspace.status.item()) == 0
 
+    # ---- the fused step itemised: the local part alone (split pass + local merge, no exchange) against the whole
+    #      step; what the exchange and the cross-rank merge add is the difference
+    local_only_us = 1e3 * timed(lambda i: attention.attn_decode(q, ks[i % n_sets], vs[i % n_sets], out=out,
+                                                                workspace=ws_local), 50)
+    fused_items = {"local_split_and_merge_us": local_only_us, "whole_step_us": ms_per_step * 1e3,
+                   "exchange_and_cross_merge_us": ms_per_step * 1e3 - local_only_us,
+                   "streaming_floor_us": 2 * rows * Hkv * D * 2 / (hbm_peak * 1e3)}
+
+    # ---- parity, outside the timed region: the product path on the real rows (copy 0) against the engine's CPU
+    #      attn() over the UNSHARDED sequence; every rank's output is checked on rank 0
+    out.fill_(float("nan"))
+    if fused is not None:
+        fused(q, ks[0], vs[0], out=out)
+    else:
+        nccl(q, ks[0], vs[0], out=out_a)
+    torch.cuda.synchronize()
+    gathered = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered, out)
+    parity = None
+    if rank == 0:
+        import oracle
+        chk = oracle.best()
+        chk.set_num_threads(None)
+        want = chk.attn_decode(wl.widen(q_np, shape.q_dtype), k_np, v_np)
+        errs = [wl.error_metrics(g.cpu().numpy(), want) for g in gathered]
+        max_abs, max_rel = max(e[0] for e in errs), max(e[1] for e in errs)
+        finite = all(bool(torch.isfinite(g).all()) for g in gathered)
+        parity = {"max_abs": max_abs, "max_rel": max_rel, "abs_tol": wl.ABS_TOL, "rel_tol": wl.REL_TOL,
+                  "ok": bool(finite and max_abs <= wl.ABS_TOL and max_rel <= wl.REL_TOL), "ranks_checked": world,
+                  "checker": f"{chk.kind} attn() over all {T} rows on {chk.num_threads()} host threads",
+                  "rel_definition": "|a-b| / max(|b|, 1e-2*rms(b))"}
+
+    # ---- the same workload on ONE GPU, timed by rank 0 in this process while the other ranks wait: the like-for-like
+    #      point for strong scaling (two copies of the whole sequence rotated, 512 MiB each > L2)
+    strong = None
+    if rank == 0:
+        del ks, vs
+        torch.cuda.empty_cache()
+        kf = [torch.from_numpy(k_np).to(dev)]
+        vf = [torch.from_numpy(v_np).to(dev)]
+        kf.append(torch.randn((1, T, Hkv, D), generator=gen, device=dev, dtype=torch.float16))
+        vf.append(torch.randn((1, T, Hkv, D), generator=gen, device=dev, dtype=torch.float16))
+        out1 = torch.empty((1, H, D), dtype=torch.float32, device=dev)
+        for i in range(4):
+            attention.attn_decode(q, kf[i % 2], vf[i % 2], out=out1, workspace=ws_local)
+        n1 = max(20, min(args.steps, 100))
+        t1_ms = time_steps(torch, lambda i: attention.attn_decode(q, kf[i % 2], vf[i % 2], out=out1,
+                                                                  workspace=ws_local), n1) / n1
+        attention.attn_decode(q, kf[0], vf[0], out=out1, workspace=ws_local)
+        torch.cuda.synchronize()
+        e1 = wl.error_metrics(out1.cpu().numpy(), want)
+        strong = {"workload": shape.name, "t1_us": t1_ms * 1e3, "tN_us": ms_per_step * 1e3, "n_gpus": world,
+                  "speedup": t1_ms / ms_per_step, "efficiency": t1_ms / ms_per_step / world,
+                  "t1_parity": {"max_abs": e1[0], "max_rel": e1[1]},
+                  "note": "t1 = the whole sequence on one GPU (attn_decode, same process, same clocks), "
+                          "tN = this line's ms_per_step"}
+        del kf, vf
+    dist.barrier()
+
     # end to end with host buffers: q from pinned host memory, result read back, every step
+    if rank == 0:
+        ks = [torch.from_numpy(np.ascontiguousarray(k_np[:, r0:r1])).to(dev)]
+        vs = [torch.from_numpy(np.ascontiguousarray(v_np[:, r0:r1])).to(dev)]
+        n_sets_e2e = 1
+    else:
+        n_sets_e2e = n_sets
+    n_sets_e2e = int(torch.tensor([n_sets_e2e], device=dev).item())
     q_host = q.cpu().pin_memory()
     out_host = torch.empty((1, H, D), dtype=torch.float32).pin_memory()
 
-    # with the graph path, the host copies ride in the same graph launch as the step (one launch per token)
-    e2e_graphs = None
-    if graphs is not None:
-        try:
-            e2e_graphs = []
-            for j in range(n_sets):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    q.copy_(q_host, non_blocking=True)
-                    fused(q, ks[j], vs[j], out=out)
-                    out_host.copy_(out, non_blocking=True)
-                e2e_graphs.append(g)
-            ok = True
-        except Exception:
-            ok = False
-        if not agree(ok):
-            e2e_graphs = None
-
     def e2e_step(i):
-        if e2e_graphs is not None:
-            e2e_graphs[i % n_sets].replay()
+        q.copy_(q_host, non_blocking=True)
+        j = i % n_sets_e2e
+        if fused is not None:
+            fused(q, ks[j], vs[j], out=out)
         else:
-            q.copy_(q_host, non_blocking=True)
-            step(i)
-            out_host.copy_(out if fused is not None else out_a.view(1, H, D), non_blocking=True)
+            nccl(q, ks[j], vs[j], out=out_a)
+        out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_ms = timed(e2e_step, args.steps)
@@ -629,25 +860,32 @@ def run_multi(args, world: int, rank: int, local_rank: int):
             "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
-            "config": {**workload_config(shape, world), "exchange": launch_mode,
-                       "l2": f"{rows * Hkv * D * 4 >> 20} MiB of KV per GPU per step, {n_sets} copies rotated"},
+            "config": workload_config(shape, world),
+            "exchange": launch_mode,
+            "l2": f"{rows * Hkv * D * 4 >> 20} MiB of KV per GPU per step, {n_sets} copies rotated",
             "tok_per_s": 1.0 / (ms_per_step * 1e-3),
+            "parity": parity,
             "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": hbm_peak, "unit": "GB/s",
                          "frac": gbs / world / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
                          "note": "per GPU: algorithmic bytes / N / step time (local decode + exchange + merge)"},
             "e2e": {"value": alg_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": q.numel() * 2,
-                    "d2h_bytes_per_step": H * D * 4, "ms_per_step": e2e_ms},
+                    "d2h_bytes_per_step": H * D * 4, "ms_per_step": e2e_ms,
+                    "what": "q copied from pinned host memory, the sharded decode step, the result copied back and "
+                            "the stream synchronised, every step (eager launches)"},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
-            "extra": {"paths_ms_per_step": paths, "nccl_path_breakdown": parts, "status_ok": status_ok},
+            "extra": {"strong_scaling": strong, "fused_path_breakdown": fused_items, "paths_ms_per_step": paths,
+                      "nccl_path_breakdown": parts, "status_ok": status_ok},
         }
         print(json.dumps(line), flush=True)
+    ok = agree(rank != 0 or (parity is not None and parity["ok"] and status_ok))
     dist.barrier()
     torch.cuda.synchronize()
     # Tearing the process group down while captured graphs or symmetric-memory handles are alive can block;
-    # the line is printed, so leave directly.
+    # the line is printed, so leave directly (non-zero when the result was outside the tolerance).
     sys.stdout.flush()
-    os._exit(0)
+    sys.stderr.flush()
+    os._exit(0 if ok else 1)
 
 
 def main():
@@ -666,6 +904,8 @@ def main():
                     help="with --generate-only: launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--generate-short", action="store_true",
                     help="with --generate-only: prompts of 8-16 tokens and 8 new tokens (for profiler launch lists)")
+    ap.add_argument("--decode-trace", action="store_true",
+                    help="per-CTA time stamps of one attn_decode call (needs the profiling build, see decode_trace)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the resident-input steps of the 1-GPU workload (used for profiler captures)")
     args = ap.parse_args()
@@ -674,6 +914,11 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, max(world, args.gpus), rank)
+        return
+    if args.decode_trace:
+        import torch
+        load_package()
+        decode_trace(torch)
         return
     if args.gemv_only:
         import torch

@@ -73,7 +73,7 @@ enum {
  * attn() loop of src/model/block.cpp:157-164 for a whole batch at once. */
 typedef struct AttnDecodeArgs {
     void* o;       /* out: [batch][n_heads][head_dim], o_dtype */
-    const void* q; /* in : [batch][n_heads][head_dim], q_dtype (already RoPE'd) */
+    const void* q; /* in : [batch][n_heads][head_dim], q_dtype (already RoPE'd), 16-byte aligned */
     const void* k; /* in : kv_dtype, sequence b at k + b*kv_batch_stride, row t at + t*kv_row_stride */
     const void* v; /* in : same geometry as k */
     float* lse;    /* optional out: [batch][n_heads] natural-log sum-exp of the scaled scores
@@ -85,7 +85,9 @@ typedef struct AttnDecodeArgs {
     uint32_t n_heads;
     uint32_t n_kv_heads;
     uint32_t head_dim;       /* 64 or 128 */
-    const uint32_t* kv_len;  /* device pointer [batch], valid rows per sequence; NULL = kv_len_uniform for all */
+    const uint32_t* kv_len;  /* device pointer [batch], valid rows per sequence; NULL = kv_len_uniform for all. The
+                                values are read on the device and must not exceed the rows the caches hold: the
+                                kernel has no capacity to clamp them to */
     uint32_t kv_len_uniform; /* used when kv_len == NULL */
     uint64_t kv_row_stride;   /* elements between rows; 0 = n_kv_heads*head_dim */
     uint64_t kv_batch_stride; /* elements between sequences; may be 0 only when batch == 1 */
@@ -94,6 +96,12 @@ typedef struct AttnDecodeArgs {
     void* workspace;          /* device scratch, >= attn_decode_workspace_bytes(), 16-byte aligned */
     size_t workspace_bytes;
     uint32_t* status; /* optional device word, ATTN_STATUS_* bits are ORed in; NULL to skip */
+    uint32_t kv_early; /* != 0: the caller vouches that (i) kv_len[] / kv_len_uniform were in place before the previous
+                          kernel of the stream was launched and (ii) the only K/V row that kernel (or any kernel still
+                          running) writes is each sequence's LAST valid row, kv_len - 1 - true for the engine's step
+                          outside the sliding window, where the rotary kernel appends row pos just before attention
+                          (src/model/block.cu:147-161, src/model/model.cpp:65-68). The split pass then starts streaming
+                          every tile that cannot hold that row before it waits for the previous kernel. 0 = wait first. */
 } AttnDecodeArgs;
 
 /* Scratch size for attn_decode with these dimensions on the current device. */
@@ -120,12 +128,19 @@ typedef struct AttnPrefillArgs {
     uint32_t n_kv_heads;
     uint32_t head_dim;
     float scale;      /* 0 = 1/sqrt(head_dim) */
-    uint32_t fast;    /* 0: probabilities enter the tensor cores as a 16-bit value plus a 16-bit residual
-                         (two MMAs; fp32-level accuracy). 1: one rounded 16-bit value (one MMA). */
+    uint32_t p_mode;  /* how the probabilities P enter the tensor cores for the P.V product (ATTN_PREFILL_P_*) */
     uint32_t* status; /* optional device word for ATTN_STATUS_* bits */
-    float* debug_s_tile; /* optional device buffer [128][128]: raw Q.K^T of the first tile of the last rows of
-                            head 0 / sequence 0, for bring-up checks; NULL in normal use */
 } AttnPrefillArgs;
+
+enum {
+    /* P in the input type plus its rounding residual as a second MMA (~2^-17 per element): the mode that meets the
+     * parity tolerance on every row, short ones included. The default. */
+    ATTN_PREFILL_P_RESIDUAL = 0,
+    /* P rounded once to the input type (fp16: 2^-11, bf16: 2^-9 per element): one MMA per key block, two thirds of
+     * the tensor work. Within a few 1e-3 absolute, but rows with few keys miss the relative bound (their outputs pass
+     * through zero, where the bound is 1e-4 of the output's RMS). */
+    ATTN_PREFILL_P_INPUT_TYPE = 1
+};
 
 int attn_prefill_causal(const AttnPrefillArgs* args, void* stream);
 
@@ -260,19 +275,25 @@ int attn_decode_static_scratch(const AttnDecodeArgs* args, void* stream);
 /* Decode with the KV sequence of every sequence sharded across the GPUs of one NVLink box, exchange fused into the
  * merge pass (no counterpart in the reference, which is single-GPU: include/model/device.hpp:54,127-128). Each rank
  * calls this with its own rows in `decode` (same q on every rank). Two launches: the split pass over the local rows,
- * then one kernel that merges the local partials per row, stores the row's (O, LSE) into every rank's exchange
- * buffer with plain peer stores, raises a per-row flag on every rank, waits (bounded) for the other ranks' flags
- * for that row and merges the world_size records that arrived. decode.o / decode.lse receive the final result on
- * every rank.
+ * then one kernel whose CTAs each merge the local partials of one cell (an output row, or a 32/64-float slice of it),
+ * store the cell's values and the row's LSE into every rank's exchange buffer with plain 64-bit peer stores
+ * (each word = fp32 bits | step << 32, so a word is its own arrival flag: no fence, no separate flag), wait (bounded)
+ * until the words of the other ranks for that cell carry the current step, and merge the world_size records.
+ * decode.o / decode.lse receive the final result on every rank.
  *   peer_buffers[r]: device pointer, valid on THIS GPU, to rank r's exchange buffer (peer-mapped memory, e.g. a
  *                    symmetric allocation); peer_buffers[rank] is this rank's own buffer. Every buffer has
- *                    attn_decode_sharded_exchange_bytes() bytes and is zero before the first step.
+ *                    attn_decode_sharded_exchange_bytes() bytes, is 16-byte aligned and is zero before the first
+ *                    step. Layout in 64-bit words: rec[2 (step parity)][world_size (source rank)][cells] with
+ *                    cells = batch*n_heads * head_dim/c and c + 1 words per cell (c values, then the LSE),
+ *                    c = attn_decode_sharded_cell_floats(); then two control words (steps completed, cells
+ *                    finished in the running step).
  *   step           : 0 = the kernel counts steps itself in the exchange buffer (every rank must then make the same
  *                    sequence of calls on its buffer; the launch arguments stay constant, so the call can be
  *                    replayed from a CUDA graph). Otherwise 1, 2, 3, ...: the same value on every rank for the
  *                    same call, consecutive calls using consecutive values (records are double-buffered by the
- *                    parity of the step).
- *   poll_limit     : flag polls before a row gives up with ATTN_STATUS_WAIT_TIMEOUT in decode.status
+ *                    parity of the step; a peer can be at most one step ahead, so a record is never overwritten
+ *                    before it was read). Restarting the numbering needs freshly zeroed buffers.
+ *   poll_limit     : polls per word before a cell gives up with ATTN_STATUS_WAIT_TIMEOUT in decode.status
  *                    (0 = a default of about a second). The context stays usable after a timeout. */
 #define ATTN_MAX_PEERS 8
 typedef struct AttnDecodeShardedArgs {
@@ -285,6 +306,8 @@ typedef struct AttnDecodeShardedArgs {
 } AttnDecodeShardedArgs;
 
 size_t attn_decode_sharded_exchange_bytes(uint32_t batch, uint32_t n_heads, uint32_t head_dim, uint32_t world_size);
+/* Floats of head_dim per exchange cell for these dimensions (32, 64 or 128; 0 = unsupported head_dim). */
+uint32_t attn_decode_sharded_cell_floats(uint32_t batch, uint32_t n_heads, uint32_t head_dim);
 int attn_decode_sharded(const AttnDecodeShardedArgs* args, void* stream);
 
 /* Merge of n partial results with the engine's online-softmax state merge

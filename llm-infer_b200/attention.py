@@ -33,6 +33,17 @@ def _stream_ptr(stream) -> int:
     return s.cuda_stream
 
 
+def _dense(t: torch.Tensor, stream, what: str) -> torch.Tensor:
+    """``t`` itself when it is contiguous. Otherwise a contiguous copy, made on the current stream; with an explicit
+    ``stream`` that copy would not be ordered with the kernel that reads it (and its memory could be reused before the
+    kernel ran), so a non-contiguous operand is refused there."""
+    if t.is_contiguous():
+        return t
+    if stream is not None:
+        raise ValueError(f"{what} must be contiguous when an explicit stream is given")
+    return t.contiguous()
+
+
 def _require_cuda(*tensors: torch.Tensor) -> None:
     for t in tensors:
         if t is not None and not t.is_cuda:
@@ -55,7 +66,8 @@ class DecodeWorkspace:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
 
-def _decode_args(q, k_cache, v_cache, kv_len, out, lse, out_dtype, scale, workspace, max_ctas):
+def _decode_args(q, k_cache, v_cache, kv_len, out, lse, out_dtype, scale, workspace, max_ctas, stream=None,
+                 kv_early=False):
     """Validates the operands of a decode call and fills the C struct. Returns (args, out, workspace)."""
     _require_cuda(q, k_cache, v_cache)
     B, H, D = q.shape
@@ -66,7 +78,7 @@ def _decode_args(q, k_cache, v_cache, kv_len, out, lse, out_dtype, scale, worksp
         raise ValueError("K and V caches must share dtype and strides")
     if k_cache.stride(3) != 1 or k_cache.stride(2) != D:
         raise ValueError("cache layout must be [row][kv_head][head_dim] with dense heads")
-    q = q.contiguous()
+    q = _dense(q, stream, "q")
     if out is None:
         out = torch.empty((B, H, D), dtype=out_dtype, device=q.device)
     elif out.shape != (B, H, D) or not out.is_contiguous():
@@ -95,21 +107,26 @@ def _decode_args(q, k_cache, v_cache, kv_len, out, lse, out_dtype, scale, worksp
     a.max_ctas = int(max_ctas)
     a.workspace, a.workspace_bytes = workspace.buf.data_ptr(), workspace.nbytes
     a.status = workspace.status.data_ptr()
+    a.kv_early = int(bool(kv_early))
     return a, out, workspace, q
 
 
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len=None, *, out=None, lse=None,
                 out_dtype=torch.float32, scale: float = 0.0, workspace: DecodeWorkspace | None = None,
-                max_ctas: int = 0, stream=None) -> torch.Tensor:
+                max_ctas: int = 0, kv_early: bool = False, stream=None) -> torch.Tensor:
     """Single-token attention of every query head over its sequence's KV cache.
 
     q        [B, H, D]        fp32 / fp16 / bf16, already rotated
     k_cache  [B, T, Hkv, D]   fp16 / bf16; only the last dim must be dense, rows and sequences may be strided
     v_cache  same geometry as k_cache
-    kv_len   None (all T rows valid), an int, or an int32/uint32 CUDA tensor [B]
+    kv_len   None (all T rows valid), an int, or an int32/uint32 CUDA tensor [B]; the values of a tensor are read
+             on the device and are not checked against T: a length beyond the cache reads past it
+    kv_early True when the lengths were in place before the previous kernel of the stream was launched and that kernel
+             writes no K/V row other than each sequence's last valid one: streaming then starts before it has finished
     returns  out [B, H, D] in out_dtype; fills ``lse`` [B, H] (fp32) when given
     """
-    a, out, _, _q = _decode_args(q, k_cache, v_cache, kv_len, out, lse, out_dtype, scale, workspace, max_ctas)
+    a, out, _, _q = _decode_args(q, k_cache, v_cache, kv_len, out, lse, out_dtype, scale, workspace, max_ctas, stream,
+                                 kv_early)
     with torch.cuda.device(out.device):
         _b.check(_b.load().attn_decode(C.byref(a), _stream_ptr(stream)), "attn_decode")
     return out
@@ -121,7 +138,7 @@ def attn_decode_sharded(q, k_shard, v_shard, kv_len_local=None, *, peer_buffers,
     """Decode over this rank's KV rows with the cross-GPU exchange fused into the merge pass (C ABI
     ``attn_decode_sharded``). ``peer_buffers`` holds one device pointer per rank (as int) to that rank's exchange
     buffer, valid on this GPU; ``step = 0`` lets the kernel count steps itself. Returns the final out [B, H, D]."""
-    a, out, _, _q = _decode_args(q, k_shard, v_shard, kv_len_local, out, lse, out_dtype, scale, workspace, 0)
+    a, out, _, _q = _decode_args(q, k_shard, v_shard, kv_len_local, out, lse, out_dtype, scale, workspace, 0, stream)
     s = _b.AttnDecodeShardedArgs()
     s.decode = a
     s.world_size, s.rank, s.step, s.poll_limit = world_size, rank, step, poll_limit
@@ -136,14 +153,29 @@ def exchange_bytes(batch: int, n_heads: int, head_dim: int, world_size: int) -> 
     return int(_b.load().attn_decode_sharded_exchange_bytes(batch, n_heads, head_dim, world_size))
 
 
+def exchange_record(buffer: torch.Tensor, batch: int, n_heads: int, head_dim: int, world_size: int, parity: int,
+                    source_rank: int):
+    """Decodes one record of an exchange buffer (what ``source_rank`` delivered for the step of that parity):
+    returns (o [batch*n_heads, head_dim] fp32, lse [batch*n_heads] fp32, steps [cells, c+1] int64 = the step tag of
+    every word). For tests and debugging; the layout is described at attn_decode_sharded in the header."""
+    c = int(_b.load().attn_decode_sharded_cell_floats(batch, n_heads, head_dim))
+    rows, nsl = batch * n_heads, head_dim // c
+    rank_words = rows * nsl * (c + 1)
+    words = buffer.view(torch.int64)[(parity * world_size + source_rank) * rank_words:][:rank_words].view(rows, nsl, c + 1)
+    vals = words.contiguous().view(torch.float32).view(rows, nsl, c + 1, 2)[..., 0]  # low half of each word
+    return vals[..., :c].reshape(rows, head_dim), vals[:, 0, c].contiguous(), (words >> 32).view(rows * nsl, c + 1)
+
+
 def attn_prefill_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, out=None, out_dtype=None,
-                        scale: float = 0.0, fast: bool = False, status=None, debug_s_tile=None,
+                        scale: float = 0.0, p_mode: int = _b.PREFILL_P_RESIDUAL, status=None,
                         stream=None) -> torch.Tensor:
     """Causal attention of whole prompts: row t attends rows 0..t (the engine's token-at-a-time prefill,
     tools/infer.cpp:271-274, as one kernel).
 
     q [B, S, H, D], k / v [B, S, Hkv, D], fp16 or bf16, dense; D = 128. Returns out [B, S, H, D] in ``out_dtype``
-    (fp32 or the input dtype; default the input dtype).
+    (fp32 or the input dtype; default the input dtype). ``p_mode`` (binding.PREFILL_P_*) selects how the
+    probabilities enter the tensor cores: with a residual term (second MMA; the default and the parity mode) or
+    rounded once to the input type.
     """
     _require_cuda(q, k, v)
     lib = _b.load()
@@ -151,7 +183,7 @@ def attn_prefill_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, ou
     Hkv = k.shape[2]
     if k.shape != (B, S, Hkv, D) or v.shape != k.shape or not (q.dtype == k.dtype == v.dtype):
         raise ValueError("q, k, v must share batch, length, head_dim and dtype")
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q, k, v = _dense(q, stream, "q"), _dense(k, stream, "k"), _dense(v, stream, "v")
     if out is None:
         out = torch.empty((B, S, H, D), dtype=out_dtype or q.dtype, device=q.device)
     elif out.shape != (B, S, H, D) or not out.is_contiguous():
@@ -160,9 +192,8 @@ def attn_prefill_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, ou
     a.o, a.q, a.k, a.v = out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr()
     a.o_dtype, a.dtype = _dtype_code(out), _dtype_code(q)
     a.batch, a.seq_len, a.n_heads, a.n_kv_heads, a.head_dim = B, S, H, Hkv, D
-    a.scale, a.fast = float(scale), int(bool(fast))
+    a.scale, a.p_mode = float(scale), int(p_mode)
     a.status = status.data_ptr() if status is not None else None
-    a.debug_s_tile = debug_s_tile.data_ptr() if debug_s_tile is not None else None
     with torch.cuda.device(q.device):
         _b.check(lib.attn_prefill_causal(C.byref(a), _stream_ptr(stream)), "attn_prefill_causal")
     return out
@@ -183,7 +214,7 @@ def rope_kv_insert(q, k, v, k_cache, v_cache, pos, kv_pos, *, theta: float, rota
         raise ValueError("shape mismatch")
     if q.dtype != torch.float32 or k.dtype != torch.float32 or v.dtype != torch.float32 or k_cache.dtype != torch.float16:
         raise TypeError("q, k, v must be fp32 and the caches fp16")
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q, k, v = _dense(q, stream, "q"), _dense(k, stream, "k"), _dense(v, stream, "v")
     if q_out is None:
         q_out = torch.empty((B, H, D), dtype=q_out_dtype, device=q.device)
     a = _b.AttnRopeInsertArgs()
@@ -212,10 +243,12 @@ class HostDecodeStep:
     host_in   pinned fp32 [B*H*D + 2*B*Hkv*D]: q, then k, then v of the current token
     k_cache, v_cache  fp16 [B, T, Hkv, D] on the device; pos, kv_pos int32 [B] on the device
     out_host  pinned fp32 [B, H, D]
+    kv_early  True when every kv_pos[b] is the sequence's last valid row (the token is appended, no sliding window):
+              attention then starts streaming the older rows while the insert kernel still runs
     """
 
     def __init__(self, host_in, k_cache, v_cache, pos, kv_pos, out_host, *, n_heads: int, theta: float,
-                 rotary_dim: int = 0, kv_len=None, workspace: DecodeWorkspace | None = None):
+                 rotary_dim: int = 0, kv_len=None, workspace: DecodeWorkspace | None = None, kv_early: bool = False):
         if not (host_in.is_pinned() and out_host.is_pinned()):
             raise ValueError("host_in and out_host must be pinned host tensors")
         B, T, Hkv, D = k_cache.shape
@@ -237,7 +270,8 @@ class HostDecodeStep:
             self._dev_in.copy_(host_in, non_blocking=True)
             rope_kv_insert(q32, k32, v32, k_cache, v_cache, pos, kv_pos, theta=theta, rotary_dim=rotary_dim,
                            q_out=self._q_rot)
-            attn_decode(self._q_rot, k_cache, v_cache, kv_len, out=self._out, workspace=self.workspace)
+            attn_decode(self._q_rot, k_cache, v_cache, kv_len, out=self._out, workspace=self.workspace,
+                        kv_early=kv_early)
             out_host.copy_(self._out, non_blocking=True)
 
         with torch.cuda.device(dev):
@@ -266,7 +300,7 @@ def _gemv(entry: str, x, w, n: int, out, out2, out3, out_dtype, clip, accumulate
         raise ValueError("swiglu needs an even number of rows (gate rows, then up rows) and a single output")
     if out3 is not None and out2 is None:
         raise ValueError("out3 without out2")
-    x, w = x.contiguous(), w.contiguous()
+    x, w = _dense(x, stream, "x"), _dense(w, stream, "w")
     d = rows // 2 if swiglu else rows
     segs = [t for t in (out2, out3) if t is not None]
     d0 = d - sum(t.shape[1] for t in segs)

@@ -10,13 +10,15 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libllm_infer_attn.so")
+# LLM_INFER_ATTN_LIB may name another build of the same library (the profiling build of build.py --trace)
+LIB_PATH = os.environ.get("LLM_INFER_ATTN_LIB") or os.path.join(HERE, "libllm_infer_attn.so")
 
 ATTN_OK = 0
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 STATIC_SCRATCH_BYTES = 8 << 20
 STATUS_WAIT_TIMEOUT = 1
 STATUS_BAD_SHAPE = 2
+PREFILL_P_RESIDUAL, PREFILL_P_INPUT_TYPE = 0, 1
 
 # every symbol include/llm_infer_attn.h declares
 EXPORTED_SYMBOLS = (
@@ -24,6 +26,7 @@ EXPORTED_SYMBOLS = (
     "attn_decode",
     "attn_decode_static_scratch",
     "attn_decode_sharded_exchange_bytes",
+    "attn_decode_sharded_cell_floats",
     "attn_decode_sharded",
     "attn_merge",
     "attn_prefill_causal",
@@ -51,7 +54,28 @@ SYMBOL_HELPERS = (
     "attention_graph_add_node",
     "attention_graph_exec_update",
     "attention_launch",
+    "attention_status",
+    "kernels_b200_function",
+    "kernels_b200_launch_dims",
+    "kernels_b200_copy_embedding",
+    "kernels_b200_rmsnorm",
+    "kernels_b200_fused_gemv_clip",
+    "kernels_b200_rope",
 )
+# mangled names of the engine's __global__ symbols this library defines (include/kernels.cuh:9-26)
+ENGINE_KERNEL_SYMBOLS = (
+    "_Z20copy_embedding_floatPfPKfjj",
+    "_Z19copy_embedding_halfPfPK6__halfjj",
+    "_Z7rmsnormPfPKfS1_jf",
+    "_Z15fused_gemv_clipPfPKfPK6__halfjjSt8optionalIfE",
+    "_Z19fused_gemv_clip_f2hP6__halfPKfPKS_jjSt8optionalIfE",
+    "_Z8rope_f2fPfPKfjjjfj",
+    "_Z8rope_f2hP6__halfPKfjjjfj",
+    "_Z8rope_h2hP6__halfPKS_jjjfj",
+    "_Z9attentionPfPKfPK6__halfS4_j",
+)
+KERNEL_IDS = {"copy_embedding_float": 0, "copy_embedding_half": 1, "rmsnorm": 2, "fused_gemv_clip": 3,
+              "fused_gemv_clip_f2h": 4, "rope_f2f": 5, "rope_f2h": 6, "rope_h2h": 7}
 
 
 class AttnDecodeArgs(C.Structure):
@@ -77,6 +101,7 @@ class AttnDecodeArgs(C.Structure):
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
+        ("kv_early", C.c_uint32),
     ]
 
 
@@ -108,9 +133,8 @@ class AttnPrefillArgs(C.Structure):
         ("n_kv_heads", C.c_uint32),
         ("head_dim", C.c_uint32),
         ("scale", C.c_float),
-        ("fast", C.c_uint32),
+        ("p_mode", C.c_uint32),
         ("status", C.c_void_p),
-        ("debug_s_tile", C.c_void_p),
     ]
 
 
@@ -208,6 +232,8 @@ def load() -> C.CDLL:
     lib.attn_decode_static_scratch.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
     lib.attn_decode_sharded_exchange_bytes.restype = C.c_size_t
     lib.attn_decode_sharded_exchange_bytes.argtypes = [C.c_uint32] * 4
+    lib.attn_decode_sharded_cell_floats.restype = C.c_uint32
+    lib.attn_decode_sharded_cell_floats.argtypes = [C.c_uint32] * 3
     lib.attn_decode_sharded.restype = C.c_int
     lib.attn_decode_sharded.argtypes = [C.POINTER(AttnDecodeShardedArgs), C.c_void_p]
     lib.attn_prefill_causal.restype = C.c_int
@@ -262,6 +288,21 @@ def load() -> C.CDLL:
     lib.attention_graph_exec_update.restype = C.c_int
     lib.attention_graph_exec_update.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                 C.c_void_p, C.c_uint32]
+    lib.attention_status.restype = C.c_int
+    lib.attention_status.argtypes = [C.POINTER(C.c_uint32), C.c_int, C.c_void_p]
+    u32, vp, f32 = C.c_uint32, C.c_void_p, C.c_float
+    lib.kernels_b200_function.restype = vp
+    lib.kernels_b200_function.argtypes = [C.c_int]
+    lib.kernels_b200_launch_dims.restype = C.c_int
+    lib.kernels_b200_launch_dims.argtypes = [C.c_int, u32, C.POINTER(u32), C.POINTER(u32)]
+    lib.kernels_b200_copy_embedding.restype = C.c_int
+    lib.kernels_b200_copy_embedding.argtypes = [C.c_int, vp, vp, u32, u32, u32, u32, vp, vp, vp]
+    lib.kernels_b200_rmsnorm.restype = C.c_int
+    lib.kernels_b200_rmsnorm.argtypes = [vp, vp, vp, u32, f32, u32, u32, vp, vp, vp]
+    lib.kernels_b200_fused_gemv_clip.restype = C.c_int
+    lib.kernels_b200_fused_gemv_clip.argtypes = [C.c_int, vp, vp, vp, u32, u32, C.c_int, f32, u32, u32, vp, vp, vp]
+    lib.kernels_b200_rope.restype = C.c_int
+    lib.kernels_b200_rope.argtypes = [C.c_int, vp, vp, u32, u32, u32, f32, u32, u32, u32, vp, vp, vp]
     lib.attention_launch.restype = C.c_int
     lib.attention_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]
     _lib = lib

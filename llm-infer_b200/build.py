@@ -2,6 +2,8 @@
 
     python llm-infer_b200/build.py            # build if sources are newer than the library
     python llm-infer_b200/build.py --force
+    python llm-infer_b200/build.py --trace    # profiling build (libllm_infer_attn_trace.so): the decode kernels
+                                              # record time stamps per CTA; loaded when LLM_INFER_ATTN_LIB names it
 
 Only sm_100a code is generated. nvcc cross-compiles, so no GPU is needed to build.
 """
@@ -16,6 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libllm_infer_attn.so")
+TRACE_LIB = os.path.join(HERE, "libllm_infer_attn_trace.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -34,26 +37,28 @@ def _deps() -> list[str]:
         glob.glob(os.path.join(INCLUDE, "*.cuh"))
 
 
-def needs_build() -> bool:
-    if not os.path.exists(LIB):
+def needs_build(lib: str = LIB) -> bool:
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(lib)
     return any(os.path.getmtime(f) > t for f in _deps())
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    """Compile every .cu under csrc/ (one object per file, in parallel) and link the library."""
-    if not force and not needs_build():
-        return LIB
+def build_library(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """Compile every .cu under csrc/ (one object per file, in parallel) and link the library. ``trace`` builds the
+    profiling variant (-DATTN_TRACE) next to the product library, which it never replaces."""
+    lib = TRACE_LIB if trace else LIB
+    if not force and not needs_build(lib):
+        return lib
     nvcc = os.environ.get("NVCC", "nvcc")
-    objdir = os.path.join(HERE, "build")
+    objdir = os.path.join(HERE, "build_trace" if trace else "build")
     os.makedirs(objdir, exist_ok=True)
     procs = []
     objs = []
     for src in sources():
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-c", src, "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *(["-DATTN_TRACE"] if trace else []), "-I", INCLUDE, "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -65,9 +70,9 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         failed |= pr.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB, *objs])
-    return LIB
+    subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", lib, *objs])
+    return lib
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))

@@ -24,6 +24,8 @@ struct AttentionSymbolConfig {
     float* part_o;
     float* part_lse;
     uint32_t* counters;
+    uint32_t* status;     // one word of the workspace: ATTN_STATUS_* bits
+    uint32_t smem_bytes;  // dynamic shared memory the node must be launched with
 };
 
 __constant__ AttentionSymbolConfig g_cfg;
@@ -32,6 +34,7 @@ __constant__ AttentionSymbolConfig g_cfg;
 struct HostCfg {
     bool ok = false;
     uint32_t grid = 0, smem = 0;
+    uint32_t* status = nullptr;
 };
 HostCfg g_host_cfg[64];
 
@@ -48,6 +51,15 @@ attention(float* o, const float* q, const half* k, const half* v, uint32_t kv_to
     using namespace b200;
     extern __shared__ __align__(128) unsigned char smem[];
     const AttentionSymbolConfig& c = g_cfg;
+    // The body needs exactly this block size (8 consumer warps + the producer warp, named barriers over 256 threads)
+    // and the configured amount of dynamic shared memory (barriers and the K/V ring). A node added with the engine's
+    // old geometry (128 threads, no shared memory, src/model/block.cu:214-224) is refused here instead of touching
+    // shared memory it does not own: nothing is written except the status bit.
+    if (c.configured && (blockDim.x != static_cast<unsigned>(decode_detail::kThreads) || blockDim.y != 1 ||
+                         blockDim.z != 1 || gridDim.y != 1 || gridDim.z != 1 || dynamic_smem_bytes() < c.smem_bytes)) {
+        if (threadIdx.x == 0 && blockIdx.x == 0 && c.status) atomicOr(c.status, ATTN_STATUS_BAD_SHAPE);
+        return;
+    }
     if (!c.configured || kv_tokens == 0) {
         // kv_tokens == 0 cannot happen in the engine (kv_len >= 1); an unconfigured device is a host bug.
         if (kv_tokens == 0 && c.configured) {
@@ -78,7 +90,7 @@ attention(float* o, const float* q, const half* k, const half* v, uint32_t kv_to
     p.max_ctas = 0;
     p.min_tiles_per_cta = c.min_tiles_per_cta;
     p.nstages = c.nstages;
-    p.status = nullptr;
+    p.status = c.status;
     p.o = o;
     p.lse = nullptr;
     p.o_dtype = ATTN_DTYPE_F32;
@@ -152,7 +164,10 @@ int attention_configure(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim
     c.part_o = ws;
     c.part_lse = ws + plan.part_o_floats;
     c.counters = reinterpret_cast<uint32_t*>(ws + plan.part_o_floats + plan.part_lse_floats) + plan.prefix_words;
-    B200_CUDA_TRY(cudaMemsetAsync(c.counters, 0, static_cast<size_t>(plan.nseg) * 4, stream));
+    c.status = c.counters + ((static_cast<size_t>(plan.nseg) + 3) & ~3ull);
+    c.smem_bytes = static_cast<uint32_t>(plan.smem_bytes);
+    // counters (rounded up to four words) and the status word behind them start at zero
+    B200_CUDA_TRY(cudaMemsetAsync(c.counters, 0, (((static_cast<size_t>(plan.nseg) + 3) & ~3ull) + 4) * 4, stream));
     B200_CUDA_TRY(cudaMemcpyToSymbolAsync(g_cfg, &c, sizeof(c), 0, cudaMemcpyHostToDevice, stream));
     B200_CUDA_TRY(cudaStreamSynchronize(stream));  // c lives on this stack frame
     B200_CUDA_TRY(cudaFuncSetAttribute(attention, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -160,6 +175,18 @@ int attention_configure(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim
     g_host_cfg[dev].ok = true;
     g_host_cfg[dev].grid = plan.grid;
     g_host_cfg[dev].smem = static_cast<uint32_t>(plan.smem_bytes);
+    g_host_cfg[dev].status = c.status;
+    return ATTN_OK;
+}
+
+int attention_status(uint32_t* bits, int clear, void* stream_v) {
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    if (!bits || dev < 0 || dev >= 64 || !g_host_cfg[dev].ok) return ATTN_ERR_INVALID_ARG;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    B200_CUDA_TRY(cudaMemcpyAsync(bits, g_host_cfg[dev].status, 4, cudaMemcpyDeviceToHost, stream));
+    if (clear) B200_CUDA_TRY(cudaMemsetAsync(g_host_cfg[dev].status, 0, 4, stream));
+    B200_CUDA_TRY(cudaStreamSynchronize(stream));
     return ATTN_OK;
 }
 

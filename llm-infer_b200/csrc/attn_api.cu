@@ -1,6 +1,7 @@
 // C-ABI entry points (include/llm_infer_attn.h): argument validation, planning
 // and kernel launches. Nothing here allocates, frees or synchronises.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "attn_internal.cuh"
@@ -59,6 +60,11 @@ constexpr uint32_t kMinRowsPerCta = 64;
 // Largest number of partials per segment for which the last-arriving CTA merges them itself.
 constexpr uint32_t kFusedMaxParts = 0;
 
+#ifdef ATTN_TRACE
+unsigned long long* g_trace_split = nullptr;
+unsigned long long* g_trace_merge = nullptr;
+#endif
+
 }  // namespace
 }  // namespace b200
 
@@ -101,7 +107,7 @@ int decode_impl(const AttnDecodeArgs* a, void* stream_v, const Exchange* xchg) {
     const uint64_t row_stride = a->kv_row_stride ? a->kv_row_stride : static_cast<uint64_t>(a->n_kv_heads) * a->head_dim;
     if (row_stride < static_cast<uint64_t>(a->n_kv_heads) * a->head_dim) return ATTN_ERR_INVALID_ARG;
     // bulk copies need 16-byte aligned sources: 8 elements of 16 bits
-    if (!aligned16(a->k) || !aligned16(a->v) || row_stride % 8 != 0 || a->kv_batch_stride % 8 != 0)
+    if (!aligned16(a->k) || !aligned16(a->v) || !aligned16(a->q) || row_stride % 8 != 0 || a->kv_batch_stride % 8 != 0)
         return ATTN_ERR_ALIGNMENT;
     if (!a->workspace || a->workspace_bytes < plan.workspace_bytes) return ATTN_ERR_WORKSPACE;
     if (!aligned16(a->workspace)) return ATTN_ERR_ALIGNMENT;
@@ -129,9 +135,17 @@ int decode_impl(const AttnDecodeArgs* a, void* stream_v, const Exchange* xchg) {
     p.scale_log2 = scale * 1.4426950408889634f;
     p.q_dtype = a->q_dtype;
     p.max_ctas = a->max_ctas;
-    p.min_tiles_per_cta = (kMinRowsPerCta + plan.tile_rows - 1) / plan.tile_rows;
+    uint32_t min_rows = kMinRowsPerCta;
+#ifdef ATTN_TRACE
+    if (const char* e = getenv("ATTN_TRACE_MIN_ROWS")) min_rows = static_cast<uint32_t>(atoi(e));  // profiling knob
+#endif
+    p.min_tiles_per_cta = (min_rows + plan.tile_rows - 1) / plan.tile_rows;
     p.nstages = plan.nstages;
+    p.kv_early = a->kv_early ? 1u : 0u;
     p.status = a->status;
+#ifdef ATTN_TRACE
+    p.trace = g_trace_split;
+#endif
 
     const bool kv_bf16 = a->kv_dtype == ATTN_DTYPE_BF16;
     const bool qsplit = a->q_dtype != ATTN_DTYPE_F16;
@@ -172,13 +186,17 @@ int decode_impl(const AttnDecodeArgs* a, void* stream_v, const Exchange* xchg) {
     m.min_tiles_per_cta = p.min_tiles_per_cta;
     m.seg_prefix = p.seg_prefix;
     m.status = a->status;
+#ifdef ATTN_TRACE
+    m.trace = g_trace_merge;
+#endif
     if (xchg) {
         const AttnDecodeShardedArgs* s = xchg->s;
         m.xchg_world = s->world_size;
         m.xchg_rank = s->rank;
         m.xchg_step = s->step;
-        m.xchg_poll_limit = s->poll_limit ? s->poll_limit : (1u << 23);
-        for (uint32_t r = 0; r < s->world_size; ++r) m.xchg_peers[r] = static_cast<float*>(s->peer_buffers[r]);
+        m.xchg_poll_limit = s->poll_limit ? s->poll_limit : (1u << 21);
+        for (uint32_t r = 0; r < s->world_size; ++r)
+            m.xchg_peers[r] = static_cast<unsigned long long*>(s->peer_buffers[r]);
     }
     return launch_merge(m, stream, /*dependent_launch=*/true);
 }
@@ -190,9 +208,13 @@ int attn_decode(const AttnDecodeArgs* a, void* stream_v) { return decode_impl(a,
 
 size_t attn_decode_sharded_exchange_bytes(uint32_t batch, uint32_t n_heads, uint32_t head_dim, uint32_t world_size) {
     if (world_size == 0 || world_size > ATTN_MAX_PEERS) return 0;
-    const size_t rows = static_cast<size_t>(batch) * n_heads;
-    const size_t rec_floats = rows * (static_cast<size_t>(head_dim) + 1);
-    return (2 * world_size * rec_floats + static_cast<size_t>(world_size) * rows + 4) * 4;  // records, flags, 2 control words
+    if (batch == 0 || n_heads == 0 || head_dim == 0 || head_dim % 32 != 0) return 0;
+    return exchange_words(static_cast<uint64_t>(batch) * n_heads, head_dim, world_size) * 8;  // records + 2 control words
+}
+
+uint32_t attn_decode_sharded_cell_floats(uint32_t batch, uint32_t n_heads, uint32_t head_dim) {
+    if (batch == 0 || n_heads == 0 || head_dim == 0 || head_dim % 32 != 0) return 0;
+    return merge_slice_floats(static_cast<uint64_t>(batch) * n_heads, head_dim);
 }
 
 int attn_decode_sharded(const AttnDecodeShardedArgs* s, void* stream_v) {
@@ -241,6 +263,15 @@ const char* attn_status_string(int code) {
 }
 
 int attn_last_cuda_error(void) { return g_last_cuda_error; }
+
+#ifdef ATTN_TRACE
+// Profiling build only: device buffers that receive eight time stamps per CTA of the split pass and of the merge
+// pass of every following attn_decode / attn_decode_sharded call (null = off).
+void attn_trace_set_buffers(unsigned long long* split_pass, unsigned long long* merge_pass) {
+    g_trace_split = split_pass;
+    g_trace_merge = merge_pass;
+}
+#endif
 
 uint64_t attn_kernel_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
 

@@ -81,7 +81,8 @@ int make_decode_plan(uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint
     pl.nseg = static_cast<uint32_t>(nseg);
     pl.grid = static_cast<uint32_t>(dev.sm_count);
     const size_t tile_bytes = static_cast<size_t>(pl.tile_rows) * (static_cast<size_t>(pl.hpc) * head_dim * 2 + 16);
-    const size_t fixed = static_cast<size_t>(pl.nseg + 1) * 4 + 128;
+    // behind the ring: two more barriers, the query rows of one segment (fp32 at most), the tile prefix, two words
+    const size_t fixed = 16 + static_cast<size_t>(pl.hpc) * pl.group * head_dim * 4 + static_cast<size_t>(pl.nseg + 1) * 4 + 128;
     size_t budget = static_cast<size_t>(dev.max_smem_optin);
     if (budget < fixed + 2 * (2 * tile_bytes + 24)) return ATTN_ERR_UNSUPPORTED;
     size_t nst = (budget - fixed) / (2 * tile_bytes + 24);
@@ -92,9 +93,11 @@ int make_decode_plan(uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint
     const size_t rows = slots * pl.ts * pl.hpc * pl.group;
     pl.part_o_floats = rows * head_dim;
     pl.part_lse_floats = (rows + 3) & ~static_cast<size_t>(3);
-    // partials, LSEs, tile prefix [nseg+1], arrival counters [nseg] of the single-launch mode
+    // partials, LSEs, tile prefix [nseg+1], arrival counters [nseg] of the single-launch mode, four words of which
+    // the first is the status word of the engine's kernel symbol
     pl.prefix_words = (static_cast<size_t>(pl.nseg) + 1 + 3) & ~3ull;
-    pl.workspace_bytes = (pl.part_o_floats + pl.part_lse_floats + pl.prefix_words + ((static_cast<size_t>(pl.nseg) + 3) & ~3ull)) * 4;
+    pl.workspace_bytes =
+        (pl.part_o_floats + pl.part_lse_floats + pl.prefix_words + ((static_cast<size_t>(pl.nseg) + 3) & ~3ull) + 4) * 4;
     *plan = pl;
     return ATTN_OK;
 }

@@ -18,7 +18,11 @@
 //     pass writes every partial before the merge pass reads it, and the arrival counters that would
 //     have to start at zero belong to the single-launch kernel, which this entry point does not use;
 //   * the first call on a device looks up the array's device address (one cudaGetSymbolAddress with
-//     that device current, checked, cached). Make that first call outside any stream capture.
+//     that device current, checked, cached). Under CUDA's default lazy module loading this lookup
+//     is also the moment the module that holds the array is loaded and its 8 MiB are reserved, so
+//     the first call belongs at start-up: before the host gives the rest of the HBM away (later it
+//     could fail with out-of-memory, reported as ATTN_ERR_CUDA) and outside any stream capture.
+//     CUDA_MODULE_LOADING=EAGER moves the reservation to the time the library is loaded.
 #include "attn_internal.cuh"
 
 namespace {

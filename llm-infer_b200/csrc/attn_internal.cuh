@@ -46,12 +46,16 @@ struct DecodeParams {
     uint32_t max_ctas;
     uint32_t min_tiles_per_cta;
     uint32_t nstages;
+    uint32_t kv_early;     // AttnDecodeArgs.kv_early
     uint32_t* status;
     // single-launch (fused merge) mode only: final output and per-segment arrival counters
     void* o;
     float* lse;
     int32_t o_dtype;
     uint32_t* counters;  // [nseg], zero before the first launch; the kernel leaves them zero
+#ifdef ATTN_TRACE
+    unsigned long long* trace;  // [grid][8] time stamps, or null
+#endif
 };
 
 struct MergeParams {
@@ -79,17 +83,43 @@ struct MergeParams {
     uint32_t max_ctas;
     uint32_t min_tiles_per_cta;
     const uint32_t* seg_prefix;
-    // cross-GPU exchange (xchg_world > 0): the locally merged row is stored into every rank's exchange buffer over
-    // NVLink, a per-row flag is raised on each of them, and the row is finished by merging the xchg_world records
-    // that arrived in this GPU's own buffer. Buffer layout, in floats: rec[2 (step parity)][world][rows*(D+1)]
-    // (O rows, then LSE), followed by uint32 flags[world][rows].
-    float* xchg_peers[ATTN_MAX_PEERS];
+    // cross-GPU exchange (xchg_world > 0): every CTA stores its locally merged slice of a row (and the row's LSE) into
+    // every rank's exchange buffer over NVLink as 64-bit words {value, step}, then collects the xchg_world records of
+    // its own slice from this GPU's buffer, waiting (bounded) until each word carries the current step, and merges
+    // them. Buffer layout: see exchange_words().
+    unsigned long long* xchg_peers[ATTN_MAX_PEERS];
     uint32_t xchg_world;
     uint32_t xchg_rank;
     uint32_t xchg_step;
     uint32_t xchg_poll_limit;
     uint32_t* status;
+#ifdef ATTN_TRACE
+    unsigned long long* trace;  // [grid][8] time stamps, or null
+#endif
 };
+
+// Floats of head_dim that one CTA of the merge pass owns. Few output rows (one long sequence: 32 rows, each with a
+// partial per split-pass CTA) are cut into 32- or 64-float slices so that the pass fills the GPU and every thread
+// has all of its loads in flight at once; many rows (batched decode) keep whole rows per CTA. A function of the
+// shape only, so that all ranks of a sharded decode lay out their exchange buffers identically.
+__host__ __device__ inline uint32_t merge_slice_floats(uint64_t rows, uint32_t head_dim) {
+    constexpr uint64_t kMaxCtas = 592;  // four CTAs per SM of a 148-SM part
+    if (head_dim % 32 == 0 && rows * (head_dim / 32) <= kMaxCtas) return 32;
+    if (head_dim % 64 == 0 && rows * (head_dim / 64) <= kMaxCtas) return 64;
+    if (head_dim % 128 == 0) return 128;
+    return head_dim % 64 == 0 ? 64 : 32;
+}
+
+// Exchange buffer of the sharded decode, in 64-bit words: rec[2 (step parity)][world (source rank)][rows * nslices]
+// cells of (slice + 1) words each (the slice's values, then the row's LSE), each word = value bits | step << 32;
+// then two control words (steps completed, CTAs finished in the current step).
+__host__ __device__ inline uint64_t exchange_cell_words(uint32_t slice) { return static_cast<uint64_t>(slice) + 1; }
+__host__ __device__ inline uint64_t exchange_rank_words(uint64_t rows, uint32_t head_dim, uint32_t slice) {
+    return rows * (head_dim / slice) * exchange_cell_words(slice);
+}
+__host__ __device__ inline uint64_t exchange_words(uint64_t rows, uint32_t head_dim, uint32_t world) {
+    return 2ull * world * exchange_rank_words(rows, head_dim, merge_slice_floats(rows, head_dim)) + 2;
+}
 
 // Number of CTAs that actually take tiles, identical in the split and merge passes.
 __host__ __device__ inline uint32_t active_ctas(uint32_t grid, uint32_t max_ctas, uint32_t min_tiles, uint64_t nt) {

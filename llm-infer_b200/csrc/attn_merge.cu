@@ -7,12 +7,17 @@
 // and an all-empty row (every lse_i = -inf, where the reference computes 0/0)
 // yields zeros.
 //
-// One CTA per output row (batch x head); warps split the partials, lanes split head_dim. Two users:
+// One CTA per (output row, slice of head_dim). A thread owns four floats of the slice and every P-th partial; it
+// folds its partials into a running (m, z, acc) state exactly as the reference folds tiles, with the loads of up to
+// six partials (LSE and O together) in flight before the first is used, so a row with a partial per split-pass CTA
+// (one long sequence) costs one or two L2 round trips instead of a chain of them. Warps reduce with shuffles, the
+// eight warps through shared memory with one barrier. Two users:
 //   * the decode split pass (partials of consecutive slots, located per row),
 //   * attn_merge(): partials stacked with a constant stride, e.g. the all-gather
 //     buffer of the KV-sharded multi-GPU decode.
 // With an exchange descriptor (attn_decode_sharded) the same kernel also carries the collective of the multi-GPU
-// path: peer stores of the merged row, per-row flags, bounded wait, merge of the arrived records.
+// path: peer stores of the merged slice as self-validating 64-bit words, bounded wait for the other ranks' words,
+// merge of the arrived records.
 #include "attn_internal.cuh"
 #include "merge_device.cuh"
 #include "ptx_sm100.cuh"
@@ -23,30 +28,22 @@ namespace {
 
 constexpr int kMergeWarps = 8;
 constexpr int kMergeThreads = kMergeWarps * 32;
+constexpr int kLoadsInFlight = 6;
 
-// One CTA per output row. The eight warps take every eighth partial each (so that up to a few hundred
-// partials of a long single sequence are fetched with many loads in flight) and combine through shared memory.
-template <int VEC, int CHUNKS>
-__global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_constant__ MergeParams p) {
-    using V = typename MergeVec<VEC>::type;
-    constexpr int HEAD_DIM = CHUNKS * 32 * VEC;
-    __shared__ float s_red[2][kMergeWarps];
-    __shared__ float s_acc[kMergeWarps][HEAD_DIM];
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
-    const uint32_t row = blockIdx.x;
-    // Let the next kernel of the stream be scheduled (a weight GEMV starts prefetching), then wait for the grid that
-    // produced the partials (no-op without a programmatic dependency).
-    grid_dep_launch_dependents();
-    grid_dep_wait();
+#ifdef ATTN_TRACE
+#define MTRACE(k) ATTN_TRACE_AT((p.trace && threadIdx.x == 0) ? p.trace + static_cast<size_t>(blockIdx.x) * 8 : nullptr, k)
+#else
+#define MTRACE(k) \
+    do {          \
+    } while (0)
+#endif
 
-    const float* po;
-    const float* pl;
-    uint64_t o_stride, l_stride;
-    uint32_t n;
+// Where the partials of output row `row` are: n of them, partial i at po + i * o_stride (head_dim floats) with its
+// LSE at pl + i * l_stride. For the decode split pass these are the consecutive slots the pass wrote for the row's
+// segment; with ragged lengths the tile prefix is read, which that pass writes: the wait for it happens in here.
+__device__ __forceinline__ void locate_partials(const MergeParams& p, uint32_t row, const float*& po, const float*& pl,
+                                                uint64_t& o_stride, uint64_t& l_stride, uint32_t& n) {
     if (p.split_grid) {
-        // locate the consecutive slots the split pass wrote for this row's segment
         const uint32_t b = row / p.n_heads;
         const uint32_t h = row - b * p.n_heads;
         const uint32_t kvh = h / p.group;
@@ -57,6 +54,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
         const uint32_t seg = b * p.head_groups + hg;
         uint64_t nt, tile0, tile_end;
         if (p.kv_len) {
+            grid_dep_wait();  // the tile prefix is written by the split pass
             nt = p.seg_prefix[nseg];
             tile0 = p.seg_prefix[seg];
             tile_end = p.seg_prefix[seg + 1];
@@ -90,173 +88,325 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
         po = p.part_o + static_cast<uint64_t>(row) * p.head_dim;
         pl = p.part_lse + row;
     }
+}
 
-    // pass 1: L = max lse, Z = sum exp(lse - L) over all partials (L2-only loads: the producer grid may still
-    // have been running when this CTA started)
-    float mx = -INFINITY;
-    for (uint32_t i = tid; i < n; i += kMergeThreads) mx = fmaxf(mx, __ldcg(pl + i * l_stride));
-#pragma unroll
-    for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    if (lane == 0) s_red[0][warp] = mx;
-    __syncthreads();
-    mx = s_red[0][0];
-#pragma unroll
-    for (int w = 1; w < kMergeWarps; ++w) mx = fmaxf(mx, s_red[0][w]);
-    float z = 0.f;
-    if (mx != -INFINITY) {
-        for (uint32_t i = tid; i < n; i += kMergeThreads) z += __expf(__ldcg(pl + i * l_stride) - mx);
-    }
-#pragma unroll
-    for (int off = 16; off; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
-    if (lane == 0) s_red[1][warp] = z;
-    __syncthreads();
-    z = 0.f;
-#pragma unroll
-    for (int w = 0; w < kMergeWarps; ++w) z += s_red[1][w];
-    const float inv_z = z > 0.f ? 1.f / z : 0.f;
+// Many output rows with few partials each (batched decode: a row's segment is shared by a handful of split-pass
+// CTAs): two WARPS per row (even and odd partials), lanes over head_dim, the loads of up to six partials per warp in
+// flight - a dozen partials cost one L2 round trip - and one small exchange through shared memory. Registers and
+// shared memory are kept low enough that every CTA of this pass fits next to a split-pass CTA (which leaves about
+// 17 K registers and 13 KB of shared memory per SM) and is already waiting on its SM when that pass ends.
+constexpr int kRowsPerCta = kMergeWarps / 2;
 
-    // pass 2: warp w accumulates partials w, w + 8, ...
+template <int VEC, int CHUNKS>
+__global__ void __launch_bounds__(kMergeThreads, 4) merge_rows_kernel(const __grid_constant__ MergeParams p) {
+    using V = typename MergeVec<VEC>::type;
+    constexpr int kInFlight = CHUNKS == 1 ? 6 : 3;
+    constexpr int HEAD_DIM = CHUNKS * 32 * VEC;
+    __shared__ float s_mz[kRowsPerCta][2];
+    __shared__ __align__(16) float s_acc[kRowsPerCta][HEAD_DIM];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int sub = warp & 1;  // this warp folds partials sub, sub + 2, ...
+    const int rl = warp >> 1;
+    const uint32_t row = blockIdx.x * kRowsPerCta + rl;
+    const bool live = row < p.rows;
+    MTRACE(0);
+    grid_dep_launch_dependents();
+    const float* po = nullptr;
+    const float* pl = nullptr;
+    uint64_t o_stride = 0, l_stride = 0;
+    uint32_t n = 0;
+    if (live) locate_partials(p, row, po, pl, o_stride, l_stride, n);
+    grid_dep_wait();
+    MTRACE(1);
+    float m = -INFINITY, z = 0.f;
     float acc[CHUNKS][VEC];
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c)
 #pragma unroll
         for (int e = 0; e < VEC; ++e) acc[c][e] = 0.f;
-    if (mx != -INFINITY) {
-        // four partials per round, all eight loads (LSE and O) issued before any is used: with up to a few hundred
-        // partials per row (one long sequence) this loop is bound by L2 latency, not bandwidth
-        constexpr int kBatch = 4;
-        for (uint32_t i0 = warp; i0 < n; i0 += kMergeWarps * kBatch) {
-            float lw[kBatch];
-            V x[kBatch][CHUNKS];
+    for (uint32_t i0 = sub; i0 < n; i0 += 2 * kInFlight) {
+        float lw[kInFlight];
+        V x[kInFlight][CHUNKS];
 #pragma unroll
-            for (int b = 0; b < kBatch; ++b) {
-                const uint32_t i = i0 + b * kMergeWarps;
-                const bool valid = i < n;
-                lw[b] = valid ? __ldcg(pl + i * l_stride) : -INFINITY;
-                const float* src = po + (valid ? i : 0) * o_stride + lane * VEC;
+        for (int b = 0; b < kInFlight; ++b) {
+            const uint32_t i = i0 + 2 * b;
+            lw[b] = -INFINITY;
+            if (i < n) {
+                lw[b] = __ldcg(pl + i * l_stride);
+                const float* src = po + i * o_stride + lane * VEC;
 #pragma unroll
                 for (int c = 0; c < CHUNKS; ++c) x[b][c] = __ldcg(reinterpret_cast<const V*>(src + c * 32 * VEC));
             }
+        }
+        float bm = lw[0];
 #pragma unroll
-            for (int b = 0; b < kBatch; ++b) {
-                const float w = __expf(lw[b] - mx) * inv_z;  // 0 for the padding of the last round
+        for (int b = 1; b < kInFlight; ++b) bm = fmaxf(bm, lw[b]);
+        if (bm > m) {
+            const float s = __expf(m - bm);  // 0 when nothing was folded yet
+            z *= s;
 #pragma unroll
-                for (int c = 0; c < CHUNKS; ++c) {
-                    const float* xs = reinterpret_cast<const float*>(&x[b][c]);
+            for (int c = 0; c < CHUNKS; ++c)
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) acc[c][e] = fmaf(w, xs[e], acc[c][e]);
+                for (int e = 0; e < VEC; ++e) acc[c][e] *= s;
+            m = bm;
+        }
+        if (m != -INFINITY) {
+#pragma unroll
+            for (int b = 0; b < kInFlight; ++b) {
+                if (i0 + 2 * b < n) {
+                    const float w = __expf(lw[b] - m);  // 0 for an empty partial
+                    z += w;
+#pragma unroll
+                    for (int c = 0; c < CHUNKS; ++c) {
+                        const float* xs = reinterpret_cast<const float*>(&x[b][c]);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) acc[c][e] = fmaf(w, xs[e], acc[c][e]);
+                    }
                 }
             }
         }
     }
+    MTRACE(2);
+    // the odd warp hands its state (m, z, acc) to the even warp of the row, which merges the two and stores
+    if (sub == 1) {
+        if (lane == 0) {
+            s_mz[rl][0] = m;
+            s_mz[rl][1] = z;
+        }
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) s_acc[rl][c * 32 * VEC + lane * VEC + e] = acc[c][e];
+    }
+    __syncthreads();
+    if (sub == 1 || !live) return;
+    const float m1 = s_mz[rl][0], z1 = s_mz[rl][1];
+    const float mx = fmaxf(m, m1);
+    const float e0 = m == -INFINITY ? 0.f : __expf(m - mx), e1 = m1 == -INFINITY ? 0.f : __expf(m1 - mx);
+    const float zt = z * e0 + z1 * e1;
+    const float inv_z = zt > 0.f ? 1.f / zt : 0.f;
+    const size_t obase = static_cast<size_t>(row) * p.head_dim + lane * VEC;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c)
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) s_acc[warp][c * 32 * VEC + lane * VEC + e] = acc[c][e];
-    __syncthreads();
-    const float lse_local = z > 0.f ? mx + logf(z) : -INFINITY;
-    if (p.xchg_world == 0) {
-        for (int d = tid; d < HEAD_DIM; d += kMergeThreads) {
-            float x = 0.f;
-#pragma unroll
-            for (int w = 0; w < kMergeWarps; ++w) x += s_acc[w][d];
-            store_out(p.o, p.o_dtype, static_cast<size_t>(row) * HEAD_DIM + d, x);
+        for (int e = 0; e < VEC; ++e) {
+            const float v = acc[c][e] * e0 + s_acc[rl][c * 32 * VEC + lane * VEC + e] * e1;
+            store_out(p.o, p.o_dtype, obase + c * 32 * VEC + e, v * inv_z);
         }
-        if (p.lse && tid == 0) p.lse[row] = lse_local;
+    if (p.lse && lane == 0) p.lse[row] = zt > 0.f ? mx + logf(zt) : -INFINITY;
+    MTRACE(3);
+}
+
+// XCHG: the launch carries the cross-GPU exchange (its record buffer is only reserved then, so that the plain
+// pass keeps a small shared-memory footprint and fits next to a split-pass CTA).
+template <int SLICE, bool XCHG>
+__global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_constant__ MergeParams p) {
+    constexpr int LP = SLICE / 4;             // lanes that share one partial (a float4 each)
+    constexpr int P = kMergeThreads / LP;     // partials in flight per round of one load each
+    __shared__ float s_m[kMergeWarps];
+    __shared__ float s_z[kMergeWarps];
+    __shared__ __align__(16) float s_acc[kMergeWarps][SLICE];
+    __shared__ float s_out[SLICE + 1];
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int pg = tid / LP;  // which partials: pg, pg + P, ...
+    const int dl = tid % LP;  // which four floats of the slice
+    const uint32_t nslices = p.head_dim / SLICE;
+    const uint32_t row = blockIdx.x / nslices;
+    const uint32_t slice = blockIdx.x - row * nslices;
+    MTRACE(0);
+    // Let the next kernel of the stream be scheduled (a weight GEMV starts prefetching), then wait for the grid that
+    // produced the partials (no-op without a programmatic dependency).
+    grid_dep_launch_dependents();
+
+    const float* po;
+    const float* pl;
+    uint64_t o_stride, l_stride;
+    uint32_t n;
+    locate_partials(p, row, po, pl, o_stride, l_stride, n);
+    if (po) po += slice * SLICE + dl * 4;
+    grid_dep_wait();
+    MTRACE(1);
+
+    // ---- one sweep over this thread's partials (L2-only loads: the producer grid may still have been running when
+    //      this CTA started) ----
+    float m_t = -INFINITY, z_t = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (uint32_t i0 = pg; i0 < n; i0 += P * kLoadsInFlight) {
+        float lw[kLoadsInFlight];
+        float4 x[kLoadsInFlight];
+#pragma unroll
+        for (int b = 0; b < kLoadsInFlight; ++b) {
+            const uint32_t i = i0 + b * P;
+            const bool valid = i < n;
+            lw[b] = -INFINITY;
+            x[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (valid) {  // no load for the padding of the last round
+                lw[b] = __ldcg(pl + i * l_stride);
+                x[b] = __ldcg(reinterpret_cast<const float4*>(po + i * o_stride));
+            }
+        }
+        float bm = lw[0];
+#pragma unroll
+        for (int b = 1; b < kLoadsInFlight; ++b) bm = fmaxf(bm, lw[b]);
+        if (bm > m_t) {
+            const float s = __expf(m_t - bm);  // 0 when nothing was folded yet (m_t = -inf)
+            z_t *= s;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] *= s;
+            m_t = bm;
+        }
+        if (m_t != -INFINITY) {
+#pragma unroll
+            for (int b = 0; b < kLoadsInFlight; ++b) {
+                const float w = __expf(lw[b] - m_t);  // 0 for empty partials and for the padding of the last round
+                z_t += w;
+                acc[0] = fmaf(w, x[b].x, acc[0]);
+                acc[1] = fmaf(w, x[b].y, acc[1]);
+                acc[2] = fmaf(w, x[b].z, acc[2]);
+                acc[3] = fmaf(w, x[b].w, acc[3]);
+            }
+        }
+    }
+    MTRACE(2);
+
+    // ---- warp: common maximum, then sums over the partial groups of the warp ----
+    float m_w = m_t;
+#pragma unroll
+    for (int off = 16; off; off >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xffffffffu, m_w, off));
+    const float sc = m_t == -INFINITY ? 0.f : __expf(m_t - m_w);
+    float z_w = dl == 0 ? z_t * sc : 0.f;  // z_t is replicated over the LP lanes of a partial group
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] *= sc;
+#pragma unroll
+    for (int off = 16; off; off >>= 1) z_w += __shfl_xor_sync(0xffffffffu, z_w, off);
+#pragma unroll
+    for (int off = LP; off < 32; off <<= 1) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+    }
+    if (lane < LP) *reinterpret_cast<float4*>(&s_acc[warp][lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    if (lane == 0) {
+        s_m[warp] = m_w;
+        s_z[warp] = z_w;
+    }
+    __syncthreads();
+
+    // ---- CTA: the eight warp states merged by every thread that owns an output element ----
+    float mx = s_m[0];
+#pragma unroll
+    for (int w = 1; w < kMergeWarps; ++w) mx = fmaxf(mx, s_m[w]);
+    float z = 0.f, x_out = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMergeWarps; ++w) {
+        const float e = s_m[w] == -INFINITY ? 0.f : __expf(s_m[w] - mx);
+        z = fmaf(s_z[w], e, z);
+        if (tid < SLICE) x_out = fmaf(s_acc[w][tid], e, x_out);
+    }
+    const float inv_z = z > 0.f ? 1.f / z : 0.f;
+    x_out *= inv_z;
+    const float lse_local = z > 0.f ? mx + logf(z) : -INFINITY;
+    const size_t out_idx = static_cast<size_t>(row) * p.head_dim + slice * SLICE + tid;
+    if (!XCHG || p.xchg_world == 0) {
+        if (tid < SLICE) store_out(p.o, p.o_dtype, out_idx, x_out);
+        if (p.lse && slice == 0 && tid == 0) p.lse[row] = lse_local;
+        MTRACE(3);
         return;
     }
 
     // ---- cross-GPU part: compute step followed by its collective, in the same kernel -------------------------
-    // 1. store this rank's merged row into every rank's exchange buffer (plain stores to peer memory over NVLink),
-    // 2. system-scope fence, then raise this (rank, row)'s flag on every rank with a release store,
-    // 3. wait (bounded) until every rank's flag for this row shows the current step in the local buffer,
-    // 4. merge the records that arrived locally. Rows are independent, so a CTA waits for its own row only.
+    // 1. store this rank's merged slice and LSE into every rank's exchange buffer: plain 64-bit stores to peer
+    //    memory over NVLink, each word = value | step << 32, so a word is its own arrival flag (no fence, no
+    //    separate flag write);
+    // 2. collect the world records of this (row, slice) cell from the local buffer, polling (bounded) each word until
+    //    it carries the current step;
+    // 3. merge the records. Cells are independent, so a CTA waits for its own cell only.
+    // Records are double-buffered by step parity: a peer can be at most one step ahead (it needs this rank's
+    // record of step s+1 to finish s+1), so the cell of parity s is never overwritten before it was read.
     __shared__ uint32_t s_fail;
     __shared__ uint32_t s_step;
-    const uint32_t world = p.xchg_world, me = p.xchg_rank, rows = p.rows;
-    const size_t rec_floats = static_cast<size_t>(rows) * (HEAD_DIM + 1);
-    const size_t flags_off = 2 * static_cast<size_t>(world) * rec_floats;
-    // control words behind the flags of the local buffer: [0] = steps completed so far, [1] = rows finished in this step
-    uint32_t* ctl = reinterpret_cast<uint32_t*>(p.xchg_peers[me] + flags_off) + static_cast<size_t>(world) * rows;
+    __shared__ float s_rec[XCHG ? ATTN_MAX_PEERS : 1][SLICE + 1];
+    const uint32_t world = p.xchg_world, me = p.xchg_rank;
+    const uint64_t rank_words = exchange_rank_words(p.rows, p.head_dim, SLICE);
+    constexpr uint32_t kCell = SLICE + 1;
+    // control words behind the records of the local buffer: [0] = steps completed so far, [1] = CTAs finished in this step
+    unsigned long long* ctl = p.xchg_peers[me] + 2ull * world * rank_words;
     if (tid == 0) {
         s_fail = 0;
         // step 0 in the arguments = count steps on the device (keeps the launch arguments constant, e.g. for graph replay)
-        s_step = p.xchg_step ? p.xchg_step : *reinterpret_cast<volatile uint32_t*>(ctl) + 1u;
+        s_step = p.xchg_step ? p.xchg_step : static_cast<uint32_t>(*reinterpret_cast<volatile unsigned long long*>(ctl)) + 1u;
     }
+    if (tid < SLICE) s_out[tid] = x_out;
+    if (tid == 0) s_out[SLICE] = lse_local;
     __syncthreads();
     const uint32_t step = s_step;
-    const size_t rec_me = ((step & 1u) * world + me) * rec_floats;
-    // Every CTA of this launch has read the step by now or will before it finishes its own row, and the counter only
-    // advances after all rows have finished, so all rows of one launch agree on the step.
-    auto finish_row = [&]() {
+    // Every CTA of this launch has read the step by now or will before it finishes its own cell, and the counter only
+    // advances after all CTAs have finished, so all cells of one launch agree on the step.
+    auto finish_cell = [&]() {
         if (p.xchg_step == 0 && tid == 0) {
             __threadfence();
-            if (atomicAdd(ctl + 1, 1u) == rows - 1) {
+            if (atomicAdd(ctl + 1, 1ull) == gridDim.x - 1) {
                 ctl[1] = 0;
                 __threadfence();
-                atomicAdd(ctl, 1u);
+                atomicAdd(ctl, 1ull);
             }
         }
     };
-    for (int d = tid; d < HEAD_DIM; d += kMergeThreads) {
-        float x = 0.f;
-#pragma unroll
-            for (int w = 0; w < kMergeWarps; ++w) x += s_acc[w][d];
-        for (uint32_t r = 0; r < world; ++r) p.xchg_peers[r][rec_me + static_cast<size_t>(row) * HEAD_DIM + d] = x;
+    const uint64_t cell_off = (static_cast<uint64_t>(step & 1u) * world) * rank_words +
+                              static_cast<uint64_t>(blockIdx.x) * kCell;  // + source rank * rank_words
+    const unsigned long long tag = static_cast<unsigned long long>(step) << 32;
+    for (uint32_t idx = tid; idx < world * kCell; idx += kMergeThreads) {
+        const uint32_t r = idx / kCell, w = idx - r * kCell;
+        st_sys_u64(p.xchg_peers[r] + cell_off + me * rank_words + w, tag | __float_as_uint(s_out[w]));
     }
-    if (tid == 0) {
-        for (uint32_t r = 0; r < world; ++r) p.xchg_peers[r][rec_me + static_cast<size_t>(rows) * HEAD_DIM + row] = lse_local;
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < static_cast<int>(world)) {
-        uint32_t* remote = reinterpret_cast<uint32_t*>(p.xchg_peers[tid] + flags_off) + static_cast<size_t>(me) * rows + row;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(step) : "memory");
-        const uint32_t* local = reinterpret_cast<const uint32_t*>(p.xchg_peers[me] + flags_off) + static_cast<size_t>(tid) * rows + row;
+    MTRACE(3);
+    for (uint32_t idx = tid; idx < world * kCell; idx += kMergeThreads) {
+        const uint32_t r = idx / kCell, w = idx - r * kCell;
+        const unsigned long long* src = p.xchg_peers[me] + cell_off + r * rank_words + w;
         bool seen = false;
         for (uint32_t it = 0; it < p.xchg_poll_limit; ++it) {
-            uint32_t v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
-            if (v == step) { seen = true; break; }
-            __nanosleep(64);
+            const unsigned long long v = ld_sys_u64(src);
+            if (static_cast<uint32_t>(v >> 32) == step) {
+                s_rec[r][w] = __uint_as_float(static_cast<uint32_t>(v));
+                seen = true;
+                break;
+            }
+            if (it > 8) __nanosleep(40);
         }
         if (!seen) {
-            // a peer never delivered this row: report it and leave the output row untouched
+            // a peer never delivered this cell: report it and leave the output untouched
             if (p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
             atomicExch(&s_fail, 1u);
         }
     }
     __syncthreads();
+    MTRACE(4);
     if (s_fail) {
-        finish_row();
+        finish_cell();
         return;
     }
-    const float* mine = p.xchg_peers[me] + (step & 1u) * world * rec_floats;
     float gmx = -INFINITY;
-    for (uint32_t r = 0; r < world; ++r) gmx = fmaxf(gmx, __ldcg(mine + r * rec_floats + static_cast<size_t>(rows) * HEAD_DIM + row));
-    float gz = 0.f;
+    for (uint32_t r = 0; r < world; ++r) gmx = fmaxf(gmx, s_rec[r][SLICE]);
+    float gz = 0.f, acc_d = 0.f;
     if (gmx != -INFINITY) {
-        for (uint32_t r = 0; r < world; ++r) gz += __expf(__ldcg(mine + r * rec_floats + static_cast<size_t>(rows) * HEAD_DIM + row) - gmx);
-    }
-    const float inv_gz = gz > 0.f ? 1.f / gz : 0.f;
-    for (int d = tid; d < HEAD_DIM; d += kMergeThreads) {
-        float acc_d = 0.f;
-        if (gmx != -INFINITY) {
-            for (uint32_t r = 0; r < world; ++r) {
-                const float w = __expf(__ldcg(mine + r * rec_floats + static_cast<size_t>(rows) * HEAD_DIM + row) - gmx) * inv_gz;
-                acc_d = fmaf(w, __ldcg(mine + r * rec_floats + static_cast<size_t>(row) * HEAD_DIM + d), acc_d);
-            }
+        for (uint32_t r = 0; r < world; ++r) {
+            const float w = __expf(s_rec[r][SLICE] - gmx);  // 0 for a rank whose shard was empty
+            gz += w;
+            if (tid < SLICE) acc_d = fmaf(w, s_rec[r][tid], acc_d);
         }
-        store_out(p.o, p.o_dtype, static_cast<size_t>(row) * HEAD_DIM + d, acc_d);
     }
-    if (p.lse && tid == 0) p.lse[row] = gz > 0.f ? gmx + logf(gz) : -INFINITY;
-    finish_row();
+    if (tid < SLICE) store_out(p.o, p.o_dtype, out_idx, gz > 0.f ? acc_d / gz : 0.f);
+    if (p.lse && slice == 0 && tid == 0) p.lse[row] = gz > 0.f ? gmx + logf(gz) : -INFINITY;
+    finish_cell();
+    MTRACE(5);
 }
 
-template <int VEC, int CHUNKS>
-int launch_merge_vec(const MergeParams& p, cudaStream_t stream, bool dependent_launch) {
+template <int SLICE>
+int launch_merge_slice(const MergeParams& p, cudaStream_t stream, bool dependent_launch) {
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(p.rows);
+    cfg.gridDim = dim3(p.rows * (p.head_dim / SLICE));
     cfg.blockDim = dim3(kMergeThreads);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
@@ -267,7 +417,27 @@ int launch_merge_vec(const MergeParams& p, cudaStream_t stream, bool dependent_l
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_kernel<VEC, CHUNKS>, p));
+    if (p.xchg_world) B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_kernel<SLICE, true>, p));
+    else B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_kernel<SLICE, false>, p));
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return ATTN_OK;
+}
+
+template <int VEC, int CHUNKS>
+int launch_merge_rows(const MergeParams& p, cudaStream_t stream, bool dependent_launch) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((p.rows + kRowsPerCta - 1) / kRowsPerCta);
+    cfg.blockDim = dim3(kMergeThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (dependent_launch) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_rows_kernel<VEC, CHUNKS>, p));
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return ATTN_OK;
 }
@@ -276,13 +446,25 @@ int launch_merge_vec(const MergeParams& p, cudaStream_t stream, bool dependent_l
 
 int launch_merge(const MergeParams& p, cudaStream_t stream, bool dependent_launch) {
     if (p.rows == 0) return ATTN_OK;
-    const uint32_t d = p.head_dim;
-    // lanes own VEC consecutive floats of each 32*VEC chunk; head_dim is 1 or 2 chunks
-    if (d == 256) return launch_merge_vec<4, 2>(p, stream, dependent_launch);
-    if (d == 128) return launch_merge_vec<4, 1>(p, stream, dependent_launch);
-    if (d == 64) return launch_merge_vec<2, 1>(p, stream, dependent_launch);
-    if (d == 32) return launch_merge_vec<1, 1>(p, stream, dependent_launch);
-    return ATTN_ERR_UNSUPPORTED;
+    if (p.head_dim % 32 != 0) return ATTN_ERR_UNSUPPORTED;
+    // Many rows: the split pass's CTAs are shared out over many segments, so a row has few partials (on average
+    // (CTAs + segments) / segments of them) and a warp folds them alone; likewise a caller's short stack of partials.
+    const bool few_parts = p.split_grid ? p.rows >= 256 : (p.rows >= 256 && p.n_parts <= 16);
+    if (few_parts && p.xchg_world == 0) {
+        switch (p.head_dim) {
+            case 32: return launch_merge_rows<1, 1>(p, stream, dependent_launch);
+            case 64: return launch_merge_rows<2, 1>(p, stream, dependent_launch);
+            case 128: return launch_merge_rows<4, 1>(p, stream, dependent_launch);
+            case 256: return launch_merge_rows<4, 2>(p, stream, dependent_launch);
+            default: break;
+        }
+    }
+    switch (merge_slice_floats(p.rows, p.head_dim)) {
+        case 32: return launch_merge_slice<32>(p, stream, dependent_launch);
+        case 64: return launch_merge_slice<64>(p, stream, dependent_launch);
+        case 128: return launch_merge_slice<128>(p, stream, dependent_launch);
+        default: return ATTN_ERR_UNSUPPORTED;
+    }
 }
 
 }  // namespace b200

@@ -21,8 +21,12 @@
 //               softmax of one tile overlaps the tensor work of the other
 //   warps 10-11 idle (they only take part in the register re-allocation of their warpgroup)
 // Tensor memory (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each. P overwrites S in place as
-// packed 16-bit pairs: columns [0,64) the rounded value, [64,128) its residual (second MMA) when the
-// precise mode is on, which keeps P at ~2^-17 relative accuracy instead of bf16's 2^-9.
+// packed 16-bit pairs in columns [0,64). Two ways to hand P to the tensor cores (template PMODE):
+//   kPResidual  P in the input type plus its rounding residual in columns [64,128) and a second PV MMA: ~2^-17,
+//               the mode that meets the parity tolerance on every row (the default).
+//   kPInput     P rounded once to the input type (fp16: 2^-11, bf16: 2^-9 per element), one PV MMA.
+// A and B of one MMA must have the same 16-bit format: an fp16 P against a bf16 V (the instruction descriptor has
+// separate format fields) raises an illegal-instruction error on this part, so there is no such mode.
 // Online softmax follows the engine's state merge (src/attention.cu:41-65): running maximum m, sum l,
 // accumulator rescaled by exp(m_old - m_new); the rescale is skipped until the maximum has grown by more
 // than 2^8, and the true l normalises at the end, so the result is unchanged.
@@ -46,6 +50,9 @@ constexpr uint32_t kSubTileBytes = 128 * 64 * 2;       // [128 rows][64 elements
 constexpr uint32_t kTileBytes = 2 * kSubTileBytes;     // 128 x 128 16-bit elements
 constexpr int kStages = 2;
 constexpr uint32_t kTmemCols = 512;
+#ifdef ATTN_TRACE
+float* g_prefill_debug = nullptr;
+#endif
 
 struct PrefillParams {
     void* o;
@@ -55,10 +62,13 @@ struct PrefillParams {
     uint32_t m_tiles;     // ceil(seq / 128)
     uint32_t pair_heads;  // 1: tiles are heads (2*hp, 2*hp+1) at the same rows; 0: rows (2*mp, 2*mp+1) of one head
     float scale_log2;
-    uint32_t precise;  // 1: P = rounded + residual (two PV MMAs)
     uint32_t* status;
+#ifdef ATTN_TRACE
     float* debug;  // optional [128][128] dump of the first S tile of CTA (0,0,0)
+#endif
 };
+
+enum : int { kPResidual = 0, kPInput = 1 };
 
 // ---- barriers (8 bytes each) inside shared memory ----
 enum {
@@ -187,17 +197,17 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
            (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// Instruction descriptor of kind::f16: fp32 accumulate, A/B format fmt (0 = f16, 1 = bf16), A K-major,
-// B K-major (b_mn = 0) or MN-major (b_mn = 1), M = 128, N = 128.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn) {
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor of kind::f16: fp32 accumulate, A format a_fmt and B format b_fmt (0 = f16, 1 = bf16; always
+// given the same value here), A K-major, B K-major (b_mn = 0) or MN-major (b_mn = 1), M = 128, N = 128.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t a_fmt, uint32_t b_fmt, uint32_t b_mn) {
+    return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 }
 
 __device__ __forceinline__ void report_timeout(uint32_t* status) {
     if (status) atomicOr(status, ATTN_STATUS_WAIT_TIMEOUT);
 }
 
-template <bool BF16>
+template <bool BF16, int PMODE>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -286,10 +296,12 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tmem_ld32(tmem_s(t) + lane_addr + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
             }
             tmem_wait_ld();
+#ifdef ATTN_TRACE
             if (p.debug && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == gridDim.z - 1 && t == 0 && j == 0) {
 #pragma unroll
                 for (int c = 0; c < 128; ++c) p.debug[r * 128 + c] = s[c];
             }
+#endif
             // causal mask: only the diagonal block needs it (keys of later blocks are never visited)
             if (j * BN + BN - 1 > q_row) {
 #pragma unroll
@@ -341,9 +353,11 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     // Rounded pair by one packed convert; its fp32 value is recovered with integer / half-add
                     // operations so that no scalar convert (special-function pipe, already busy with exp2) is used.
                     hi[i] = pack2<BF16>(p0, p1);
-                    float h0, h1;
-                    unpack2<BF16>(hi[i], h0, h1);
-                    lo[i] = pack2<BF16>(p0 - h0, p1 - h1);
+                    if constexpr (PMODE == kPResidual) {
+                        float h0, h1;
+                        unpack2<BF16>(hi[i], h0, h1);
+                        lo[i] = pack2<BF16>(p0 - h0, p1 - h1);
+                    }
                 }
                 // 32 keys -> 16 packed columns: rounded part at column 16c, residual at 64 + 16c
                 asm volatile(
@@ -352,7 +366,7 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                       "r"(hi[5]), "r"(hi[6]), "r"(hi[7]), "r"(hi[8]), "r"(hi[9]), "r"(hi[10]), "r"(hi[11]), "r"(hi[12]),
                       "r"(hi[13]), "r"(hi[14]), "r"(hi[15])
                     : "memory");
-                if (p.precise) {
+                if constexpr (PMODE == kPResidual) {
                     asm volatile(
                         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                         ::"r"(tmem_s(t) + lane_addr + 64 + c * 16), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]),
@@ -464,8 +478,8 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         } else if (warp == 9 && lane == 0 && n_iter > 0) {
             // =============================== MMA issuer ===============================
             constexpr uint32_t fmt = BF16 ? 1u : 0u;
-            constexpr uint32_t idesc_qk = instr_desc(fmt, 0);
-            constexpr uint32_t idesc_pv = instr_desc(fmt, 1);
+            constexpr uint32_t idesc_qk = instr_desc(fmt, fmt, 0);
+            constexpr uint32_t idesc_pv = instr_desc(fmt, fmt, 1);
             // S_t = Q_t K^T: 8 MMAs of K = 16 over head_dim; operands K-major, 128-byte swizzle, 8-row groups 1024 B apart
             auto issue_qk = [&](int t, uint32_t st) {
                 const uint32_t qa = base + kSmemQ + t * kTileBytes;
@@ -486,7 +500,7 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     mma_ts(tmem_o(t), tmem_s(t) + kc * 8, smem_desc(va + kc * 2048, kSubTileBytes, 1024), idesc_pv,
                            accumulate || kc > 0);
                 }
-                if (p.precise) {
+                if constexpr (PMODE == kPResidual) {
 #pragma unroll
                     for (int kc = 0; kc < BN / 16; ++kc) {
                         mma_ts(tmem_o(t), tmem_s(t) + 64 + kc * 8, smem_desc(va + kc * 2048, kSubTileBytes, 1024),
@@ -606,9 +620,11 @@ extern "C" int attn_prefill_causal(const AttnPrefillArgs* a, void* stream_v) {
     p.pair_heads = (p.group % 2 == 0) ? 1u : 0u;
     const float scale = a->scale != 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(a->head_dim));
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.precise = a->fast ? 0u : 1u;
     p.status = a->status;
-    p.debug = a->debug_s_tile;
+#ifdef ATTN_TRACE
+    p.debug = g_prefill_debug;
+#endif
+    if (a->p_mode > 1) return ATTN_ERR_INVALID_ARG;
 
     dim3 grid;
     if (p.pair_heads) grid = dim3(a->n_heads / 2, a->batch, p.m_tiles);
@@ -626,5 +642,16 @@ extern "C" int attn_prefill_causal(const AttnPrefillArgs* a, void* stream_v) {
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
         return ATTN_OK;
     };
-    return a->dtype == ATTN_DTYPE_BF16 ? launch(prefill_causal_kernel<true>) : launch(prefill_causal_kernel<false>);
+    if (a->dtype == ATTN_DTYPE_BF16) {
+        return a->p_mode == ATTN_PREFILL_P_INPUT_TYPE ? launch(prefill_causal_kernel<true, kPInput>)
+                                                      : launch(prefill_causal_kernel<true, kPResidual>);
+    }
+    return a->p_mode == ATTN_PREFILL_P_INPUT_TYPE ? launch(prefill_causal_kernel<false, kPInput>)
+                                                  : launch(prefill_causal_kernel<false, kPResidual>);
 }
+
+#ifdef ATTN_TRACE
+// Profiling build only: [128][128] floats that receive the raw Q.K^T of the first key block of the last row tile of
+// head 0 / sequence 0 of every following attn_prefill_causal call (null = off).
+extern "C" void attn_trace_set_prefill_debug(float* s_tile) { g_prefill_debug = s_tile; }
+#endif

@@ -82,10 +82,55 @@ struct SegTable {
     }
 };
 
-__device__ __forceinline__ float load_q(const void* q, int32_t dtype, size_t idx) {
-    if (dtype == ATTN_DTYPE_F32) return reinterpret_cast<const float*>(q)[idx];
-    if (dtype == ATTN_DTYPE_F16) return __half2float(reinterpret_cast<const __half*>(q)[idx]);
-    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(q)[idx]);
+// Two consecutive elements of q as floats (one 4- or 8-byte load).
+template <typename T>
+__device__ __forceinline__ float2 load_q_pair(const T* p);
+template <>
+__device__ __forceinline__ float2 load_q_pair<float>(const float* p) {
+    return *reinterpret_cast<const float2*>(p);
+}
+template <>
+__device__ __forceinline__ float2 load_q_pair<__half>(const __half* p) {
+    return __half22float2(*reinterpret_cast<const __half2*>(p));
+}
+template <>
+__device__ __forceinline__ float2 load_q_pair<__nv_bfloat16>(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+// The A fragments (m16n8k16, row-major 16 x D) of one kv head's query heads for one lane: rows gq and gq + 8, columns
+// kc*16 + cq*2 + {0, 1, 8, 9}. The element type is fixed per instantiation and no data-dependent branch sits between
+// the pair loads, so the compiler issues them together and the fetch costs about one memory round trip (a
+// per-element load behind a run-time type switch serialised them: several microseconds per call). Rows past the G
+// real heads read row G-1 and are zeroed.
+template <typename T, int KC, bool QSPLIT, bool BF16>
+__device__ __forceinline__ void load_q_fragments(const T* q_head0, int D, int G, int gq, int cq, bool ghi,
+                                                 uint32_t (&qhi)[KC][4], uint32_t (&qlo)[QSPLIT ? KC : 1][4]) {
+    const int r0 = gq < G ? gq : G - 1;
+    const int r1 = gq + 8 < G ? gq + 8 : G - 1;
+    const T* p0 = q_head0 + static_cast<size_t>(r0) * D + cq * 2;
+    const T* p1 = q_head0 + static_cast<size_t>(r1) * D + cq * 2;
+    const float keep0 = gq < G ? 1.f : 0.f;
+    const float keep1 = gq + 8 < G ? 1.f : 0.f;
+#pragma unroll
+    for (int kc = 0; kc < KC; ++kc) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            // a0:(gq, k) a1:(gq+8, k) a2:(gq, k+8) a3:(gq+8, k+8), k = kc*16 + cq*2 + {0,1}
+            const bool hi_row = r & 1;
+            float x0 = 0.f, x1 = 0.f;
+            if (!hi_row || ghi) {  // ghi is uniform over the grid: no divergence, no load for rows that hold no head
+                const float2 v = load_q_pair<T>((hi_row ? p1 : p0) + kc * 16 + ((r >> 1) << 3));
+                const float keep = hi_row ? keep1 : keep0;
+                x0 = v.x * keep;
+                x1 = v.y * keep;
+            }
+            qhi[kc][r] = pack2<BF16>(x0, x1);
+            if constexpr (QSPLIT) {
+                qlo[kc][r] = pack2<BF16>(x0 - round16<BF16>(x0), x1 - round16<BF16>(x1));
+            }
+        }
+    }
 }
 
 template <int D, int HPC, bool QSPLIT, bool BF16, bool FUSED>
@@ -105,29 +150,57 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     const uint32_t nseg = p.batch * p.head_groups;
 
     unsigned char* tiles = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(nst) * 2 * TILEB);
-    uint32_t* prefix = reinterpret_cast<uint32_t*>(bars + 3 * nst);
-    // fused mode: one word behind the prefix area carries the arrival ticket from thread 0 to the other warps
+    // layout behind the tile ring: the query rows of the running segment (HPC*G rows of D elements, room for 4 bytes
+    // each; 16-byte aligned like the tiles, as a bulk copy needs), barriers [3*nst + 2], the tile prefix [nseg + 1]
+    // and two words of the single-launch mode (the arrival ticket carried from thread 0 to the other warps, and the
+    // "a wait ran out somewhere in this CTA" mark)
+    unsigned char* q_smem = smem + static_cast<size_t>(nst) * 2 * TILEB;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(q_smem + static_cast<size_t>(HPC) * p.group * D * 4);
+    uint32_t* prefix = reinterpret_cast<uint32_t*>(bars + 3 * nst + 2);
     volatile uint32_t* s_ticket = prefix + nseg + 1;
+    volatile uint32_t* s_abort = prefix + nseg + 2;
     const uint32_t bar_full_k = smem_u32(bars);
     const uint32_t bar_full_v = bar_full_k + 8 * nst;
     const uint32_t bar_empty = bar_full_v + 8 * nst;
+    const uint32_t bar_q_full = bar_empty + 8 * nst;
+    const uint32_t bar_q_empty = bar_q_full + 8;
     const uint32_t tiles_u32 = smem_u32(tiles);
+    const uint32_t q_esize = p.q_dtype == ATTN_DTYPE_F32 ? 4u : 2u;
+    const uint32_t q_seg_bytes = HPC * p.group * D * q_esize;  // the query rows of one segment are contiguous in q
 
+#ifdef ATTN_TRACE
+#define DTRACE(k) ATTN_TRACE_AT(p.trace ? p.trace + static_cast<size_t>(blockIdx.x) * 8 : nullptr, k)
+#else
+#define DTRACE(k) \
+    do {          \
+    } while (0)
+#endif
+    if (tid == 0) DTRACE(0);
     // The merge pass may be scheduled as soon as every CTA got here; it waits for
-    // this grid to finish before reading the partials. This grid in turn waits for
-    // the kernel before it (which wrote q and the newest cache row) before reading.
+    // this grid to finish before reading the partials.
     grid_dep_launch_dependents();
-    grid_dep_wait();
 
+    // Set-up that reads nothing another kernel writes runs while the previous kernel of the stream may still be
+    // finishing.
     if (tid == 0) {
         for (uint32_t s = 0; s < nst; ++s) {
             mbar_init(bar_full_k + 8 * s, 1);
             mbar_init(bar_full_v + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, kConsumerWarps);
         }
+        mbar_init(bar_q_full, 1);
+        mbar_init(bar_q_empty, kConsumerWarps);
         mbar_init_fence();
+        if constexpr (FUSED) *s_abort = 0u;
     }
+    // This grid waits for the kernel before it (which wrote q, the newest cache row and possibly the lengths) before
+    // it reads any of them. With kv_early the caller vouches that the lengths were in place before that kernel was
+    // launched and that the only cache row it writes is each sequence's last valid one: the wait then moves behind the
+    // tile prefix, and the producer warp starts the tiles that cannot hold that row before it waits (below), so the
+    // first K/V bytes are already on their way while the previous kernel finishes.
+    const bool early = p.kv_early != 0;
+    if (!early) grid_dep_wait();
+    if (tid == 0) DTRACE(1);
 
     // ---- tile prefix over segments (ragged lengths only) --------------------
     uint64_t nt;
@@ -157,6 +230,7 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         __syncthreads();
         nt = prefix[nseg];
         if (blockIdx.x == 0 && p.seg_prefix) {
+            if (early) grid_dep_wait();  // the previous kernel may still be reading the old table
             for (uint32_t s = tid; s <= nseg; s += kThreads) p.seg_prefix[s] = prefix[s];
         }
     } else {
@@ -165,6 +239,7 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         __syncthreads();
     }
     if (nt == 0) return;
+    if (tid == 0) DTRACE(2);
 
     const uint32_t active = active_ctas(gridDim.x, p.max_ctas, p.min_tiles_per_cta, nt);
     const uint32_t cta = blockIdx.x;
@@ -180,16 +255,12 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     if (warp == kConsumerWarps) {
         // ===================== producer warp =====================
         const uint64_t policy = l2_policy_evict_first();
-        for (uint32_t i = 0; i < n_my; ++i) {
-            const uint32_t gt = t_begin + i;
-            while (gt >= seg.tile_end) seg = table.load(seg.seg + 1);
+        const uint64_t q_policy = l2_policy_evict_last();  // a segment's query rows are read by every CTA that shares it
+        uint32_t q_seg = 0xffffffffu, n_seg = 0;           // segment whose query rows were requested last; segments so far
+
+        // One K tile and one V tile of `seg` into ring stage i % nst: a bulk copy per cache row.
+        auto issue_tile = [&](uint32_t i, uint32_t gt) {
             const uint32_t st = i % nst;
-            if (i >= nst) {
-                if (!mbar_wait(bar_empty + 8 * st, ((i / nst) - 1) & 1)) {
-                    if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
-                    return;
-                }
-            }
             const uint32_t tok0 = (gt - seg.tile0) * TT;
             const size_t seq_off = static_cast<size_t>(seg.b) * p.kv_batch_stride + static_cast<size_t>(seg.hg) * (HPC * D);
             const uint32_t kdst = tiles_u32 + st * 2 * TILEB;
@@ -216,11 +287,58 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
                 const uint16_t* src = p.v + seq_off + static_cast<size_t>(row) * p.kv_row_stride;
                 bulk_g2s(vdst + j * PITCH, src, ROWB, bar_full_v + 8 * st, policy);
             }
+        };
+        // The query rows of `seg` into their buffer (the previous segment's must have been taken).
+        auto issue_q = [&]() -> bool {
+            if (n_seg > 0 && !mbar_wait(bar_q_empty, (n_seg - 1) & 1)) {
+                if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+                return false;
+            }
+            if (lane == 0) {
+                const unsigned char* src = reinterpret_cast<const unsigned char*>(p.q) +
+                    (static_cast<size_t>(seg.b) * p.n_heads + static_cast<size_t>(seg.hg) * HPC * p.group) * D * q_esize;
+                mbar_arrive_expect_tx(bar_q_full, q_seg_bytes);
+                bulk_g2s(smem_u32(q_smem), src, q_seg_bytes, bar_q_full, q_policy);
+            }
+            q_seg = seg.seg;
+            ++n_seg;
+            return true;
+        };
+
+        uint32_t i = 0;
+        if (early) {
+            // Fill the ring before waiting for the previous kernel, stopping in front of a segment's last tile (the
+            // one that holds the row that kernel may be writing); a segment boundary is therefore never crossed here.
+            for (; i < n_my && i < nst; ++i) {
+                const uint32_t gt = t_begin + i;
+                if (gt + 1 >= seg.tile_end) break;
+                issue_tile(i, gt);
+            }
+            grid_dep_wait();
+            if (i > 0 && !issue_q()) return;  // the running segment's query rows, which that kernel produced
         }
+        for (; i < n_my; ++i) {
+            const uint32_t gt = t_begin + i;
+            while (gt >= seg.tile_end) seg = table.load(seg.seg + 1);
+            // The query rows travel in front of the segment's first tile, on the same copy engine: they land before the
+            // tile does, instead of queueing (as loads issued by the consumer warps did, for several microseconds)
+            // behind three stages of K/V traffic. One buffer: the consumers copy it into registers at the start of
+            // the segment and release it at once.
+            if (seg.seg != q_seg && !issue_q()) return;
+            if (i >= nst) {
+                if (!mbar_wait(bar_empty + 8 * (i % nst), ((i / nst) - 1) & 1)) {
+                    if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+                    return;
+                }
+            }
+            issue_tile(i, gt);
+        }
+        if (lane == 0) DTRACE(7);
         return;
     }
 
     // ===================== consumer warps =====================
+    if (early) grid_dep_wait();      // before the first partial is written and the query rows are used
     const int hh = warp / TS;        // kv head within the head group
     const int ts = warp - hh * TS;   // row sub-tile
     const int gq = lane >> 2;        // MMA row owned by this lane (and gq + 8)
@@ -237,33 +355,44 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     float o[DN][4];
     float m0, m1, l0, l1;  // running max (scaled, log2 domain) and sum for rows gq, gq + 8
 
-    auto begin_segment = [&]() {
-        const size_t head0 = (static_cast<size_t>(seg.b) * p.n_heads + (static_cast<size_t>(seg.hg) * HPC + hh) * G);
-#pragma unroll
-        for (int kc = 0; kc < KC; ++kc) {
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                // a0:(gq, k) a1:(gq+8, k) a2:(gq, k+8) a3:(gq+8, k+8), k = kc*16 + cq*2 + {0,1}
-                const int row = gq + ((r & 1) << 3);
-                const int col = kc * 16 + cq * 2 + ((r >> 1) << 3);
-                float x0 = 0.f, x1 = 0.f;
-                if (row < static_cast<int>(G)) {
-                    const size_t idx = (head0 + row) * D + col;
-                    x0 = load_q(p.q, p.q_dtype, idx);
-                    x1 = load_q(p.q, p.q_dtype, idx + 1);
-                }
-                qhi[kc][r] = pack2<BF16>(x0, x1);
-                if constexpr (QSPLIT) {
-                    qlo[kc][r] = pack2<BF16>(x0 - round16<BF16>(x0), x1 - round16<BF16>(x1));
-                }
-            }
+    uint32_t n_seg = 0;  // segments this CTA has started (parity of the query-row barriers)
+    bool failed = false;
+    // What a warp does when one of its bounded waits runs out: two-pass mode has no barrier after this point, so the
+    // warp simply leaves (its partials are missing and the status bit says so); in single-launch mode it stays, see
+    // fused_merge below.
+    auto wait_failed = [&]() {
+        if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+        if constexpr (FUSED) {
+            *s_abort = 1u;
+            failed = true;
         }
+    };
+
+    // Returns false when the wait for the query rows ran out.
+    auto begin_segment = [&]() -> bool {
+        if (!mbar_wait(bar_q_full, n_seg & 1)) {
+            wait_failed();
+            return false;
+        }
+        ++n_seg;
+        const size_t off = static_cast<size_t>(hh) * G * D;  // this warp's kv head inside the staged rows
+        if (p.q_dtype == ATTN_DTYPE_F16) {
+            load_q_fragments<__half, KC, QSPLIT, BF16>(reinterpret_cast<const __half*>(q_smem) + off, D, G, gq, cq, ghi, qhi, qlo);
+        } else if (p.q_dtype == ATTN_DTYPE_F32) {
+            load_q_fragments<float, KC, QSPLIT, BF16>(reinterpret_cast<const float*>(q_smem) + off, D, G, gq, cq, ghi, qhi, qlo);
+        } else {
+            load_q_fragments<__nv_bfloat16, KC, QSPLIT, BF16>(reinterpret_cast<const __nv_bfloat16*>(q_smem) + off, D, G, gq,
+                                                              cq, ghi, qhi, qlo);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_q_empty);
 #pragma unroll
         for (int dn = 0; dn < DN; ++dn) {
             o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.f;
         }
         m0 = m1 = -INFINITY;
         l0 = l1 = 0.f;
+        return true;
     };
 
     auto end_segment = [&]() {
@@ -298,16 +427,32 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     // Fused (single-launch) mode: the CTA that delivers the last partial of a segment merges it.
     // No CTA ever waits for another: each one adds 1 to the segment's counter after its partials are
     // visible, and whoever sees the final count does the merge and puts the counter back to zero.
+    // A consumer warp whose bounded wait ran out does not leave: it marks the CTA as aborted, stops computing and keeps
+    // walking the tile list so that it still meets the other warps at the named barriers below. An aborted CTA
+    // raises the status bit BEFORE it takes its ticket, and the CTA that takes a segment's last ticket reads the
+    // status word AFTER: the merge is skipped (output untouched, counters back to zero) whenever a partial is missing.
     auto fused_merge = [&]() {
         if constexpr (FUSED) {
             __threadfence();
             asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (tid == 0) *s_ticket = atomicAdd(p.counters + seg.seg, 1u);
+            if (tid == 0) {
+                if (*s_abort) {
+                    if (p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+                    __threadfence();
+                }
+                *s_ticket = atomicAdd(p.counters + seg.seg, 1u);
+            }
             asm volatile("bar.sync 1, 256;" ::: "memory");
             const uint32_t c_first = cta_of_tile(seg.tile0, nt, active);
             const uint32_t c_last = cta_of_tile(seg.tile_end - 1, nt, active);
             if (*s_ticket == c_last - c_first) {
                 __threadfence();
+                const bool poisoned =
+                    *s_abort || (p.status && (*reinterpret_cast<volatile uint32_t*>(p.status) & ATTN_STATUS_WAIT_TIMEOUT));
+                if (poisoned) {
+                    if (tid == 0) p.counters[seg.seg] = 0u;
+                    return;
+                }
                 const uint64_t first_slot = (static_cast<uint64_t>(c_first) + seg.seg) * TS;
                 const uint64_t l_stride = static_cast<uint64_t>(HPC) * G;
                 const uint32_t n = (c_last - c_first + 1) * TS;
@@ -322,15 +467,23 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         }
     };
 
-    begin_segment();
+    if (!begin_segment()) {
+        if constexpr (!FUSED) return;
+    }
+    if (warp == 0 && lane == 0) DTRACE(3);
 
     for (uint32_t i = 0; i < n_my; ++i) {
         const uint32_t gt = t_begin + i;
         if (gt >= seg.tile_end) {
-            end_segment();
+            if (!failed) end_segment();
             fused_merge();
             do { seg = table.load(seg.seg + 1); } while (gt >= seg.tile_end);
-            begin_segment();
+            if (!failed && !begin_segment()) {
+                if constexpr (!FUSED) return;
+            }
+        }
+        if constexpr (FUSED) {
+            if (failed) continue;
         }
         const uint32_t st = i % nst;
         const uint32_t par = (i / nst) & 1;
@@ -338,9 +491,10 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         const uint32_t vbase = kbase + TILEB;
 
         if (!mbar_wait(bar_full_k + 8 * st, par)) {
-            if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
-            return;
+            wait_failed();
+            if constexpr (FUSED) continue; else return;
         }
+        if (i == 0 && warp == 0 && lane == 0) DTRACE(4);
 
         // ---- S = Q K^T : 16 (heads) x 16 (rows of this sub-tile) ----
         float s[2][4];
@@ -423,8 +577,8 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         }
 
         if (!mbar_wait(bar_full_v + 8 * st, par)) {
-            if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
-            return;
+            wait_failed();
+            if constexpr (FUSED) continue; else return;
         }
 
         // ---- O += P V : 16 (heads) x D, contraction over this sub-tile's 16 rows ----
@@ -441,8 +595,11 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * st);
     }
-    end_segment();
+    if (warp == 0 && lane == 0) DTRACE(5);
+    if (!failed) end_segment();
+    if (warp == 0 && lane == 0) DTRACE(6);
     fused_merge();
+#undef DTRACE
 }
 
 }  // namespace decode_detail

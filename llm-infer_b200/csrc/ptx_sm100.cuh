@@ -143,4 +143,40 @@ __device__ __forceinline__ void grid_dep_launch_dependents() {
 }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// 64-bit system-scope accesses for records that another GPU writes into this GPU's memory (or the reverse) over
+// NVLink. A naturally aligned 64-bit scalar access is single-copy atomic, so a word that carries 32 bits of data and
+// a 32-bit step tag is never seen half-written: the reader needs no separate flag and the writer no fence.
+__device__ __forceinline__ void st_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint32_t dynamic_smem_bytes() {
+    uint32_t v;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(v));
+    return v;
+}
+
+// Time stamps of the profiling build (-DATTN_TRACE): a kernel stores the nanosecond timer at a few points per CTA
+// into a buffer registered with attn_trace_set_buffer(); the product build compiles none of it.
+#ifdef ATTN_TRACE
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define ATTN_TRACE_AT(buf, slot)                         \
+    do {                                                 \
+        if (buf) (buf)[slot] = ::b200::trace_now();      \
+    } while (0)
+#else
+#define ATTN_TRACE_AT(buf, slot) \
+    do {                         \
+    } while (0)
+#endif
+
 }  // namespace b200

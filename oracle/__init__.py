@@ -129,6 +129,17 @@ class Oracle:
     def num_threads(self) -> int:
         return int(self.lib.oracle_num_threads() if self.kind == "port" else self.lib.ref_num_threads())
 
+    def set_num_threads(self, n: int | None = None) -> int:
+        """OpenMP threads for the following calls; None = every core this process may run on (a launcher such as
+        torch.distributed.run exports OMP_NUM_THREADS=1 to its workers). Returns the count now in effect."""
+        if n is None:
+            n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        fn = self.lib.oracle_set_num_threads if self.kind == "port" else self.lib.ref_set_num_threads
+        fn.argtypes = [C.c_int]
+        fn.restype = None
+        fn(int(n))
+        return self.num_threads()
+
     def f32_to_f16(self, x: float) -> int:
         return int(self.lib.oracle_f32_to_f16(x) if self.kind == "port" else self.lib.ref_f32_to_f16(x))
 
@@ -200,10 +211,11 @@ class Oracle:
 
     # -- the small per-token steps (port only; the reference versions run inside generate_greedy) --
     def rmsnorm(self, x, weight, eps) -> np.ndarray:
-        assert self.kind == "port"
         x, weight = _f32(x), _f32(weight)
         out = np.empty_like(x)
-        self.lib.oracle_rmsnorm(_ptr(out, _f32p), _ptr(x, _f32p), _ptr(weight, _f32p), x.size, eps)
+        fn = self.lib.oracle_rmsnorm if self.kind == "port" else self.lib.ref_rmsnorm
+        fn.argtypes = [_f32p, _f32p, _f32p, C.c_uint32, C.c_float]
+        fn(_ptr(out, _f32p), _ptr(x, _f32p), _ptr(weight, _f32p), x.size, eps)
         return out
 
     def swiglu(self, hb, hb2) -> np.ndarray:

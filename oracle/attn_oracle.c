@@ -123,6 +123,16 @@ int oracle_num_threads(void) {
 #endif
 }
 
+/* A launcher may export OMP_NUM_THREADS=1 to its workers (torch.distributed.run does); the timed CPU baseline asks
+ * for the host's cores explicitly. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* -------------------------------------------------------------------- softmax */
 
 /* kernels_cpu.hpp:122-138 */

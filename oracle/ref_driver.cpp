@@ -30,6 +30,16 @@ int ref_num_threads(void) {
 #endif
 }
 
+/* A launcher may export OMP_NUM_THREADS=1 to its workers (torch.distributed.run does); the timed CPU baseline asks
+ * for the host's cores explicitly. */
+void ref_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 uint16_t ref_f32_to_f16(float x) { return f32_to_f16(x); }
 float ref_f16_to_f32(uint16_t x) { return f16_to_f32(x); }
 
@@ -152,6 +162,11 @@ extern "C" void ref_matmul_clip(float* out, const float* x, const uint16_t* w, u
     if (clip > 0.f) {
         for (uint32_t j = 0; j < d; ++j) out[j] = std::min(std::max(out[j], -clip), clip);
     }
+}
+
+// include/kernels_cpu.hpp:43-54, the engine's own rmsnorm (x / rms * weight).
+extern "C" void ref_rmsnorm(float* out, const float* x, const float* weight, uint32_t size, float eps) {
+    rmsnorm(out, x, weight, size, eps);
 }
 
 // ---- one token through the whole model, and greedy generation ----

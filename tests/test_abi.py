@@ -26,12 +26,15 @@ def test_graph_node_symbol_is_exported(built_lib, pkg):
     """The engine's kernel symbol (include/kernels.cuh:26) and every helper include/kernels_b200.cuh declares."""
     text = open(os.path.join(ROOT, "include", "kernels_b200.cuh")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    declared = set(re.findall(r"\b(attention_[a-z0-9_]+)\s*\(", text))
+    declared = set(re.findall(r"\b((?:attention|kernels_b200)_[a-z0-9_]+)\s*\(", text))
     assert declared == set(pkg.binding.SYMBOL_HELPERS)
     for name in declared:
         assert hasattr(built_lib, name), name
-    # the __global__ itself, under its C++ name: attention(float*, float const*, __half const*, __half const*, unsigned)
-    assert hasattr(built_lib, "_Z9attentionPfPKfPK6__halfS4_j")
+    # the __global__ symbols themselves, under the C++ names the engine's objects refer to (include/kernels.cuh:9-26),
+    # e.g. attention(float*, float const*, __half const*, __half const*, unsigned)
+    assert "_Z9attentionPfPKfPK6__halfS4_j" in pkg.binding.ENGINE_KERNEL_SYMBOLS
+    for name in pkg.binding.ENGINE_KERNEL_SYMBOLS:
+        assert hasattr(built_lib, name), name
 
 
 def test_status_strings(built_lib):

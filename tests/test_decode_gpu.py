@@ -155,6 +155,35 @@ def test_bitwise_deterministic_and_canaries(attention, wl):
     assert int(ws.status.item()) == 0
 
 
+def test_early_streaming_after_an_appending_kernel(attention, wl, checker):
+    """kv_early: the split pass may start its K/V copies before the kernel in front of it (here the rotary kernel that
+    appends the token's row) has finished, for every tile that cannot hold that row. Back-to-back steps through the
+    programmatic-launch chain, ragged and uniform lengths, must give the result of the plain call and of the CPU."""
+    import torch
+    from gpu_util import check_close, to_device
+    B, H, Hkv, D, T = 3, 32, 8, 128, 700
+    q, k, v = _rand(wl, 77, B, H, Hkv, D, T, "f32", "f16")
+    rng = np.random.default_rng(78)
+    lens = np.array([700, 33, 257], dtype=np.int32)
+    kd, vd = to_device(k, "f16"), to_device(v, "f16")
+    knew = rng.standard_normal((B, Hkv, D), dtype=np.float32)
+    vnew = rng.standard_normal((B, Hkv, D), dtype=np.float32)
+    pos = torch.from_numpy(lens - 1).cuda()
+    lens_d = torch.from_numpy(lens).cuda()
+    ws = attention.DecodeWorkspace(B, H, Hkv, D)
+    outs = []
+    for early in (False, True, True):
+        kc, vc = kd.clone(), vd.clone()
+        q_rot = attention.rope_kv_insert(torch.from_numpy(q).cuda(), torch.from_numpy(knew).cuda(),
+                                         torch.from_numpy(vnew).cuda(), kc, vc, pos, pos, theta=10000.0)
+        outs.append(attention.attn_decode(q_rot, kc, vc, lens_d, workspace=ws, kv_early=early))
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    want = checker.attn_decode(q_rot.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy(), lens.astype(np.uint32))
+    check_close(wl, outs[1].cpu().numpy(), want, "kv_early after rope insert")
+    assert int(ws.status.item()) == 0
+
+
 def test_max_ctas_limits_split_without_changing_result(attention, wl, checker):
     from gpu_util import check_close, run_decode
     q, k, v = _rand(wl, 15, 1, 32, 8, 128, 5000)
@@ -203,6 +232,32 @@ def test_merge_of_many_partials(attention, port, n_parts, D):
             assert abs(lse[r] - want_lse) <= 1e-5 * max(1.0, abs(want_lse))
 
 
+@pytest.mark.parametrize("n_parts", [1, 5, 6, 7, 16])
+@pytest.mark.parametrize("D", [32, 64, 128, 256])
+def test_merge_of_many_rows_with_few_partials(attention, port, n_parts, D):
+    """Hundreds of rows with a handful of partials each (batched decode) take the warp-per-row form of the merge pass:
+    same result as the restated LSE merge, empty partials and empty rows included."""
+    import torch
+    rng = np.random.default_rng(n_parts * 11 + D)
+    rows = 300
+    part_o = rng.standard_normal((n_parts, rows, D), dtype=np.float32)
+    part_lse = (rng.standard_normal((n_parts, rows), dtype=np.float32) * 3).astype(np.float32)
+    part_lse[rng.random((n_parts, rows)) < 0.2] = -np.inf
+    part_lse[:, 7] = -np.inf
+    lse = torch.empty(rows, dtype=torch.float32, device="cuda")
+    got = attention.attn_merge(torch.from_numpy(part_o).cuda(), torch.from_numpy(part_lse).cuda(), lse=lse)
+    torch.cuda.synchronize()
+    got, lse = got.cpu().numpy(), lse.cpu().numpy()
+    for r in range(0, rows, 13):
+        want, want_lse = port.lse_merge(part_o[:, r], part_lse[:, r])
+        if np.isinf(part_lse[:, r]).all():
+            assert (got[r] == 0).all() and lse[r] == -np.inf
+        else:
+            np.testing.assert_allclose(got[r], want, rtol=0, atol=2e-5)
+            assert abs(lse[r] - want_lse) <= 1e-5 * max(1.0, abs(want_lse))
+    assert (got[7] == 0).all() and lse[7] == -np.inf
+
+
 def _sharded_single_gpu(attention, q, k, v, world, rank, bufs, out, status_ws, step=0, poll_limit=0):
     import torch
     return attention.attn_decode_sharded(q, k, v, peer_buffers=[b.data_ptr() for b in bufs], world_size=world,
@@ -224,8 +279,8 @@ def test_fused_exchange_with_one_rank_equals_plain_decode(attention, wl, checker
         torch.cuda.synchronize()
         check_close(wl, out.cpu().numpy(), want, f"fused exchange, call {call}")
     assert int(ws.status.item()) == 0
-    ctl = buf.view(torch.int32)[-4:-2].tolist()
-    assert ctl == [3, 0]  # three steps completed, no row pending
+    ctl = buf.view(torch.int64)[-2:].tolist()
+    assert ctl == [3, 0]  # three steps completed, no cell pending
 
 
 def test_fused_exchange_times_out_cleanly_when_a_peer_never_arrives(attention, wl, checker):
@@ -243,11 +298,12 @@ def test_fused_exchange_times_out_cleanly_when_a_peer_never_arrives(attention, w
     torch.cuda.synchronize()
     assert int(ws.status.item()) & 1  # ATTN_STATUS_WAIT_TIMEOUT
     assert torch.isnan(out).all()
-    # this rank's record did reach the "peer": what a live rank 1 would have merged
-    rec = absent_peer[: 32 * 129]  # parity 1, source rank 0 -> offset (1*2+0)*rec_floats
-    rec = absent_peer[2 * 32 * 129: 3 * 32 * 129]
+    # this rank's record did reach the "peer": what a live rank 1 would have merged (step 1 -> parity 1, source rank 0)
+    rec_o, rec_lse, steps = attention.exchange_record(absent_peer, 1, 32, 128, 2, parity=1, source_rank=0)
+    assert (steps == 1).all()
     want = checker.attn_decode(q.astype(np.float32), k, v)
-    check_close(wl, rec[: 32 * 128].view(1, 32, 128).cpu().numpy(), want, "record delivered to the peer buffer")
+    check_close(wl, rec_o.view(1, 32, 128).cpu().numpy(), want, "record delivered to the peer buffer")
+    assert torch.isfinite(rec_lse).all()
     ws.status.zero_()
     got = attention.attn_decode(qd, kd, vd, workspace=ws)
     torch.cuda.synchronize()

@@ -1,7 +1,7 @@
 """GPU parity of the tcgen05 causal-prefill kernel, called through the C ABI, against the CPU checker: row t of
 the result must equal the engine's decode attention with kv_len = t + 1 (src/model/model.cpp:68,
 include/kernels_cpu.hpp:140-167). Tolerance: max abs 2e-3, max rel 1e-2 (relative error measured against
-max(|ref|, 1% of the RMS of ref)), for the default (precise) mode."""
+max(|ref|, 1% of the RMS of ref)), for the default mode (probabilities as a 16-bit value plus residual)."""
 import ctypes as C
 import os
 
@@ -33,11 +33,14 @@ def _dev(x, dtype):
     return torch.from_numpy(np.ascontiguousarray(x)).cuda()
 
 
-def _run(attention, q, k, v, dtype, out_fp32=True, fast=False):
+P_RESIDUAL, P_INPUT = 0, 1  # binding.PREFILL_P_*
+
+
+def _run(attention, q, k, v, dtype, out_fp32=True, p_mode=P_RESIDUAL):
     import torch
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     out = attention.attn_prefill_causal(_dev(q, dtype), _dev(k, dtype), _dev(v, dtype),
-                                        out_dtype=torch.float32 if out_fp32 else None, fast=fast, status=status)
+                                        out_dtype=torch.float32 if out_fp32 else None, p_mode=p_mode, status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "device status word reports a timed-out wait"
     return out.float().cpu().numpy()
@@ -101,11 +104,12 @@ def test_16_bit_output_and_determinism(attention, wl, checker):
     assert (np.abs(got - want) <= 1e-4 + 2.0 ** -8 * np.abs(want)).all()
 
 
-def test_fast_mode_is_close_but_not_the_parity_mode(attention, wl, checker):
-    """fast=1 feeds the tensor cores one rounded 16-bit probability: an error of about 2^-9 of a row's typical
-    output magnitude (bf16), which stays within a few 1e-3 absolute but not within the strict relative bound."""
+def test_single_rounding_mode_is_close_but_not_the_parity_mode(attention, wl, checker):
+    """ATTN_PREFILL_P_INPUT_TYPE feeds the tensor cores one probability rounded to the input type: for bf16 an error
+    of about 2^-9 of a row's typical output magnitude, which stays within a few 1e-3 absolute but not within the
+    strict relative bound."""
     q, k, v = wl.prefill_inputs(wl.PrefillShape("t", 10, 1, 512, 8, 2, 128, "bf16"))
-    got = _run(attention, q, k, v, "bf16", fast=True)
+    got = _run(attention, q, k, v, "bf16", p_mode=P_INPUT)
     max_abs, _ = wl.error_metrics(got, _want(wl, checker, q, k, v, "bf16"))
     assert max_abs <= 8e-3
 
