@@ -252,6 +252,69 @@ int attn_swiglu(float* hb, const float* hb2, uint64_t count, void* stream);
 /* out[b] = first index of the maximum of logits[b][0..vocab) (greedy sampling, tools/infer.cpp:64-74). */
 int attn_argmax(uint32_t* out, const float* logits, uint32_t batch, uint32_t vocab, void* stream);
 
+/* ---- Whole prompts at once -------------------------------------------------------------------------------------
+ * The engine feeds a prompt one token per forward pass (tools/infer.cpp:271-274). The entry points below process
+ * the tokens of all prompts together, rows = tokens packed one sequence after the other: one GEMM per projection on
+ * the tensor cores instead of one GEMV per token, attn_prefill_causal() per sequence for the attention, and the
+ * row-wise steps in between. Per token the results are those of the engine's forward pass (src/model/block.cpp:105-223).
+ * Activations travel between these steps as a PAIR of fp16 matrices, the rounded value and the rounding residual
+ * (value + residual carries about 22 bits of the fp32 number), because the tensor cores multiply 16-bit operands and a
+ * single rounding (2^-11) would show in the greedy token stream. */
+
+/* C[t][j] (+)= sum_i (a_hi[t][i] + a_lo[t][i]) * w[j][i]: t < m tokens, j < n_out, i < k. a_hi, a_lo fp16 [m][k] and
+ * w fp16 [n_out][k] (the engine's weight layout, k fastest), c fp32 with row stride ldc. Replaces, for m tokens at
+ * once, matmul() of include/kernels_cpu.hpp:69-80 / fused_gemv_clip of src/kernels.cu:229-239. a_lo may be NULL (one
+ * MMA per k-step instead of two): a caller whose weights are not exact in fp16 (Q8_0) makes a second call with the
+ * weights' residual, a_lo = NULL and accumulate = 1. k a multiple of 64, n_out a multiple of 32, pointers 16-byte
+ * aligned. */
+typedef struct AttnGemmArgs {
+    float* c;
+    const void* a_hi;
+    const void* a_lo;
+    const void* w;
+    uint64_t ldc;        /* floats between rows of c; 0 = n_out */
+    uint32_t m, n_out, k;
+    int32_t accumulate;  /* != 0: c += product (the residual connections of src/model/block.cpp:169-172,219-222) */
+    uint32_t* status;    /* optional device word for ATTN_STATUS_* bits */
+} AttnGemmArgs;
+int attn_gemm_f16(const AttnGemmArgs* args, void* stream);
+
+/* Row-wise RMSNorm (include/kernels_cpu.hpp:43-67) of x [rows][dim] fp32, written as the fp16 pair hi, lo [rows][dim]. */
+int attn_rmsnorm_f16pair(void* hi, void* lo, const float* x, const float* weight, uint32_t rows, uint32_t dim, float eps,
+                         void* stream);
+/* count fp32 values -> the fp16 pair (count a multiple of 4). */
+int attn_split_f16pair(void* hi, void* lo, const float* x, uint64_t count, void* stream);
+/* gate_up [rows][ld] fp32 holding the gate projection in columns [0, hidden) and the up projection in
+ * [hidden, 2 hidden) -> silu(gate) * up (src/model/block.cpp:206-210) as the fp16 pair [rows][hidden]. ld 0 = 2 hidden. */
+int attn_swiglu_f16pair(void* hi, void* lo, const float* gate_up, uint32_t rows, uint32_t hidden, uint64_t ld, void* stream);
+/* Q8_0 rows (GGML blocks, see attn_gemv_q8_0) -> value = fp32(scale) * q as the fp16 pair [rows][n]. */
+int attn_dequant_q8_0_f16pair(void* hi, void* lo, const void* w, uint64_t rows, uint32_t n, void* stream);
+
+/* Rotary embedding of q and k of every prompt token and fp16 insert of k, v into the token's cache row
+ * (src/model/block.cpp:140-148 per token; include/kernels_cpu.hpp:82-120): qkv [tokens][ld] fp32 holds a token's q
+ * (n_heads*head_dim), k and v (n_kv_heads*head_dim each) side by side, as the stacked projection leaves them;
+ * q_out receives the rotated q as fp16 [tokens][n_heads][head_dim] (what attn_prefill_causal reads). */
+typedef struct AttnRopePromptArgs {
+    void* q_out;
+    const float* qkv;
+    void* k_cache;             /* fp16, sequence s at + s*kv_batch_stride, row t at + t*kv_row_stride (elements) */
+    void* v_cache;
+    const float* inv_freq;     /* optional device [rotary_dim/2], see AttnRopeInsertArgs */
+    const uint32_t* token_seq; /* device [tokens]: sequence of each token */
+    const uint32_t* token_pos; /* device [tokens]: position = cache row of each token */
+    uint64_t ld;               /* 0 = (n_heads + 2 n_kv_heads) * head_dim */
+    uint64_t kv_row_stride;    /* 0 = n_kv_heads*head_dim */
+    uint64_t kv_batch_stride;
+    uint32_t tokens, n_heads, n_kv_heads, head_dim;
+    uint32_t rotary_dim;       /* 0 = head_dim */
+    float theta;
+    float qkv_clip;            /* > 0: q, k, v are clamped to [-clip, clip] before the rotation (block.cpp:130-138) */
+} AttnRopePromptArgs;
+int attn_rope_prompt(const AttnRopePromptArgs* args, void* stream);
+
+/* out[r][0..dim) = x[rows[r]][0..dim): the last token of every prompt continues into the final norm and classifier. */
+int attn_gather_rows(float* out, const float* x, const uint32_t* rows, uint32_t n_rows, uint32_t dim, void* stream);
+
 /* Size of the built-in scratch array used by attn_decode_static_scratch(). */
 #define ATTN_STATIC_SCRATCH_BYTES (8u << 20)
 
@@ -342,7 +405,7 @@ uint64_t attn_kernel_launch_count(void);
 
 /* sizeof() of an argument structure as this library was compiled, so that a foreign-function binding can check its own
  * mirror of the layout: 0 AttnDecodeArgs, 1 AttnDecodeShardedArgs, 2 AttnPrefillArgs, 3 AttnRopeInsertArgs,
- * 4 AttnGemvArgs, 5 AttnMergeArgs; 0 for any other index. */
+ * 4 AttnGemvArgs, 5 AttnMergeArgs, 6 AttnGemmArgs, 7 AttnRopePromptArgs; 0 for any other index. */
 size_t attn_abi_struct_size(int which);
 
 #ifdef __cplusplus

@@ -480,5 +480,121 @@ def attn_merge(part_o: torch.Tensor, part_lse: torch.Tensor, *, out=None, lse=No
     return out
 
 
+# ---- whole prompts at once: the projection GEMM and the row-wise steps around it (rows = tokens of all prompts) ----
+def _pair_like(x: torch.Tensor, shape=None):
+    shape = tuple(x.shape) if shape is None else tuple(shape)
+    return (torch.empty(shape, dtype=torch.float16, device=x.device), torch.empty(shape, dtype=torch.float16, device=x.device))
+
+
+def gemm_f16(a_hi: torch.Tensor, a_lo, w: torch.Tensor, *, out: torch.Tensor, accumulate: bool = False, status=None,
+             stream=None) -> torch.Tensor:
+    """out[t] (+)= W (a_hi[t] + a_lo[t]) for all t at once on the tensor cores: a_hi, a_lo fp16 [m, k] (a_lo may be
+    None), w fp16 [n_out, k], out fp32 [m, n_out] (rows may be strided). The batched form of matmul()
+    (include/kernels_cpu.hpp:69-80) for the tokens of whole prompts."""
+    _require_cuda(a_hi, w, out)
+    m, k = a_hi.shape
+    n_out = w.shape[0]
+    if w.shape != (n_out, k) or a_hi.dtype != torch.float16 or w.dtype != torch.float16 or out.dtype != torch.float32 or \
+            out.shape != (m, n_out) or out.stride(1) != 1 or not (a_hi.is_contiguous() and w.is_contiguous()):
+        raise ValueError("a_hi fp16 [m, k] and w fp16 [n_out, k] dense, out fp32 [m, n_out] with dense rows")
+    if a_lo is not None and (a_lo.shape != a_hi.shape or a_lo.dtype != torch.float16 or not a_lo.is_contiguous()):
+        raise ValueError("a_lo must match a_hi")
+    a = _b.AttnGemmArgs()
+    a.c, a.a_hi, a.w = out.data_ptr(), a_hi.data_ptr(), w.data_ptr()
+    a.a_lo = a_lo.data_ptr() if a_lo is not None else None
+    a.ldc, a.m, a.n_out, a.k = out.stride(0), m, n_out, k
+    a.accumulate = int(bool(accumulate))
+    a.status = status.data_ptr() if status is not None else None
+    with torch.cuda.device(out.device):
+        _b.check(_b.load().attn_gemm_f16(C.byref(a), _stream_ptr(stream)), "attn_gemm_f16")
+    return out
+
+
+def rmsnorm_pair(x: torch.Tensor, weight: torch.Tensor, eps: float, *, out=None, stream=None):
+    """RMSNorm of every row of x [rows, dim] fp32, written as the fp16 (value, residual) pair that gemm_f16 reads."""
+    _require_cuda(x, weight)
+    rows, dim = x.shape
+    hi, lo = out if out is not None else _pair_like(x)
+    with torch.cuda.device(x.device):
+        _b.check(_b.load().attn_rmsnorm_f16pair(hi.data_ptr(), lo.data_ptr(), x.data_ptr(), weight.data_ptr(), rows, dim,
+                                                float(eps), _stream_ptr(stream)), "attn_rmsnorm_f16pair")
+    return hi, lo
+
+
+def split_pair(x: torch.Tensor, *, out=None, stream=None):
+    """Dense fp32 tensor -> fp16 (value, residual) pair of the same shape."""
+    _require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise ValueError("x must be dense fp32")
+    hi, lo = out if out is not None else _pair_like(x)
+    with torch.cuda.device(x.device):
+        _b.check(_b.load().attn_split_f16pair(hi.data_ptr(), lo.data_ptr(), x.data_ptr(), x.numel(), _stream_ptr(stream)),
+                 "attn_split_f16pair")
+    return hi, lo
+
+
+def swiglu_pair(gate_up: torch.Tensor, *, out=None, stream=None):
+    """gate_up fp32 [rows, 2 hidden] (gate columns, then up columns) -> silu(gate) * up as the fp16 pair [rows, hidden]."""
+    _require_cuda(gate_up)
+    rows, two_h = gate_up.shape
+    if gate_up.dtype != torch.float32 or gate_up.stride(1) != 1 or two_h % 2:
+        raise ValueError("gate_up must be fp32 [rows, 2 hidden] with dense rows")
+    hidden = two_h // 2
+    hi, lo = out if out is not None else _pair_like(gate_up, (rows, hidden))
+    with torch.cuda.device(gate_up.device):
+        _b.check(_b.load().attn_swiglu_f16pair(hi.data_ptr(), lo.data_ptr(), gate_up.data_ptr(), rows, hidden,
+                                               gate_up.stride(0), _stream_ptr(stream)), "attn_swiglu_f16pair")
+    return hi, lo
+
+
+def dequant_q8_0_pair(w: torch.Tensor, *, out=None, stream=None):
+    """Q8_0 rows uint8 [rows, n/32*34] -> fp32(scale) * q as the fp16 (value, residual) pair [rows, n]."""
+    _require_cuda(w)
+    rows = w.shape[0]
+    n = w.shape[1] // 34 * 32
+    if w.dtype != torch.uint8 or w.shape[1] % 34 or not w.is_contiguous():
+        raise ValueError("w must be dense uint8 [rows, n/32*34]")
+    if out is None:
+        out = (torch.empty((rows, n), dtype=torch.float16, device=w.device), torch.empty((rows, n), dtype=torch.float16, device=w.device))
+    hi, lo = out
+    with torch.cuda.device(w.device):
+        _b.check(_b.load().attn_dequant_q8_0_f16pair(hi.data_ptr(), lo.data_ptr(), w.data_ptr(), rows, n,
+                                                     _stream_ptr(stream)), "attn_dequant_q8_0_f16pair")
+    return hi, lo
+
+
+def rope_prompt(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                token_seq: torch.Tensor, token_pos: torch.Tensor, *, n_heads: int, theta: float, rotary_dim: int = 0,
+                qkv_clip: float = 0.0, inv_freq=None, stream=None) -> torch.Tensor:
+    """Rotate q and k of every prompt token and insert k, v (fp16) into the token's cache row: qkv fp32 [tokens,
+    (H + 2 Hkv) D] as the stacked projection leaves it, q_out fp16 [tokens, H, D], caches fp16 [B, T, Hkv, D],
+    token_seq / token_pos int32 [tokens] on the device. Per token what src/model/block.cpp:140-148 does."""
+    _require_cuda(qkv, q_out, k_cache, v_cache, token_seq, token_pos)
+    tokens = qkv.shape[0]
+    _, _, Hkv, D = k_cache.shape
+    if qkv.dtype != torch.float32 or qkv.stride(1) != 1 or qkv.shape[1] != (n_heads + 2 * Hkv) * D or \
+            q_out.dtype != torch.float16 or q_out.shape != (tokens, n_heads, D) or not q_out.is_contiguous():
+        raise ValueError("qkv fp32 [tokens, (H + 2 Hkv) D], q_out dense fp16 [tokens, H, D]")
+    a = _b.AttnRopePromptArgs()
+    a.q_out, a.qkv, a.k_cache, a.v_cache = q_out.data_ptr(), qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+    a.inv_freq = inv_freq.data_ptr() if inv_freq is not None else None
+    a.token_seq, a.token_pos = token_seq.data_ptr(), token_pos.data_ptr()
+    a.ld, a.kv_row_stride, a.kv_batch_stride = qkv.stride(0), k_cache.stride(1), k_cache.stride(0)
+    a.tokens, a.n_heads, a.n_kv_heads, a.head_dim = tokens, n_heads, Hkv, D
+    a.rotary_dim, a.theta, a.qkv_clip = rotary_dim, float(theta), float(qkv_clip)
+    with torch.cuda.device(qkv.device):
+        _b.check(_b.load().attn_rope_prompt(C.byref(a), _stream_ptr(stream)), "attn_rope_prompt")
+    return q_out
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, *, out: torch.Tensor, stream=None) -> torch.Tensor:
+    """out[r] = x[rows[r]] (fp32 rows; rows int32 on the device)."""
+    _require_cuda(x, rows, out)
+    with torch.cuda.device(x.device):
+        _b.check(_b.load().attn_gather_rows(out.data_ptr(), x.data_ptr(), rows.data_ptr(), rows.numel(), x.shape[1],
+                                            _stream_ptr(stream)), "attn_gather_rows")
+    return out
+
+
 def kernel_launch_count() -> int:
     return int(_b.load().attn_kernel_launch_count())

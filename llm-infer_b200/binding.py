@@ -31,6 +31,13 @@ EXPORTED_SYMBOLS = (
     "attn_merge",
     "attn_prefill_causal",
     "attn_rope_kv_insert",
+    "attn_gemm_f16",
+    "attn_rmsnorm_f16pair",
+    "attn_split_f16pair",
+    "attn_swiglu_f16pair",
+    "attn_dequant_q8_0_f16pair",
+    "attn_rope_prompt",
+    "attn_gather_rows",
     "attn_gemv_f16",
     "attn_gemv_q8_0",
     "attn_embed_f16",
@@ -203,6 +210,43 @@ class AttnMergeArgs(C.Structure):
     ]
 
 
+class AttnGemmArgs(C.Structure):
+    _fields_ = [
+        ("c", C.c_void_p),
+        ("a_hi", C.c_void_p),
+        ("a_lo", C.c_void_p),
+        ("w", C.c_void_p),
+        ("ldc", C.c_uint64),
+        ("m", C.c_uint32),
+        ("n_out", C.c_uint32),
+        ("k", C.c_uint32),
+        ("accumulate", C.c_int32),
+        ("status", C.c_void_p),
+    ]
+
+
+class AttnRopePromptArgs(C.Structure):
+    _fields_ = [
+        ("q_out", C.c_void_p),
+        ("qkv", C.c_void_p),
+        ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p),
+        ("inv_freq", C.c_void_p),
+        ("token_seq", C.c_void_p),
+        ("token_pos", C.c_void_p),
+        ("ld", C.c_uint64),
+        ("kv_row_stride", C.c_uint64),
+        ("kv_batch_stride", C.c_uint64),
+        ("tokens", C.c_uint32),
+        ("n_heads", C.c_uint32),
+        ("n_kv_heads", C.c_uint32),
+        ("head_dim", C.c_uint32),
+        ("rotary_dim", C.c_uint32),
+        ("theta", C.c_float),
+        ("qkv_clip", C.c_float),
+    ]
+
+
 class AttnError(RuntimeError):
     def __init__(self, code: int, what: str, cuda_error: int = 0):
         self.code = code
@@ -262,13 +306,29 @@ def load() -> C.CDLL:
     lib.attn_rope_kv_insert.argtypes = [C.POINTER(AttnRopeInsertArgs), C.c_void_p]
     lib.attn_merge.restype = C.c_int
     lib.attn_merge.argtypes = [C.POINTER(AttnMergeArgs), C.c_void_p]
+    lib.attn_gemm_f16.restype = C.c_int
+    lib.attn_gemm_f16.argtypes = [C.POINTER(AttnGemmArgs), C.c_void_p]
+    lib.attn_rmsnorm_f16pair.restype = C.c_int
+    lib.attn_rmsnorm_f16pair.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_float,
+                                         C.c_void_p]
+    lib.attn_split_f16pair.restype = C.c_int
+    lib.attn_split_f16pair.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]
+    lib.attn_swiglu_f16pair.restype = C.c_int
+    lib.attn_swiglu_f16pair.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64, C.c_void_p]
+    lib.attn_dequant_q8_0_f16pair.restype = C.c_int
+    lib.attn_dequant_q8_0_f16pair.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p]
+    lib.attn_rope_prompt.restype = C.c_int
+    lib.attn_rope_prompt.argtypes = [C.POINTER(AttnRopePromptArgs), C.c_void_p]
+    lib.attn_gather_rows.restype = C.c_int
+    lib.attn_gather_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
     lib.attn_status_string.restype = C.c_char_p
     lib.attn_status_string.argtypes = [C.c_int]
     lib.attn_last_cuda_error.restype = C.c_int
     lib.attn_kernel_launch_count.restype = C.c_uint64
     lib.attn_abi_struct_size.restype = C.c_size_t
     lib.attn_abi_struct_size.argtypes = [C.c_int]
-    mirrors = (AttnDecodeArgs, AttnDecodeShardedArgs, AttnPrefillArgs, AttnRopeInsertArgs, AttnGemvArgs, AttnMergeArgs)
+    mirrors = (AttnDecodeArgs, AttnDecodeShardedArgs, AttnPrefillArgs, AttnRopeInsertArgs, AttnGemvArgs, AttnMergeArgs,
+               AttnGemmArgs, AttnRopePromptArgs)
     for index, mirror in enumerate(mirrors):
         if lib.attn_abi_struct_size(index) != C.sizeof(mirror):
             raise RuntimeError(f"{mirror.__name__}: the ctypes mirror ({C.sizeof(mirror)} bytes) does not match the "

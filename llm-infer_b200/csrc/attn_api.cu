@@ -283,6 +283,8 @@ size_t attn_abi_struct_size(int which) {
         case 3: return sizeof(AttnRopeInsertArgs);
         case 4: return sizeof(AttnGemvArgs);
         case 5: return sizeof(AttnMergeArgs);
+        case 6: return sizeof(AttnGemmArgs);
+        case 7: return sizeof(AttnRopePromptArgs);
         default: return 0;
     }
 }

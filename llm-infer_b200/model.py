@@ -83,7 +83,7 @@ def random_weights(cfg: ModelConfig, seed: int, device="cpu", weight_type: str =
 
 
 class Llama:
-    """Batched token-at-a-time forward and greedy generation on one GPU."""
+    """Batched token-at-a-time forward, whole-prompt prefill and greedy generation on one GPU."""
 
     def __init__(self, cfg: ModelConfig, weights: dict, batch: int, device=None, weight_type: str = "f16"):
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -207,6 +207,83 @@ class Llama:
         A.argmax(self.logits, out=self.next_token)
         self.tokens.copy_(self.next_token)
 
+    def can_prefill(self, prompts, n_new: int = 0) -> bool:
+        """Whether prefill() can take these prompts: head_dim 128 (the tensor-core attention kernel), inner dimensions
+        in multiples of 64, and every sequence inside its cache (no sliding window during the prompt or after it)."""
+        c = self.cfg
+        dims_ok = c.head_dim == 128 and c.dim % 64 == 0 and c.hidden_dim % 64 == 0 and (c.n_heads * c.head_dim) % 64 == 0
+        return dims_ok and max(len(p) for p in prompts) + n_new <= c.max_seq_len
+
+    def prefill(self, prompts) -> None:
+        """The prompt phase for all sequences at once instead of one token per step: the tokens of every prompt are
+        packed into one matrix of rows; per layer one tensor-core GEMM per projection (attn_gemm_f16; Q8_0 weights are
+        expanded per matrix into an fp16 value / residual pair first), the rotary kernel that also fills the KV caches,
+        causal attention per sequence (attn_prefill_causal straight over that sequence's cache rows), and the
+        row-wise norm / SwiGLU steps. Per token this is the engine's forward pass (src/model/block.cpp:105-223) with
+        InferenceMode::Prefill for all but the last token of a prompt (src/model/model.cpp:74-76); the last tokens go
+        through the final norm, classifier and greedy pick. Afterwards the caches hold rows 0 .. len-1 of every
+        sequence and self.next_token / self.tokens / self.logits are what the token-at-a-time loop would have left."""
+        import numpy as np
+        c, w, B, dev = self.cfg, self.w, self.batch, self.device
+        if len(prompts) != B or not self.can_prefill(prompts):
+            raise ValueError("prefill() needs one prompt per sequence, head_dim 128 and prompts that fit the cache")
+        q8 = self.weight_type == "q8_0"
+        lens = [len(p) for p in prompts]
+        starts = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        T = int(starts[-1])
+        host = torch.tensor([t for p in prompts for t in p], dtype=torch.int32).pin_memory()
+        seq = torch.from_numpy(np.repeat(np.arange(B, dtype=np.int32), lens)).pin_memory()
+        pos = torch.from_numpy(np.concatenate([np.arange(n, dtype=np.int32) for n in lens])).pin_memory()
+        last = torch.from_numpy((starts[1:] - 1).astype(np.int32)).pin_memory()
+        tokens, token_seq, token_pos, last_rows = (t.to(dev, non_blocking=True) for t in (host, seq, pos, last))
+        f32, f16 = torch.float32, torch.float16
+        e = lambda *s, dtype=f32: torch.empty(*s, dtype=dtype, device=dev)  # noqa: E731
+        q_dim, kv_dim, H, D = self._q_dim, self._kv_dim, c.n_heads, c.head_dim
+        x = e(T, c.dim)
+        pair_d = (e(T, c.dim, dtype=f16), e(T, c.dim, dtype=f16))
+        pair_q = pair_d if q_dim == c.dim else (e(T, q_dim, dtype=f16), e(T, q_dim, dtype=f16))
+        pair_h = (e(T, c.hidden_dim, dtype=f16), e(T, c.hidden_dim, dtype=f16))
+        qkv = e(T, q_dim + 2 * kv_dim)
+        q16 = e(T, H, D, dtype=f16)
+        att = e(T, H, D)
+        gate_up = e(T, 2 * c.hidden_dim)
+        if q8:  # room for the largest matrix of a layer as an fp16 pair
+            biggest = max(w[k].shape[1] * (w[k].shape[2] // 34 * 32) for k in ("wqkv", "wo", "w13", "w2"))
+            w_hi, w_lo = e(biggest, dtype=f16), e(biggest, dtype=f16)
+
+        def project(a_pair, wmat, out, accumulate):
+            if q8:
+                rows, n = wmat.shape[0], wmat.shape[1] // 34 * 32
+                pair = (w_hi[:rows * n].view(rows, n), w_lo[:rows * n].view(rows, n))
+                A.dequant_q8_0_pair(wmat, out=pair)
+                A.gemm_f16(a_pair[0], a_pair[1], pair[0], out=out, accumulate=accumulate, status=self.status)
+                A.gemm_f16(a_pair[0], None, pair[1], out=out, accumulate=True, status=self.status)
+            else:
+                A.gemm_f16(a_pair[0], a_pair[1], wmat, out=out, accumulate=accumulate, status=self.status)
+
+        self._embed(w["embed"], tokens, out=x, status=self.status)
+        for l in range(c.n_layers):
+            A.rmsnorm_pair(x, w["rms_att"][l], c.norm_eps, out=pair_d)
+            project(pair_d, w["wqkv"][l], qkv, False)
+            A.rope_prompt(qkv, q16, self.k_cache[l], self.v_cache[l], token_seq, token_pos, n_heads=H,
+                          theta=c.rope_theta, rotary_dim=c.rotary_dim, qkv_clip=c.qkv_clip)
+            for b in range(B):
+                s0, s1, n = int(starts[b]), int(starts[b + 1]), lens[b]
+                A.attn_prefill_causal(q16[s0:s1].unsqueeze(0), self.k_cache[l, b, :n].unsqueeze(0),
+                                      self.v_cache[l, b, :n].unsqueeze(0), out=att[s0:s1].unsqueeze(0), status=self.status)
+            A.split_pair(att.view(T, q_dim), out=pair_q)
+            project(pair_q, w["wo"][l], x, True)                          # x += Wo att
+            A.rmsnorm_pair(x, w["rms_ffn"][l], c.norm_eps, out=pair_d)
+            project(pair_d, w["w13"][l], gate_up, False)                  # gate | up
+            A.swiglu_pair(gate_up, out=pair_h)
+            project(pair_h, w["w2"][l], x, True)                          # x += W2 (silu(gate) * up)
+        # the last token of every prompt: final norm, classifier, greedy pick (the decode step's own kernels)
+        A.gather_rows(x, last_rows, out=self.x)
+        A.rmsnorm(self.x, w["rms_final"], c.norm_eps, out=self.xb)
+        self._gemv(self.xb, w["wcls"], out=self.logits)
+        A.argmax(self.logits, out=self.next_token)
+        self.tokens.copy_(self.next_token)
+
     def capture(self) -> None:
         """Record the step once per mode (prefill: no classifier; decode: classifier + greedy pick + feedback) as CUDA
         graphs, the way the engine drives its CUDA step (include/model/device.hpp:161-262): a step then costs one
@@ -244,13 +321,16 @@ class Llama:
             self._launch_step(kv_sink, want_logits)
         return self.logits if want_logits else None
 
-    def generate(self, prompts, n_new: int, want_logits: bool = False, timing: dict | None = None):
+    def generate(self, prompts, n_new: int, want_logits: bool = False, timing: dict | None = None,
+                 prompt_mode: str = "auto"):
         """Greedy generation for a ragged batch: prompts is a list of B token-id lists. Every sequence is fed one
         token per step from position 0 (its prompt, then its own picks), exactly the engine's loop
         (tools/infer.cpp:271-300, without the end-of-sequence stop); sequences start late so that all prompts end
         at the same step and the generation steps run as one dense batch. Returns int32 [B, n_new] on the host
         (and the logits each pick was made from, [B, n_new, vocab], when asked). ``timing`` (a dict) receives the
-        device time of the prompt phase and of the generation phase in ms (CUDA events)."""
+        device time of the prompt phase and of the generation phase in ms (CUDA events). ``prompt_mode``: "token" feeds
+        the prompts one token per step as described; "batched" runs prefill() (all prompt tokens at once on the tensor
+        cores); "auto" picks "batched" whenever can_prefill() allows it."""
         B = self.batch
         if len(prompts) != B or any(len(p) == 0 for p in prompts):
             raise ValueError("one non-empty prompt per sequence of the batch")
@@ -261,8 +341,13 @@ class Llama:
         out = torch.zeros((B, n_new), dtype=torch.int32, device=self.device)
         out_logits = torch.zeros((B, n_new, self.cfg.vocab_size), device=self.device) if want_logits else None
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        if prompt_mode not in ("auto", "token", "batched"):
+            raise ValueError("prompt_mode must be 'auto', 'token' or 'batched'")
+        batched = prompt_mode == "batched" or (prompt_mode == "auto" and self.can_prefill(prompts, n_new))
         ev[0].record()
-        for step in range(longest):
+        if batched:
+            self.prefill(prompts)
+        for step in range(0 if batched else longest):
             # a sequence that has not started yet is fed its first token at position 0 again (row 0 is rewritten)
             pos = [max(step - d, 0) for d in delay]
             host = torch.tensor([p[q] for p, q in zip(prompts, pos)], dtype=torch.int32).pin_memory()
@@ -278,7 +363,9 @@ class Llama:
         torch.cuda.synchronize(self.device)
         if timing is not None:
             timing.update(prompt_ms=ev[0].elapsed_time(ev[1]), generate_ms=ev[1].elapsed_time(ev[2]),
-                          prompt_steps=longest, generate_steps=n_new - 1)
+                          prompt_steps=longest, generate_steps=n_new - 1,
+                          prompt_mode="batched (tensor-core GEMMs + causal prefill attention)" if batched
+                          else "token-at-a-time")
         if int(self.status.item()) != 0 or int(self.workspace.status.item()) != 0:
             raise RuntimeError("a kernel reported a status bit (token id out of range or a wait that ran out)")
         return (out.cpu(), out_logits.cpu()) if want_logits else out.cpu()

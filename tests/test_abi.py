@@ -90,7 +90,7 @@ def test_work_split_arithmetic_matches_between_passes():
 def test_ctypes_mirrors_have_the_library_struct_sizes(built_lib, pkg):
     b = pkg.binding
     mirrors = (b.AttnDecodeArgs, b.AttnDecodeShardedArgs, b.AttnPrefillArgs, b.AttnRopeInsertArgs, b.AttnGemvArgs,
-               b.AttnMergeArgs)
+               b.AttnMergeArgs, b.AttnGemmArgs, b.AttnRopePromptArgs)
     for index, mirror in enumerate(mirrors):
         assert built_lib.attn_abi_struct_size(index) == C.sizeof(mirror), mirror.__name__
     assert built_lib.attn_abi_struct_size(99) == 0

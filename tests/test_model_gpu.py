@@ -22,13 +22,13 @@ def _numpy_weights(w):
     return {k: v.numpy() for k, v in w.items()}
 
 
-def _run_case(M, checker, cfg, prompts, n_new, seed, graph=False, weight_type="f16"):
+def _run_case(M, checker, cfg, prompts, n_new, seed, graph=False, weight_type="f16", prompt_mode="token"):
     import torch
     w = M.random_weights(cfg, seed, weight_type=weight_type)
     llama = M.Llama(cfg, w, batch=len(prompts), weight_type=weight_type)
     if graph:
         llama.capture()
-    got_tokens, got_logits = llama.generate(prompts, n_new, want_logits=True)
+    got_tokens, got_logits = llama.generate(prompts, n_new, want_logits=True, prompt_mode=prompt_mode)
     wn = _numpy_weights(w)
     safe_all = True
     cfg_dict = dict(cfg.as_dict(), weight_type=weight_type)
@@ -87,6 +87,7 @@ def test_q8_0_model_with_split_k_down_projection(M, port):
     w = M.random_weights(cfg, 8, weight_type="q8_0")
     assert M.Llama(cfg, w, batch=8, weight_type="q8_0")._k_split == 2
     _run_case(M, port, cfg, prompts, n_new=8, seed=8, graph=True, weight_type="q8_0")
+    _run_case(M, port, cfg, prompts, n_new=8, seed=8, weight_type="q8_0", prompt_mode="batched")
 
 
 @pytest.mark.parametrize("weight_type", ["f16", "q8_0"])
@@ -104,13 +105,14 @@ def test_model_file_round_trip_generates_the_same_tokens(M, tmp_path, weight_typ
     assert np.array_equal(a.numpy(), b.numpy()) and len(set(a.flatten().tolist())) > 3
 
 
-def test_head_dim_128_gqa4_clip_and_partial_rotary(M, checker):
+@pytest.mark.parametrize("prompt_mode", ["token", "batched"])
+def test_head_dim_128_gqa4_clip_and_partial_rotary(M, checker, prompt_mode):
     cfg = M.ModelConfig(dim=1024, hidden_dim=1536, n_layers=3, n_heads=8, n_kv_heads=2, head_dim=128,
                         vocab_size=777, max_seq_len=96, norm_eps=1e-5, rope_theta=500000.0, rotary_dim=64,
                         qkv_clip=2.5)
     rng = np.random.default_rng(12)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (17, 1, 40, 8)]
-    _run_case(M, checker, cfg, prompts, n_new=16, seed=2)
+    _run_case(M, checker, cfg, prompts, n_new=16, seed=2, prompt_mode=prompt_mode)
 
 
 def test_sliding_window_with_sink_rows(M, checker):
@@ -123,13 +125,42 @@ def test_sliding_window_with_sink_rows(M, checker):
     _run_case(M, checker, cfg, prompts, n_new=20, seed=3)
 
 
-def test_llama3_8b_shaped_layer(M, checker):
-    """One layer with the 8B model's dimensions (dim 4096, 32/8 heads of 128, FFN 14336, theta 5e5), small vocabulary."""
+@pytest.mark.parametrize("prompt_mode", ["token", "batched"])
+def test_llama3_8b_shaped_layer(M, checker, prompt_mode):
+    """One layer with the 8B model's dimensions (dim 4096, 32/8 heads of 128, FFN 14336, theta 5e5), small vocabulary;
+    prompts fed token by token, and all at once through the tensor-core GEMMs and the causal prefill kernel."""
     cfg = M.ModelConfig(dim=4096, hidden_dim=14336, n_layers=1, n_heads=32, n_kv_heads=8, head_dim=128,
                         vocab_size=2048, max_seq_len=48, norm_eps=1e-5, rope_theta=500000.0)
     rng = np.random.default_rng(14)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (12, 30)]
-    _run_case(M, checker, cfg, prompts, n_new=8, seed=4)
+    _run_case(M, checker, cfg, prompts, n_new=8, seed=4, prompt_mode=prompt_mode)
+
+
+def test_whole_prompt_prefill_equals_the_token_loop(M, port):
+    """Longer ragged prompts (several 128-row tiles, one shorter than a tile), fp16 and Q8_0 weights: the batched prompt
+    phase must leave the model where the token-at-a-time loop leaves it - same greedy tokens afterwards, logits
+    within the attention tolerance - and match the CPU forward pass for the Q8_0 case."""
+    cfg = M.ModelConfig(dim=512, hidden_dim=1024, n_layers=3, n_heads=4, n_kv_heads=2, head_dim=128, vocab_size=900,
+                        max_seq_len=420, norm_eps=1e-5, rope_theta=500000.0)
+    rng = np.random.default_rng(77)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (300, 7, 129, 400)]
+    for weight_type in ("f16", "q8_0"):
+        w = M.random_weights(cfg, 17, weight_type=weight_type)
+        a = M.Llama(cfg, w, batch=4, weight_type=weight_type)
+        assert a.can_prefill(prompts, 12)
+        tok_a, log_a = a.generate(prompts, 12, want_logits=True, prompt_mode="token")
+        b = M.Llama(cfg, w, batch=4, weight_type=weight_type)
+        tok_b, log_b = b.generate(prompts, 12, want_logits=True, prompt_mode="batched")
+        la, lb = log_a.numpy(), log_b.numpy()
+        rms = float(np.sqrt(np.mean(la ** 2)))
+        assert np.abs(la - lb).max() <= 2e-3 + 1e-2 * rms
+        srt = np.sort(la, axis=-1)
+        safe = (srt[..., -1] - srt[..., -2]) > 1e-3
+        ta, tb = tok_a.numpy(), tok_b.numpy()
+        for s in range(4):
+            upto = 12 if safe[s].all() else int(np.argmin(safe[s]))  # compare up to the first near-tie
+            assert np.array_equal(ta[s, :upto], tb[s, :upto]), (weight_type, s)
+    _run_case(M, port, cfg, prompts[:2], n_new=6, seed=17, weight_type="q8_0", prompt_mode="batched")
 
 
 def test_small_steps_against_port(M, port):
