@@ -279,6 +279,11 @@ def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, pro
     timing = {}
     tokens = llama.generate(prompts, n_new, timing=timing)
     gen_ms = timing["generate_ms"] / max(1, timing["generate_steps"])
+    # the prompt phase the other two ways, for comparison: one token per step (the engine's loop), and the batched
+    # path without the residual terms (not the parity mode)
+    t_tok, t_single = {}, {}
+    tokens_tok = llama.generate(prompts, 2, timing=t_tok, prompt_mode="token")
+    llama.generate(prompts, 2, timing=t_single, prompt_mode="batched-single-rounding")
     res = {
         "workload": "Llama-3-8B-shaped random-init model loaded from a seed-generated Q8_0 GGUF file, batch 8, prompts "
                     f"{lengths}, {n_new} new tokens each, greedy, one CUDA graph launch per step",
@@ -286,6 +291,9 @@ def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, pro
         "generate_tok_per_s": batch * 1e3 / gen_ms, "generate_ms_per_step": gen_ms,
         "prompt_tok_per_s": sum(lengths) * 1e3 / timing["prompt_ms"],
         "prompt_ms": timing["prompt_ms"], "prompt_mode": timing.get("prompt_mode", "token-at-a-time"),
+        "prompt_tok_per_s_token_at_a_time": sum(lengths) * 1e3 / t_tok["prompt_ms"],
+        "prompt_tok_per_s_single_rounding": sum(lengths) * 1e3 / t_single["prompt_ms"],
+        "first_two_tokens_equal_token_at_a_time_path": bool((tokens[:, :2] == tokens_tok).all()),
         "weight_bytes_per_decode_step": weight_bytes,
         "weight_stream_gbs": weight_bytes / (gen_ms * 1e-3) / 1e9,
         "distinct_tokens_generated": int(len(set(tokens.flatten().tolist()))),
@@ -456,6 +464,34 @@ def decode_trace(torch):
                                                         "merge": "[min, median, max] over CTAs, same origin"}}), flush=True)
 
 
+def gemm_measure(torch, steps: int, warmup: int, tflops_peak: float, peak_kind: str, small: bool = False):
+    """The projection GEMM of the whole-prompt path alone (attn_gemm_f16: tokens x weights on the tensor cores,
+    activations as an fp16 value + residual pair = two MMAs per k-step), on the four projections of a
+    Llama-3-8B-shaped layer at the C5 prompt load (9101 tokens). Useful FLOPs = 2 m n k; the tensor cores do twice
+    that. ``small`` = one 4096^3 case only (profiler captures)."""
+    from llm_infer_b200 import attention as A
+    dev = torch.device("cuda", torch.cuda.current_device())
+    shapes = [(4096, 4096, 4096)] if small else [(9101, 6144, 4096), (9101, 4096, 4096), (9101, 28672, 4096),
+                                                  (9101, 4096, 14336)]
+    res = {}
+    for m, n, k in shapes:
+        hi = torch.randn((m, k), device=dev).half()
+        lo = (torch.randn((m, k), device=dev) * 1e-4).half()
+        ws = [(torch.randn((n, k), device=dev) * k ** -0.5).half() for _ in range(2)]
+        out = torch.empty((m, n), device=dev)
+        for i in range(max(3, warmup)):
+            A.gemm_f16(hi, lo, ws[i % 2], out=out)
+        ms = time_steps(torch, lambda i: A.gemm_f16(hi, lo, ws[i % 2], out=out), steps) / steps
+        useful = 2.0 * m * n * k
+        res[f"m{m}_n{n}_k{k}"] = {"us": round(ms * 1e3, 1), "useful_tflops": round(useful / ms / 1e9, 1),
+                                  "tensor_tflops": round(2 * useful / ms / 1e9, 1),
+                                  "tensor_frac_of_peak": round(2 * useful / ms / 1e9 / tflops_peak, 3)}
+        del hi, lo, ws, out
+    res["note"] = (f"tensor_tflops = 2 x useful (value + residual MMAs); frac of {peak_kind} cuBLAS bf16 burst peak "
+                   f"{tflops_peak:.0f} TFLOP/s")
+    return res
+
+
 def time_steps(torch, fn, steps: int):
     """CUDA-event time of `steps` calls of fn(i) on the current stream, in ms."""
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -621,6 +657,10 @@ def run_single(args):
         extra["gemv_layer"] = gemv_measure(torch, 60, 6, hbm_peak, peak_kind)
     except Exception as e:
         extra["gemv_layer"] = {"error": str(e)[:300]}
+    try:
+        extra["prompt_gemm"] = gemm_measure(torch, 10, 3, tflops_peak, peak_kind)
+    except Exception as e:
+        extra["prompt_gemm"] = {"error": str(e)[:300]}
     try:
         extra["generate_c5"] = generate_measure(torch)
     except Exception as e:
@@ -904,6 +944,8 @@ def main():
                     help="with --generate-only: launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--generate-short", action="store_true",
                     help="with --generate-only: prompts of 8-16 tokens and 8 new tokens (for profiler launch lists)")
+    ap.add_argument("--gemm-only", action="store_true",
+                    help="time only the whole-prompt projection GEMM (with --steps <= 5: one 4096^3 case, for profiler captures)")
     ap.add_argument("--decode-trace", action="store_true",
                     help="per-CTA time stamps of one attn_decode call (needs the profiling build, see decode_trace)")
     ap.add_argument("--kernel-only", action="store_true",
@@ -919,6 +961,13 @@ def main():
         import torch
         load_package()
         decode_trace(torch)
+        return
+    if args.gemm_only:
+        import torch
+        load_package()
+        _, tflops_peak, peak_kind = measured_peaks()
+        print(json.dumps({"prompt_gemm": gemm_measure(torch, args.steps, args.warmup, tflops_peak, peak_kind,
+                                                      small=args.steps <= 5)}), flush=True)
         return
     if args.gemv_only:
         import torch

@@ -66,7 +66,9 @@ enum {
 enum {
     ATTN_STATUS_OK = 0u,
     ATTN_STATUS_WAIT_TIMEOUT = 1u, /* a bounded wait on a shared-memory barrier ran out */
-    ATTN_STATUS_BAD_SHAPE = 2u     /* device-side shape check failed */
+    ATTN_STATUS_BAD_SHAPE = 2u,    /* device-side shape check failed */
+    ATTN_STATUS_BAD_INDEX = 4u     /* checking build (-DATTN_BOUNDS_CHECK) only: an index left its buffer; the access was
+                                      skipped */
 };
 
 /* Single-token (decode) attention over the KV cache. Replaces the per-head
@@ -102,6 +104,9 @@ typedef struct AttnDecodeArgs {
                           outside the sliding window, where the rotary kernel appends row pos just before attention
                           (src/model/block.cu:147-161, src/model/model.cpp:65-68). The split pass then starts streaming
                           every tile that cannot hold that row before it waits for the previous kernel. 0 = wait first. */
+    uint32_t kv_capacity; /* rows each sequence's caches hold (the engine's max_seq_len); 0 = not stated. When stated, a
+                             length beyond it (a corrupted kv_len[] entry) is clamped to it on the device and
+                             ATTN_STATUS_BAD_SHAPE is ORed into *status, instead of reading past the cache. */
 } AttnDecodeArgs;
 
 /* Scratch size for attn_decode with these dimensions on the current device. */
@@ -114,7 +119,7 @@ int attn_decode(const AttnDecodeArgs* args, void* stream);
  * run once per prompt token with kv_len = pos + 1 (tools/infer.cpp:271-274, src/model/model.cpp:68), so row t
  * of the result is attn() (include/kernels_cpu.hpp:140-167) over rows 0..t. Dense layouts, 16-bit inputs:
  *   q, o : [batch][seq_len][n_heads][head_dim]      k, v : [batch][seq_len][n_kv_heads][head_dim]
- * (k, v are the engine's cache layout [row][kv_head][head_dim] per sequence). head_dim must be 128. */
+ * (k, v are the engine's cache layout [row][kv_head][head_dim] per sequence). head_dim 128 or 64. */
 typedef struct AttnPrefillArgs {
     void* o;          /* out, o_dtype */
     const void* q;    /* in, dtype */

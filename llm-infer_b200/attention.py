@@ -108,6 +108,7 @@ def _decode_args(q, k_cache, v_cache, kv_len, out, lse, out_dtype, scale, worksp
     a.workspace, a.workspace_bytes = workspace.buf.data_ptr(), workspace.nbytes
     a.status = workspace.status.data_ptr()
     a.kv_early = int(bool(kv_early))
+    a.kv_capacity = T  # a device-side length beyond the cache is clamped and reported (ATTN_STATUS_BAD_SHAPE)
     return a, out, workspace, q
 
 
@@ -120,7 +121,7 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, k
     k_cache  [B, T, Hkv, D]   fp16 / bf16; only the last dim must be dense, rows and sequences may be strided
     v_cache  same geometry as k_cache
     kv_len   None (all T rows valid), an int, or an int32/uint32 CUDA tensor [B]; the values of a tensor are read
-             on the device and are not checked against T: a length beyond the cache reads past it
+             on the device: one beyond T is clamped to T there and sets ATTN_STATUS_BAD_SHAPE in workspace.status
     kv_early True when the lengths were in place before the previous kernel of the stream was launched and that kernel
              writes no K/V row other than each sequence's last valid one: streaming then starts before it has finished
     returns  out [B, H, D] in out_dtype; fills ``lse`` [B, H] (fp32) when given
@@ -172,7 +173,7 @@ def attn_prefill_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, ou
     """Causal attention of whole prompts: row t attends rows 0..t (the engine's token-at-a-time prefill,
     tools/infer.cpp:271-274, as one kernel).
 
-    q [B, S, H, D], k / v [B, S, Hkv, D], fp16 or bf16, dense; D = 128. Returns out [B, S, H, D] in ``out_dtype``
+    q [B, S, H, D], k / v [B, S, Hkv, D], fp16 or bf16, dense; D = 128 or 64. Returns out [B, S, H, D] in ``out_dtype``
     (fp32 or the input dtype; default the input dtype). ``p_mode`` (binding.PREFILL_P_*) selects how the
     probabilities enter the tensor cores: with a residual term (second MMA; the default and the parity mode) or
     rounded once to the input type.

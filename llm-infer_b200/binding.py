@@ -109,6 +109,7 @@ class AttnDecodeArgs(C.Structure):
         ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
         ("kv_early", C.c_uint32),
+        ("kv_capacity", C.c_uint32),
     ]
 
 

@@ -2,6 +2,9 @@
 
     python llm-infer_b200/build.py            # build if sources are newer than the library
     python llm-infer_b200/build.py --force
+    python llm-infer_b200/build.py --check    # checking build (libllm_infer_attn_check.so, -DATTN_BOUNDS_CHECK): the
+                                              # decode passes verify their workspace indices and report instead of
+                                              # accessing; loaded when LLM_INFER_ATTN_LIB names it
     python llm-infer_b200/build.py --trace    # profiling build (libllm_infer_attn_trace.so): the decode kernels
                                               # record time stamps per CTA; loaded when LLM_INFER_ATTN_LIB names it
 
@@ -19,6 +22,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libllm_infer_attn.so")
 TRACE_LIB = os.path.join(HERE, "libllm_infer_attn_trace.so")
+CHECK_LIB = os.path.join(HERE, "libllm_infer_attn_check.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -44,21 +48,23 @@ def needs_build(lib: str = LIB) -> bool:
     return any(os.path.getmtime(f) > t for f in _deps())
 
 
-def build_library(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+def build_library(force: bool = False, verbose: bool = False, trace: bool = False, check: bool = False) -> str:
     """Compile every .cu under csrc/ (one object per file, in parallel) and link the library. ``trace`` builds the
-    profiling variant (-DATTN_TRACE) next to the product library, which it never replaces."""
-    lib = TRACE_LIB if trace else LIB
+    profiling variant (-DATTN_TRACE), ``check`` the index-checking variant (-DATTN_BOUNDS_CHECK), each next to the
+    product library, which they never replace."""
+    lib = TRACE_LIB if trace else CHECK_LIB if check else LIB
     if not force and not needs_build(lib):
         return lib
     nvcc = os.environ.get("NVCC", "nvcc")
-    objdir = os.path.join(HERE, "build_trace" if trace else "build")
+    objdir = os.path.join(HERE, "build_trace" if trace else "build_check" if check else "build")
     os.makedirs(objdir, exist_ok=True)
     procs = []
     objs = []
     for src in sources():
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, *(["-DATTN_TRACE"] if trace else []), "-I", INCLUDE, "-c", src, "-o", obj]
+        defines = ["-DATTN_TRACE"] if trace else ["-DATTN_BOUNDS_CHECK"] if check else []
+        cmd = [nvcc, *NVCC_FLAGS, *defines, "-I", INCLUDE, "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -75,4 +81,5 @@ def build_library(force: bool = False, verbose: bool = False, trace: bool = Fals
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))
+    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv,
+                        check="--check" in sys.argv))

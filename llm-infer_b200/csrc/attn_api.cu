@@ -142,6 +142,10 @@ int decode_impl(const AttnDecodeArgs* a, void* stream_v, const Exchange* xchg) {
     p.min_tiles_per_cta = (min_rows + plan.tile_rows - 1) / plan.tile_rows;
     p.nstages = plan.nstages;
     p.kv_early = a->kv_early ? 1u : 0u;
+    p.kv_capacity = a->kv_capacity;
+#ifdef ATTN_BOUNDS_CHECK
+    p.part_rows = plan.part_o_floats / a->head_dim;
+#endif
     p.status = a->status;
 #ifdef ATTN_TRACE
     p.trace = g_trace_split;
@@ -182,6 +186,10 @@ int decode_impl(const AttnDecodeArgs* a, void* stream_v, const Exchange* xchg) {
     m.batch = a->batch;
     m.kv_len = a->kv_len;
     m.kv_len_uniform = a->kv_len_uniform;
+    m.kv_capacity = a->kv_capacity;
+#ifdef ATTN_BOUNDS_CHECK
+    m.part_rows = plan.part_o_floats / a->head_dim;
+#endif
     m.max_ctas = p.max_ctas;
     m.min_tiles_per_cta = p.min_tiles_per_cta;
     m.seg_prefix = p.seg_prefix;

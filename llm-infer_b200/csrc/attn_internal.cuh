@@ -47,6 +47,10 @@ struct DecodeParams {
     uint32_t min_tiles_per_cta;
     uint32_t nstages;
     uint32_t kv_early;     // AttnDecodeArgs.kv_early
+    uint32_t kv_capacity;  // rows a sequence's caches hold, 0 = not stated (lengths beyond it are clamped and reported)
+#ifdef ATTN_BOUNDS_CHECK
+    uint64_t part_rows;    // rows of part_o / entries of part_lse that exist
+#endif
     uint32_t* status;
     // single-launch (fused merge) mode only: final output and per-segment arrival counters
     void* o;
@@ -80,9 +84,13 @@ struct MergeParams {
     uint32_t batch;
     const uint32_t* kv_len;
     uint32_t kv_len_uniform;
+    uint32_t kv_capacity;
     uint32_t max_ctas;
     uint32_t min_tiles_per_cta;
     const uint32_t* seg_prefix;
+#ifdef ATTN_BOUNDS_CHECK
+    uint64_t part_rows;
+#endif
     // cross-GPU exchange (xchg_world > 0): every CTA stores its locally merged slice of a row (and the row's LSE) into
     // every rank's exchange buffer over NVLink as 64-bit words {value, step}, then collects the xchg_world records of
     // its own slice from this GPU's buffer, waiting (bounded) until each word carries the current step, and merges
@@ -119,6 +127,11 @@ __host__ __device__ inline uint64_t exchange_rank_words(uint64_t rows, uint32_t 
 }
 __host__ __device__ inline uint64_t exchange_words(uint64_t rows, uint32_t head_dim, uint32_t world) {
     return 2ull * world * exchange_rank_words(rows, head_dim, merge_slice_floats(rows, head_dim)) + 2;
+}
+
+// A sequence's length as the kernels use it: clamped to the stated capacity.
+__host__ __device__ inline uint32_t clamped_len(uint32_t len, uint32_t capacity) {
+    return (capacity && len > capacity) ? capacity : len;
 }
 
 // Number of CTAs that actually take tiles, identical in the split and merge passes.

@@ -59,7 +59,7 @@ __device__ __forceinline__ void locate_partials(const MergeParams& p, uint32_t r
             tile0 = p.seg_prefix[seg];
             tile_end = p.seg_prefix[seg + 1];
         } else {
-            const uint64_t tu = (p.kv_len_uniform + p.tile_rows - 1) / p.tile_rows;
+            const uint64_t tu = (clamped_len(p.kv_len_uniform, p.kv_capacity) + p.tile_rows - 1) / p.tile_rows;
             nt = tu * nseg;
             tile0 = tu * seg;
             tile_end = tile0 + tu;
@@ -80,6 +80,12 @@ __device__ __forceinline__ void locate_partials(const MergeParams& p, uint32_t r
             o_stride = l_stride * p.head_dim;
             po = p.part_o + row0 * p.head_dim;
             pl = p.part_lse + row0;
+#ifdef ATTN_BOUNDS_CHECK
+            if (row0 + static_cast<uint64_t>(n - 1) * l_stride >= p.part_rows) {  // would read past the partials
+                if (p.status) atomicOr(p.status, ATTN_STATUS_BAD_INDEX);
+                n = 0;
+            }
+#endif
         }
     } else {
         n = p.n_parts;

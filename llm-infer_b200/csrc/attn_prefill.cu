@@ -6,7 +6,7 @@
 // kv_len = t + 1 (tools/infer.cpp:271-274, src/model/model.cpp:68, attn() of include/kernels_cpu.hpp:140-167).
 // The engine has no S x S kernel of its own; the results are pinned by that row-by-row definition.
 //
-// Layouts (dense, head_dim = 128, 16-bit elements): Q, O [B][S][H][D]; K, V [B][S][Hkv][D] — the engine's
+// Layouts (dense, head_dim = 128 or 64, 16-bit elements): Q, O [B][S][H][D]; K, V [B][S][Hkv][D] — the engine's
 // cache layout [row][kv_head][head_dim] per sequence.
 //
 // One CTA = two 128-row query tiles that share one K/V stream (two query heads of the same kv head at the
@@ -44,10 +44,10 @@ namespace {
 
 constexpr int BM = 128;   // query rows per tile
 constexpr int BN = 128;   // keys per block
-constexpr int HD = 128;   // head_dim
+constexpr int kMaxHD = 128;  // head_dim is 128 or 64 (template HDIM); shared memory is laid out for 128
 constexpr int kThreads = 384;
 constexpr uint32_t kSubTileBytes = 128 * 64 * 2;       // [128 rows][64 elements], 128-byte rows, swizzled
-constexpr uint32_t kTileBytes = 2 * kSubTileBytes;     // 128 x 128 16-bit elements
+constexpr uint32_t kTileBytes = 2 * kSubTileBytes;     // 128 x 128 16-bit elements (head_dim 64 fills the first half)
 constexpr int kStages = 2;
 constexpr uint32_t kTmemCols = 512;
 #ifdef ATTN_TRACE
@@ -198,16 +198,16 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 }
 
 // Instruction descriptor of kind::f16: fp32 accumulate, A format a_fmt and B format b_fmt (0 = f16, 1 = bf16; always
-// given the same value here), A K-major, B K-major (b_mn = 0) or MN-major (b_mn = 1), M = 128, N = 128.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t a_fmt, uint32_t b_fmt, uint32_t b_mn) {
-    return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// given the same value here), A K-major, B K-major (b_mn = 0) or MN-major (b_mn = 1), M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t a_fmt, uint32_t b_fmt, uint32_t b_mn, uint32_t n) {
+    return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
 __device__ __forceinline__ void report_timeout(uint32_t* status) {
     if (status) atomicOr(status, ATTN_STATUS_WAIT_TIMEOUT);
 }
 
-template <bool BF16, int PMODE>
+template <bool BF16, int PMODE, int HDIM>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -223,6 +223,8 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    constexpr int HD = HDIM;
+    constexpr uint32_t kLoadBytes = (HD / 64) * kSubTileBytes;  // bytes of one Q / K / V tile actually loaded
 
     // ---- which two tiles does this CTA own ----
     // The row-tile index is the slowest-varying grid dimension and counts down, so every CTA with the longest
@@ -329,7 +331,7 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 // O_t is stable here: the MMA that produced this S tile was issued after PV_t(j-1)
                 // and the tensor pipe completes in order.
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < HD / 32; ++c) {
                     float o[32];
                     tmem_ld32(tmem_o(t) + lane_addr + c * 32, o);
                     tmem_wait_ld();
@@ -395,7 +397,7 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 // pass through and stall them while they drain.
                 const uint32_t stage = base + kSmemStage + t * kStageTileBytes;
                 const bool f32_out = p.o_dtype == ATTN_DTYPE_F32;
-                const int passes = f32_out ? 4 : 2;
+                const int passes = f32_out ? HD / 32 : HD / 64;
 #pragma unroll
                 for (int pass = 0; pass < 4; ++pass) {
                     if (pass < passes) {
@@ -449,12 +451,12 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             // =============================== TMA producer ===============================
             uint32_t n_q = 0;
             for (int t = 0; t < 2; ++t) n_q += nblk[t] > 0;
-            mbar_arrive_expect_tx(bar(BAR_Q_FULL), n_q * kTileBytes);
+            mbar_arrive_expect_tx(bar(BAR_Q_FULL), n_q * kLoadBytes);
             for (int t = 0; t < 2; ++t) {
                 if (nblk[t] == 0) continue;
                 const uint32_t dst = base + kSmemQ + t * kTileBytes;
                 tma_load_4d(dst, &tm_q, bar(BAR_Q_FULL), 0, m0[t], head[t], b);
-                tma_load_4d(dst + kSubTileBytes, &tm_q, bar(BAR_Q_FULL), 64, m0[t], head[t], b);
+                if (HD > 64) tma_load_4d(dst + kSubTileBytes, &tm_q, bar(BAR_Q_FULL), 64, m0[t], head[t], b);
             }
             for (uint32_t j = 0; j < n_iter; ++j) {
                 const uint32_t st = j % kStages;
@@ -463,23 +465,23 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     break;
                 }
                 const uint32_t kdst = base + kSmemK + st * kTileBytes;
-                mbar_arrive_expect_tx(bar(BAR_K_FULL + st), kTileBytes);
+                mbar_arrive_expect_tx(bar(BAR_K_FULL + st), kLoadBytes);
                 tma_load_4d(kdst, &tm_k, bar(BAR_K_FULL + st), 0, j * BN, kvh, b);
-                tma_load_4d(kdst + kSubTileBytes, &tm_k, bar(BAR_K_FULL + st), 64, j * BN, kvh, b);
+                if (HD > 64) tma_load_4d(kdst + kSubTileBytes, &tm_k, bar(BAR_K_FULL + st), 64, j * BN, kvh, b);
                 if (j >= kStages && !mbar_wait(bar(BAR_V_EMPTY + st), ((j / kStages) - 1) & 1)) {
                     report_timeout(p.status);
                     break;
                 }
                 const uint32_t vdst = base + kSmemV + st * kTileBytes;
-                mbar_arrive_expect_tx(bar(BAR_V_FULL + st), kTileBytes);
+                mbar_arrive_expect_tx(bar(BAR_V_FULL + st), kLoadBytes);
                 tma_load_4d(vdst, &tm_v, bar(BAR_V_FULL + st), 0, j * BN, kvh, b);
-                tma_load_4d(vdst + kSubTileBytes, &tm_v, bar(BAR_V_FULL + st), 64, j * BN, kvh, b);
+                if (HD > 64) tma_load_4d(vdst + kSubTileBytes, &tm_v, bar(BAR_V_FULL + st), 64, j * BN, kvh, b);
             }
         } else if (warp == 9 && lane == 0 && n_iter > 0) {
             // =============================== MMA issuer ===============================
             constexpr uint32_t fmt = BF16 ? 1u : 0u;
-            constexpr uint32_t idesc_qk = instr_desc(fmt, fmt, 0);
-            constexpr uint32_t idesc_pv = instr_desc(fmt, fmt, 1);
+            constexpr uint32_t idesc_qk = instr_desc(fmt, fmt, 0, BN);  // S: 128 rows x 128 keys
+            constexpr uint32_t idesc_pv = instr_desc(fmt, fmt, 1, HD);  // O: 128 rows x head_dim
             // S_t = Q_t K^T: 8 MMAs of K = 16 over head_dim; operands K-major, 128-byte swizzle, 8-row groups 1024 B apart
             auto issue_qk = [&](int t, uint32_t st) {
                 const uint32_t qa = base + kSmemQ + t * kTileBytes;
@@ -558,8 +560,9 @@ prefill_causal_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 }
 
 // ------------------------------------------------------------------------------------------------ host
-// [B][S][heads][128] tensor viewed as (dim, row, head, batch); box = 128 bytes of 128 rows, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* ptr, int32_t dtype, uint32_t batch, uint32_t seq, uint32_t heads) {
+// [B][S][heads][head_dim] tensor viewed as (dim, row, head, batch); box = 128 bytes of 128 rows, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int32_t dtype, uint32_t batch, uint32_t seq, uint32_t heads,
+             uint32_t HD) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return ATTN_ERR_CUDA;
     const cuuint64_t esz = dtype == ATTN_DTYPE_F32 ? 4 : 2;
@@ -592,7 +595,7 @@ extern "C" int attn_prefill_causal(const AttnPrefillArgs* a, void* stream_v) {
     if (a->n_heads % a->n_kv_heads != 0) return ATTN_ERR_INVALID_ARG;
     if (a->dtype != ATTN_DTYPE_F16 && a->dtype != ATTN_DTYPE_BF16) return ATTN_ERR_UNSUPPORTED;
     if (a->o_dtype != ATTN_DTYPE_F32 && a->o_dtype != a->dtype) return ATTN_ERR_UNSUPPORTED;
-    if (a->head_dim != HD) return ATTN_ERR_UNSUPPORTED;
+    if (a->head_dim != 128 && a->head_dim != 64) return ATTN_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
          reinterpret_cast<uintptr_t>(a->o)) & 15u)
         return ATTN_ERR_ALIGNMENT;
@@ -602,10 +605,10 @@ extern "C" int attn_prefill_causal(const AttnPrefillArgs* a, void* stream_v) {
     if (dev.cc_major != 10) return ATTN_ERR_DEVICE;
 
     CUtensorMap tm_q, tm_k, tm_v, tm_o;
-    if ((rc = make_map(&tm_o, a->o, a->o_dtype, a->batch, a->seq_len, a->n_heads)) != ATTN_OK) return rc;
-    if ((rc = make_map(&tm_q, a->q, a->dtype, a->batch, a->seq_len, a->n_heads)) != ATTN_OK) return rc;
-    if ((rc = make_map(&tm_k, a->k, a->dtype, a->batch, a->seq_len, a->n_kv_heads)) != ATTN_OK) return rc;
-    if ((rc = make_map(&tm_v, a->v, a->dtype, a->batch, a->seq_len, a->n_kv_heads)) != ATTN_OK) return rc;
+    if ((rc = make_map(&tm_o, a->o, a->o_dtype, a->batch, a->seq_len, a->n_heads, a->head_dim)) != ATTN_OK) return rc;
+    if ((rc = make_map(&tm_q, a->q, a->dtype, a->batch, a->seq_len, a->n_heads, a->head_dim)) != ATTN_OK) return rc;
+    if ((rc = make_map(&tm_k, a->k, a->dtype, a->batch, a->seq_len, a->n_kv_heads, a->head_dim)) != ATTN_OK) return rc;
+    if ((rc = make_map(&tm_v, a->v, a->dtype, a->batch, a->seq_len, a->n_kv_heads, a->head_dim)) != ATTN_OK) return rc;
 
     PrefillParams p{};
     p.o = a->o;
@@ -642,12 +645,17 @@ extern "C" int attn_prefill_causal(const AttnPrefillArgs* a, void* stream_v) {
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
         return ATTN_OK;
     };
-    if (a->dtype == ATTN_DTYPE_BF16) {
-        return a->p_mode == ATTN_PREFILL_P_INPUT_TYPE ? launch(prefill_causal_kernel<true, kPInput>)
-                                                      : launch(prefill_causal_kernel<true, kPResidual>);
+    const bool single = a->p_mode == ATTN_PREFILL_P_INPUT_TYPE;
+    if (a->head_dim == 128) {
+        if (a->dtype == ATTN_DTYPE_BF16) {
+            return single ? launch(prefill_causal_kernel<true, kPInput, 128>) : launch(prefill_causal_kernel<true, kPResidual, 128>);
+        }
+        return single ? launch(prefill_causal_kernel<false, kPInput, 128>) : launch(prefill_causal_kernel<false, kPResidual, 128>);
     }
-    return a->p_mode == ATTN_PREFILL_P_INPUT_TYPE ? launch(prefill_causal_kernel<false, kPInput>)
-                                                  : launch(prefill_causal_kernel<false, kPResidual>);
+    if (a->dtype == ATTN_DTYPE_BF16) {
+        return single ? launch(prefill_causal_kernel<true, kPInput, 64>) : launch(prefill_causal_kernel<true, kPResidual, 64>);
+    }
+    return single ? launch(prefill_causal_kernel<false, kPInput, 64>) : launch(prefill_causal_kernel<false, kPResidual, 64>);
 }
 
 #ifdef ATTN_TRACE

@@ -60,11 +60,11 @@ struct SegTable {
         s.b = seg / p.head_groups;
         s.hg = seg - s.b * p.head_groups;
         if (p.kv_len) {
-            s.len = p.kv_len[s.b];
+            s.len = clamped_len(p.kv_len[s.b], p.kv_capacity);
             s.tile0 = prefix[seg];
             s.tile_end = prefix[seg + 1];
         } else {
-            s.len = p.kv_len_uniform;
+            s.len = clamped_len(p.kv_len_uniform, p.kv_capacity);
             s.tile0 = seg * tiles_uniform;
             s.tile_end = s.tile0 + tiles_uniform;
         }
@@ -207,7 +207,9 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     uint32_t tiles_uniform = 0;
     if (p.kv_len) {
         for (uint32_t s = tid; s < nseg; s += kThreads) {
-            uint32_t len = p.kv_len[s / p.head_groups];
+            const uint32_t stated = p.kv_len[s / p.head_groups];
+            const uint32_t len = clamped_len(stated, p.kv_capacity);
+            if (len != stated && blockIdx.x == 0 && p.status) atomicOr(p.status, ATTN_STATUS_BAD_SHAPE);
             prefix[s + 1] = (len + TT - 1) / TT;
         }
         if (tid == 0) prefix[0] = 0;
@@ -234,7 +236,7 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
             for (uint32_t s = tid; s <= nseg; s += kThreads) p.seg_prefix[s] = prefix[s];
         }
     } else {
-        tiles_uniform = (p.kv_len_uniform + TT - 1) / TT;
+        tiles_uniform = (clamped_len(p.kv_len_uniform, p.kv_capacity) + TT - 1) / TT;
         nt = static_cast<uint64_t>(tiles_uniform) * nseg;
         __syncthreads();
     }
@@ -405,6 +407,12 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         const float inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
         const size_t slot = (static_cast<size_t>(cta) + seg.seg) * TS + ts;
         const size_t row0 = (slot * HPC + hh) * G;
+#ifdef ATTN_BOUNDS_CHECK
+        if (row0 + G > p.part_rows) {  // the slot arithmetic left the workspace: record it, write nothing
+            if (lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_BAD_INDEX);
+            return;
+        }
+#endif
         constexpr float kLn2 = 0.6931471805599453f;
         if (gq < static_cast<int>(G)) {
             float* dst = p.part_o + (row0 + gq) * D + cq * 2;

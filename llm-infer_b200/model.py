@@ -208,13 +208,14 @@ class Llama:
         self.tokens.copy_(self.next_token)
 
     def can_prefill(self, prompts, n_new: int = 0) -> bool:
-        """Whether prefill() can take these prompts: head_dim 128 (the tensor-core attention kernel), inner dimensions
-        in multiples of 64, and every sequence inside its cache (no sliding window during the prompt or after it)."""
+        """Whether prefill() can take these prompts: head_dim 128 or 64 (the tensor-core attention kernel), inner
+        dimensions in multiples of 64, and every sequence inside its cache (no sliding window during the prompt or after
+        it)."""
         c = self.cfg
-        dims_ok = c.head_dim == 128 and c.dim % 64 == 0 and c.hidden_dim % 64 == 0 and (c.n_heads * c.head_dim) % 64 == 0
+        dims_ok = c.head_dim in (64, 128) and c.dim % 64 == 0 and c.hidden_dim % 64 == 0 and (c.n_heads * c.head_dim) % 64 == 0
         return dims_ok and max(len(p) for p in prompts) + n_new <= c.max_seq_len
 
-    def prefill(self, prompts) -> None:
+    def prefill(self, prompts, exact: bool = True) -> None:
         """The prompt phase for all sequences at once instead of one token per step: the tokens of every prompt are
         packed into one matrix of rows; per layer one tensor-core GEMM per projection (attn_gemm_f16; Q8_0 weights are
         expanded per matrix into an fp16 value / residual pair first), the rotary kernel that also fills the KV caches,
@@ -222,11 +223,14 @@ class Llama:
         row-wise norm / SwiGLU steps. Per token this is the engine's forward pass (src/model/block.cpp:105-223) with
         InferenceMode::Prefill for all but the last token of a prompt (src/model/model.cpp:74-76); the last tokens go
         through the final norm, classifier and greedy pick. Afterwards the caches hold rows 0 .. len-1 of every
-        sequence and self.next_token / self.tokens / self.logits are what the token-at-a-time loop would have left."""
+        sequence and self.next_token / self.tokens / self.logits are what the token-at-a-time loop would have left.
+        ``exact`` = False drops the residual terms (activations and Q8_0 weights enter the tensor cores rounded once to
+        fp16, one MMA instead of two or three): a third of the tensor work, results within about 1e-3 relative, no
+        longer guaranteed to give the token-at-a-time path's greedy tokens."""
         import numpy as np
         c, w, B, dev = self.cfg, self.w, self.batch, self.device
         if len(prompts) != B or not self.can_prefill(prompts):
-            raise ValueError("prefill() needs one prompt per sequence, head_dim 128 and prompts that fit the cache")
+            raise ValueError("prefill() needs one prompt per sequence, head_dim 64 or 128 and prompts that fit the cache")
         q8 = self.weight_type == "q8_0"
         lens = [len(p) for p in prompts]
         starts = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
@@ -256,10 +260,13 @@ class Llama:
                 rows, n = wmat.shape[0], wmat.shape[1] // 34 * 32
                 pair = (w_hi[:rows * n].view(rows, n), w_lo[:rows * n].view(rows, n))
                 A.dequant_q8_0_pair(wmat, out=pair)
-                A.gemm_f16(a_pair[0], a_pair[1], pair[0], out=out, accumulate=accumulate, status=self.status)
-                A.gemm_f16(a_pair[0], None, pair[1], out=out, accumulate=True, status=self.status)
+                A.gemm_f16(a_pair[0], a_pair[1] if exact else None, pair[0], out=out, accumulate=accumulate,
+                           status=self.status)
+                if exact:
+                    A.gemm_f16(a_pair[0], None, pair[1], out=out, accumulate=True, status=self.status)
             else:
-                A.gemm_f16(a_pair[0], a_pair[1], wmat, out=out, accumulate=accumulate, status=self.status)
+                A.gemm_f16(a_pair[0], a_pair[1] if exact else None, wmat, out=out, accumulate=accumulate,
+                           status=self.status)
 
         self._embed(w["embed"], tokens, out=x, status=self.status)
         for l in range(c.n_layers):
@@ -330,7 +337,8 @@ class Llama:
         (and the logits each pick was made from, [B, n_new, vocab], when asked). ``timing`` (a dict) receives the
         device time of the prompt phase and of the generation phase in ms (CUDA events). ``prompt_mode``: "token" feeds
         the prompts one token per step as described; "batched" runs prefill() (all prompt tokens at once on the tensor
-        cores); "auto" picks "batched" whenever can_prefill() allows it."""
+        cores); "auto" picks "batched" whenever can_prefill() allows it; "batched-single-rounding" is prefill() with
+        exact = False."""
         B = self.batch
         if len(prompts) != B or any(len(p) == 0 for p in prompts):
             raise ValueError("one non-empty prompt per sequence of the batch")
@@ -341,12 +349,12 @@ class Llama:
         out = torch.zeros((B, n_new), dtype=torch.int32, device=self.device)
         out_logits = torch.zeros((B, n_new, self.cfg.vocab_size), device=self.device) if want_logits else None
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        if prompt_mode not in ("auto", "token", "batched"):
-            raise ValueError("prompt_mode must be 'auto', 'token' or 'batched'")
-        batched = prompt_mode == "batched" or (prompt_mode == "auto" and self.can_prefill(prompts, n_new))
+        if prompt_mode not in ("auto", "token", "batched", "batched-single-rounding"):
+            raise ValueError("prompt_mode must be 'auto', 'token', 'batched' or 'batched-single-rounding'")
+        batched = prompt_mode.startswith("batched") or (prompt_mode == "auto" and self.can_prefill(prompts, n_new))
         ev[0].record()
         if batched:
-            self.prefill(prompts)
+            self.prefill(prompts, exact=prompt_mode != "batched-single-rounding")
         for step in range(0 if batched else longest):
             # a sequence that has not started yet is fed its first token at position 0 again (row 0 is rewritten)
             pos = [max(step - d, 0) for d in delay]

@@ -16,8 +16,14 @@ gather, merge order) can be exercised with CPU ranks over gloo.
 """
 from __future__ import annotations
 
+import time
+
 import torch
 import torch.distributed as dist
+
+
+class GatherTimeout(RuntimeError):
+    """The all-gather of a sharded decode did not complete before its deadline (a rank never joined)."""
 
 
 def shard_rows(total_rows: int, world: int, rank: int) -> tuple[int, int]:
@@ -31,7 +37,16 @@ def shard_rows(total_rows: int, world: int, rank: int) -> tuple[int, int]:
 class ShardedDecode:
     """Decode attention for one sequence whose KV rows are spread over the ranks of ``group``."""
 
-    def __init__(self, n_heads: int, head_dim: int, *, device, group=None, decode_fn=None, merge_fn=None):
+    def __init__(self, n_heads: int, head_dim: int, *, device, group=None, decode_fn=None, merge_fn=None,
+                 watchdog_s: float | None = None):
+        """``watchdog_s``: host-side deadline for the all-gather. The collective is then issued asynchronously and
+        polled from the host; if it has not completed when the deadline passes (a rank died or never reached the
+        step), ``gather()`` raises GatherTimeout instead of blocking for ever, after ``on_timeout`` (if set) has
+        run - the place to abort the communicator (ncclCommAbort through the process group) or to mark the rank
+        as failed. Nothing is waited for on the device and no GPU wait is left spinning: the decision is made on the
+        host. Not for use inside a CUDA-graph capture (the poll needs the host)."""
+        self.watchdog_s = watchdog_s
+        self.on_timeout = None
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -65,8 +80,27 @@ class ShardedDecode:
         return o, lse
 
     def gather(self):
-        """Step 2: one all-gather of rec_len floats per rank, on the current stream."""
-        dist.all_gather_into_tensor(self.gathered.view(-1), self.record, group=self.group)
+        """Step 2: one all-gather of rec_len floats per rank, on the current stream (with a watchdog: polled from the
+        host against the deadline)."""
+        if self.watchdog_s is None:
+            dist.all_gather_into_tensor(self.gathered.view(-1), self.record, group=self.group)
+            return self.gathered
+        work = dist.all_gather_into_tensor(self.gathered.view(-1), self.record, group=self.group, async_op=True)
+        deadline = time.monotonic() + self.watchdog_s
+        while True:
+            try:
+                if work.is_completed():
+                    break
+                failure = None
+            except RuntimeError as e:  # the backend noticed a dead peer before the deadline did
+                failure = e
+            if failure is not None or time.monotonic() > deadline:
+                if self.on_timeout is not None:
+                    self.on_timeout()
+                why = f"failed: {failure}" if failure is not None else f"did not complete within {self.watchdog_s} s"
+                raise GatherTimeout(f"rank {self.rank}: all-gather of the partial (O, LSE) records {why}") from failure
+            time.sleep(0.0005)
+        work.wait()  # orders the current stream after the collective; returns at once
         return self.gathered
 
     def merge(self, out=None, out_dtype=torch.float32):

@@ -184,6 +184,56 @@ def test_early_streaming_after_an_appending_kernel(attention, wl, checker):
     assert int(ws.status.item()) == 0
 
 
+def test_length_beyond_the_cache_is_clamped_and_reported(attention, wl, checker):
+    """A corrupted kv_len[] entry larger than the cache: the kernels clamp it to the stated capacity and raise
+    ATTN_STATUS_BAD_SHAPE instead of reading past the cache."""
+    import torch
+    from gpu_util import check_close, to_device
+    q, k, v = _rand(wl, 91, 2, 32, 8, 128, 300)
+    lens = torch.tensor([100, 5000], dtype=torch.int32, device="cuda")
+    ws = attention.DecodeWorkspace(2, 32, 8, 128)
+    out = attention.attn_decode(to_device(q, "f32"), to_device(k, "f16"), to_device(v, "f16"), lens, workspace=ws)
+    torch.cuda.synchronize()
+    assert int(ws.status.item()) == 2  # ATTN_STATUS_BAD_SHAPE
+    want = checker.attn_decode(q, k, v, np.array([100, 300], np.uint32))
+    check_close(wl, out.cpu().numpy(), want, "clamped length")
+
+
+def test_checking_build_runs_clean(pkg, wl, checker, tmp_path):
+    """The -DATTN_BOUNDS_CHECK build (the decode passes verify their workspace indices and report ATTN_STATUS_BAD_INDEX
+    instead of accessing) gives the same results with no status bit on uniform, ragged and single-long-sequence
+    shapes. Runs in a child process because the library is chosen when the binding is first loaded."""
+    import subprocess
+    import sys
+    from conftest import ROOT
+    lib = pkg.build.build_library(check=True)
+    code = f"""
+import sys, numpy as np, torch
+sys.path.insert(0, {ROOT!r}); sys.path.insert(0, {ROOT!r} + '/tests')
+from conftest import load_package
+pkg = load_package()
+from llm_infer_b200 import attention, binding
+assert binding.LIB_PATH.endswith('_check.so')
+import oracle
+wl = pkg.workloads
+for (B, T, lens) in ((3, 700, [700, 1, 333]), (1, 20000, None), (16, 512, None)):
+    q, k, v = wl.decode_inputs(wl.DecodeShape('c', 5, B, 32, 8, 128, T, 'f32', 'f16'))
+    ws = attention.DecodeWorkspace(B, 32, 8, 128)
+    l = None if lens is None else torch.tensor(lens, dtype=torch.int32, device='cuda')
+    out = attention.attn_decode(torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), l, workspace=ws)
+    torch.cuda.synchronize()
+    assert int(ws.status.item()) == 0, ws.status.item()
+    want = oracle.best().attn_decode(q, k, v, None if lens is None else np.array(lens, np.uint32))
+    a, r = wl.error_metrics(out.cpu().numpy(), want)
+    assert a <= wl.ABS_TOL and r <= wl.REL_TOL, (a, r)
+print('ok')
+"""
+    import os
+    env = dict(os.environ, LLM_INFER_ATTN_LIB=lib)
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and res.stdout.strip().endswith("ok"), res.stdout + res.stderr
+
+
 def test_max_ctas_limits_split_without_changing_result(attention, wl, checker):
     from gpu_util import check_close, run_decode
     q, k, v = _rand(wl, 15, 1, 32, 8, 128, 5000)

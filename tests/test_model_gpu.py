@@ -163,6 +163,53 @@ def test_whole_prompt_prefill_equals_the_token_loop(M, port):
     _run_case(M, port, cfg, prompts[:2], n_new=6, seed=17, weight_type="q8_0", prompt_mode="batched")
 
 
+def test_full_depth_q8_0_against_its_own_weights_in_fp16(M):
+    """All 32 layers at the 8B model's widths (small vocabulary): the Q8_0 model against the SAME weights expanded to
+    fp16 and run through the fp16 kernels (the path that is pinned on the engine's CPU matmul). The fp16 copy rounds
+    each weight once (2^-12 relative), so the two runs are compared with tolerances, teacher-forced on one token
+    stream: logits within 2e-2 of the row's RMS at every step, and the first step at which the greedy picks differ is
+    reported (a near-tie is the only legitimate reason)."""
+    import torch
+    from llm_infer_b200 import quant
+    cfg = M.ModelConfig(dim=4096, hidden_dim=14336, n_layers=32, n_heads=32, n_kv_heads=8, head_dim=128,
+                        vocab_size=4096, max_seq_len=96, norm_eps=1e-5, rope_theta=500000.0)
+    wq = M.random_weights(cfg, 23, device="cuda", weight_type="q8_0")
+    wf = {}
+    for name, t in wq.items():
+        if t.dtype != torch.uint8:
+            wf[name] = t
+            continue
+        b = t.view(*t.shape[:-1], t.shape[-1] // 34, 34)
+        d = b[..., :2].contiguous().view(torch.float16).float()
+        q = b[..., 2:].contiguous().view(torch.int8).float()
+        wf[name] = (d * q).reshape(*t.shape[:-1], -1).half()
+    rng = np.random.default_rng(23)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (40, 64)]
+    n_new = 12
+    a = M.Llama(cfg, wq, batch=2, weight_type="q8_0")
+    del wq
+    tok_a, log_a = a.generate(prompts, n_new, want_logits=True)
+    del a
+    torch.cuda.empty_cache()
+    b = M.Llama(cfg, wf, batch=2, weight_type="f16")
+    del wf
+    # teacher forcing: the fp16 model reads the Q8_0 model's picks as part of its prompt, one more per step
+    first_diff = None
+    for i in range(n_new):
+        forced = [p + tok_a[s, :i].tolist() for s, p in enumerate(prompts)]
+        tok_b, log_b = b.generate(forced, 1, want_logits=True)
+        la, lb = log_a[:, i].numpy(), log_b[:, 0].numpy()
+        rms = float(np.sqrt(np.mean(la ** 2)))
+        assert np.abs(la - lb).max() <= 2e-2 * rms, (i, np.abs(la - lb).max(), rms)
+        if first_diff is None and not np.array_equal(tok_a[:, i].numpy(), tok_b[:, 0].numpy()):
+            srt = np.sort(la, axis=-1)
+            first_diff = (i, float((srt[:, -1] - srt[:, -2]).min()))
+    print("first step with a different greedy pick (step, smallest top-2 margin there):", first_diff)
+    assert len(set(tok_a.flatten().tolist())) > 4
+    if first_diff is not None:
+        assert first_diff[1] < 2e-2 * rms, "the picks may only differ on a near-tie"
+
+
 def test_small_steps_against_port(M, port):
     """RMSNorm, SwiGLU, embedding and argmax alone (fp32: a few ulp; argmax and embedding exact)."""
     import torch

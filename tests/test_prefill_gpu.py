@@ -63,11 +63,20 @@ def test_golden_vectors(attention, wl):
     (1, 1, 4, 1, "bf16"), (1, 2, 4, 2, "f16"), (2, 127, 8, 2, "bf16"), (1, 128, 8, 2, "f16"), (1, 129, 8, 2, "bf16"),
     (2, 255, 4, 4, "bf16"), (1, 256, 4, 4, "f16"), (1, 257, 6, 6, "bf16"), (3, 300, 8, 1, "bf16"),
     (1, 512, 32, 8, "bf16"), (1, 640, 3, 1, "f16"), (1, 1000, 8, 8, "bf16")])
-def test_every_row_against_cpu_attn(attention, wl, checker, B, S, H, Hkv, dtype):
+@pytest.mark.parametrize("D", [128, 64])
+def test_every_row_against_cpu_attn(attention, wl, checker, B, S, H, Hkv, dtype, D):
     from gpu_util import check_close
-    q, k, v = wl.prefill_inputs(wl.PrefillShape("t", S * 7 + H, B, S, H, Hkv, 128, dtype))
+    q, k, v = wl.prefill_inputs(wl.PrefillShape("t", S * 7 + H, B, S, H, Hkv, D, dtype))
     got = _run(attention, q, k, v, dtype)
-    check_close(wl, got, _want(wl, checker, q, k, v, dtype), f"B{B} S{S} H{H}/{Hkv} {dtype}")
+    check_close(wl, got, _want(wl, checker, q, k, v, dtype), f"B{B} S{S} H{H}/{Hkv} D{D} {dtype}")
+
+
+def test_head_dim_64_16_bit_output(attention, wl, checker):
+    """TinyLlama-shaped heads (32 / 4, head_dim 64), bf16 in and out."""
+    q, k, v = wl.prefill_inputs(wl.PrefillShape("t", 64, 1, 333, 32, 4, 64, "bf16"))
+    got = _run(attention, q, k, v, "bf16", out_fp32=False)
+    want = _want(wl, checker, q, k, v, "bf16")
+    assert (np.abs(got - want) <= 1e-4 + 2.0 ** -8 * np.abs(want)).all()
 
 
 def test_c3_llama3_prefill_full_size_sampled_rows(attention, wl, checker):
@@ -117,9 +126,9 @@ def test_single_rounding_mode_is_close_but_not_the_parity_mode(attention, wl, ch
 def test_unsupported_head_dim_is_refused(built_lib, pkg):
     import torch
     b = pkg.binding
-    t = torch.zeros((1, 16, 4, 64), dtype=torch.float16, device="cuda")
+    t = torch.zeros((1, 16, 4, 96), dtype=torch.float16, device="cuda")
     a = b.AttnPrefillArgs()
     a.o = a.q = a.k = a.v = t.data_ptr()
     a.o_dtype = a.dtype = b.DTYPE_F16
-    a.batch, a.seq_len, a.n_heads, a.n_kv_heads, a.head_dim = 1, 16, 4, 4, 64
+    a.batch, a.seq_len, a.n_heads, a.n_kv_heads, a.head_dim = 1, 16, 4, 4, 96
     assert built_lib.attn_prefill_causal(C.byref(a), None) == -2

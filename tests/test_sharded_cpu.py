@@ -98,6 +98,50 @@ def test_sharded_decode_over_gloo(tmp_path, world, total_rows, fail_rank):
         assert np.isneginf(lse[r]).all() == (r1 == r0)
 
 
+def _watchdog_worker(rank, world, port_no, result_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port_no)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    pkg = load_package()
+    import oracle
+    from llm_infer_b200.sharded import GatherTimeout, ShardedDecode
+    port = oracle.Oracle("port")
+    op = ShardedDecode(8, 64, device="cpu", decode_fn=_cpu_decode(port), merge_fn=_cpu_merge(port), watchdog_s=1.0)
+    fired = []
+    op.on_timeout = lambda: fired.append(True)
+    outcome = "no-collective"
+    if rank == 0:
+        # rank 1 never joins this step (host-side fault injection: it simply does not call the collective)
+        try:
+            op.gather()
+            outcome = "completed"
+        except GatherTimeout:
+            outcome = "timeout" if fired else "timeout-without-callback"
+    else:
+        import time
+        time.sleep(3.0)  # alive, connected, but never reaches the step
+    with open(os.path.join(result_dir, f"watchdog{rank}.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)  # a collective is still pending on rank 0: leave without tearing the group down
+
+
+def test_gather_watchdog_fires_when_a_rank_never_joins(tmp_path):
+    """The host-side deadline around the all-gather: with one of two ranks skipping the step, the other gets
+    GatherTimeout (after its on_timeout hook ran) instead of blocking."""
+    ctx = mp.get_context("spawn")
+    port_no = _free_port()
+    procs = [ctx.Process(target=_watchdog_worker, args=(r, 2, port_no, str(tmp_path))) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(timeout=120)
+        assert not pr.is_alive() and pr.exitcode == 0
+    assert (tmp_path / "watchdog0.txt").read_text() == "timeout"
+    assert (tmp_path / "watchdog1.txt").read_text() == "no-collective"
+
+
 def test_shard_rows_partition():
     pkg = load_package()
     from llm_infer_b200.sharded import shard_rows
