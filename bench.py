@@ -464,6 +464,62 @@ def decode_trace(torch):
                                                         "merge": "[min, median, max] over CTAs, same origin"}}), flush=True)
 
 
+def attention_symbol_measure(torch, hbm_peak: float):
+    """The engine's own kernel symbol (include/kernels.cuh:26: fp32 q/o, fp16 K/V, one sequence, one launch that
+    splits and merges) driven the way the engine drives it: a CUDA-graph kernel node whose arguments are refreshed for
+    every token (include/model/device.hpp:219-237), then the graph launch. KV 4096 and 131072, 32/8 heads of 128; the
+    caches rotate through more copies than fit in L2."""
+    import ctypes as C
+    from llm_infer_b200 import binding
+    lib = binding.load()
+    rt = C.CDLL("libcudart.so.12")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    H, Hkv, D = 32, 8, 128
+    nbytes = lib.attention_workspace_bytes(H, Hkv, D)
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    if lib.attention_configure(H, Hkv, D, 0.0, ws.data_ptr(), nbytes, stream) != 0:
+        raise RuntimeError("attention_configure failed")
+    q = torch.randn((H, D), device=dev)
+    o = torch.empty((H, D), device=dev)
+    res = {}
+    for T in (4096, 131072):
+        per_copy = 2 * T * Hkv * D * 2
+        n_copies = max(2, min(64, int(300e6 // per_copy) + 1))
+        ks = [torch.randn((T, Hkv, D), device=dev, dtype=torch.float16) for _ in range(n_copies)]
+        vs = [torch.randn((T, Hkv, D), device=dev, dtype=torch.float16) for _ in range(n_copies)]
+        graph, node, gexec = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        assert rt.cudaGraphCreate(C.byref(graph), 0) == 0
+        assert lib.attention_graph_add_node(graph, C.byref(node), None, 0, o.data_ptr(), q.data_ptr(), ks[0].data_ptr(),
+                                            vs[0].data_ptr(), T) == 0
+        rt.cudaGraphInstantiate.argtypes = [C.c_void_p, C.c_void_p, C.c_ulonglong]
+        assert rt.cudaGraphInstantiate(C.byref(gexec), graph, 0) == 0
+        rt.cudaGraphLaunch.argtypes = [C.c_void_p, C.c_void_p]
+
+        def token(i):
+            j = i % n_copies
+            lib.attention_graph_exec_update(gexec, node, o.data_ptr(), q.data_ptr(), ks[j].data_ptr(), vs[j].data_ptr(), T)
+            rt.cudaGraphLaunch(gexec, stream)
+
+        for i in range(5):
+            token(i)
+        n = 100 if T <= 4096 else 30
+        us = time_steps(torch, token, n) / n * 1e3
+        bits = C.c_uint32(0)
+        lib.attention_status(C.byref(bits), 0, stream)
+        alg = per_copy + 2 * H * D * 4
+        res[f"kv{T}"] = {"us_per_token": round(us, 2), "gbs": round(alg / us / 1e3, 1),
+                         "frac_of_peak": round(alg / us / 1e3 / hbm_peak, 3), "status_bits": int(bits.value)}
+        rt.cudaGraphExecDestroy.argtypes = [C.c_void_p]
+        rt.cudaGraphDestroy.argtypes = [C.c_void_p]
+        rt.cudaGraphExecDestroy(gexec)
+        rt.cudaGraphDestroy(graph)
+        del ks, vs
+    res["note"] = ("one graph launch per token with the node's arguments refreshed first, back to back; single-launch "
+                   "mode (the CTA that delivers a segment's last partial merges it)")
+    return res
+
+
 def gemm_measure(torch, steps: int, warmup: int, tflops_peak: float, peak_kind: str, small: bool = False):
     """The projection GEMM of the whole-prompt path alone (attn_gemm_f16: tokens x weights on the tensor cores,
     activations as an fp16 value + residual pair = two MMAs per k-step), on the four projections of a
@@ -657,6 +713,10 @@ def run_single(args):
         extra["gemv_layer"] = gemv_measure(torch, 60, 6, hbm_peak, peak_kind)
     except Exception as e:
         extra["gemv_layer"] = {"error": str(e)[:300]}
+    try:
+        extra["attention_symbol"] = attention_symbol_measure(torch, hbm_peak)
+    except Exception as e:
+        extra["attention_symbol"] = {"error": str(e)[:300]}
     try:
         extra["prompt_gemm"] = gemm_measure(torch, 10, 3, tflops_peak, peak_kind)
     except Exception as e:

@@ -83,9 +83,15 @@ __device__ __forceinline__ void load_a(uint32_t (&r)[4], uint32_t seg_addr, uint
     r[3] = bytes_to_half2<2>(v1);
 }
 
-template <uint32_t CB>
-__global__ void __launch_bounds__(kThreads, 1) gemv_q8_0_kernel(const __grid_constant__ CUtensorMap tm_w,
-                                                                  const __grid_constant__ Params p) {
+// NW warps per CTA. REGX: the inner dimension is exactly NW chunks, so a warp always multiplies by the same CB blocks
+// of the activations and keeps them in registers as MMA B fragments (64 registers for CB = 8) for the whole launch:
+// no shared memory for the activations (which at batch 8 x 4096 would take 128 KB and leave room for 8 warps only), no
+// shared-memory loads for them in the inner loop, and twice the warps per SM to hide the latency of the
+// byte -> fp16 operand construction.
+template <uint32_t CB, int NW, bool REGX>
+__global__ void __launch_bounds__(NW * 32, 1) gemv_q8_0_kernel(const __grid_constant__ CUtensorMap tm_w,
+                                                                 const __grid_constant__ Params p) {
+    constexpr uint32_t kWarps = NW, kThreads = NW * 32;
     constexpr uint32_t kChunkBlocks = CB, kSegBytes = seg_bytes(CB), kSegPitch = kSegBytes, kStageBytes = stage_bytes(CB);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // tile loads want 128-byte alignment
@@ -149,11 +155,34 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q8_0_kernel(const __grid_con
     const uint32_t* my_x = s_x + (has_col ? g : 0) * p.x_col_pitch + t * 4;
     bool timed_out = false;
     uint32_t item = 0, round = 0;
+    uint4 xr[REGX ? CB : 1][2];
+    if constexpr (REGX) {
+        // B fragments of this warp's chunk (blocks [warp*CB, +CB) of sequence g), straight from global memory: the
+        // prepared form is already laid out as fragments, fp32 activations are split here
+#pragma unroll
+        for (uint32_t bi = 0; bi < CB; ++bi) {
+#pragma unroll
+            for (uint32_t s2 = 0; s2 < 2; ++s2) {
+                xr[bi][s2] = make_uint4(0, 0, 0, 0);
+                if (has_col) {
+                    const size_t e = static_cast<size_t>(g) * p.x_batch_stride + 32 * (warp * CB + bi) + 16 * s2 + 4 * t;
+                    if (p.x_split) {
+                        xr[bi][s2] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(p.x) + e);
+                    } else {
+                        const float4 v = *reinterpret_cast<const float4*>(p.x + e);
+                        xr[bi][s2] = split_activations(v.x, v.y, v.z, v.w);
+                    }
+                }
+            }
+        }
+    }
     for (uint32_t slice = slice_begin; slice < slice_end; ++slice) {
         // Activations of this slice as B fragments: for sequence c, block blk, k-step s, quarter t: four 32-bit words
         // {hi(x0,x1), hi(x2,x3), lo(x0,x1), lo(x2,x3)} of the elements x[32 blk + 16 s + 4 t .. +4). Every warp has
         // passed the previous slice's last block-wide barrier, so nobody still reads the old fragments.
-        if (p.x_split) {
+        if constexpr (REGX) {
+            // activations are in registers
+        } else if (p.x_split) {
             // prepared activations: one bulk copy per sequence, as they are; the barrier's phase counts the slices
             __syncthreads();  // (barrier initialised; with more than one slice: the old fragments are no longer read)
             if (tid == 0) {
@@ -200,7 +229,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q8_0_kernel(const __grid_con
                             load_a<true>(ahi, seg_hi, bi, t);
                         }
                         uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
-                        if (has_col) {
+                        if constexpr (REGX) {
+                            x0 = xr[bi][0];
+                            x1 = xr[bi][1];
+                        } else if (has_col) {
                             x0 = *reinterpret_cast<const uint4*>(xb + bi * 32);
                             x1 = *reinterpret_cast<const uint4*>(xb + bi * 32 + 16);
                         }
@@ -222,10 +254,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q8_0_kernel(const __grid_con
                         issue(item + p.stages);
                     }
                 }
-                store_partial(red, part, warp, g, t, tot);
+                store_partial<NW>(red, part, warp, g, t, tot);
             }
             __syncthreads();
-            reduce_and_store(p, red, s_acc, tid, parts, gi, rg, slice, slice_begin, slice_end);
+            reduce_and_store<NW>(p, red, s_acc, tid, parts, gi, rg, slice, slice_begin, slice_end);
         }
     }
     if (timed_out && lane == 0 && p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
@@ -290,6 +322,15 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     Plan wide{};
     if (!make_plan(8, &plan)) return ATTN_ERR_UNSUPPORTED;  // (the slices must be equal and one must fit next to the ring)
     if (k_split == 1 && make_plan(16, &wide) && wide.slices == 1) plan = wide;
+    // Inner dimension of exactly 16 chunks of 8 blocks (n = 4096, the model width of the 8B shape): 16 warps, each
+    // with its chunk of the activations in registers, two stages per warp, nothing else staged.
+    constexpr uint32_t kRegxWarps = 16;
+    const bool regx = k_split == 1 && n_blocks == kRegxWarps * 8;
+    if (regx) {
+        plan = Plan{8, 1, 2,
+                    2 * 2 * kRegxWarps * 128 * sizeof(float) + (kRegxWarps * kMaxStages + 2) * sizeof(uint64_t) + 128 +
+                        static_cast<size_t>(2) * kRegxWarps * stage_bytes(8)};
+    }
     const uint32_t slices = plan.slices, stages = plan.stages, slice_blocks = n_blocks / slices;
     const size_t smem = plan.smem;
 
@@ -319,9 +360,11 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     p.x_col_pitch = slice_blocks * 32 + 16;
     p.acc_groups = (slices > 1 && k_split == 1) ? groups_per_cta : 0;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    auto kernel = plan.cb == 16 ? gemv_q8_0_kernel<16> : gemv_q8_0_kernel<8>;
+    auto kernel = regx ? gemv_q8_0_kernel<8, kRegxWarps, true>
+                       : plan.cb == 16 ? gemv_q8_0_kernel<16, kWarps, false> : gemv_q8_0_kernel<8, kWarps, false>;
+    const uint32_t threads = regx ? kRegxWarps * 32 : kThreads;
     B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    B200_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(kThreads), smem, stream, tm_w, p));
+    B200_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(threads), smem, stream, tm_w, p));
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return ATTN_OK;
 }

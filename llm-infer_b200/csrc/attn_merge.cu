@@ -26,9 +26,8 @@ namespace b200 {
 
 namespace {
 
-constexpr int kMergeWarps = 8;
-constexpr int kMergeThreads = kMergeWarps * 32;
-constexpr int kLoadsInFlight = 6;
+constexpr int kMergeWarps = merge_detail::kWarps;
+constexpr int kMergeThreads = merge_detail::kThreads;
 
 #ifdef ATTN_TRACE
 #define MTRACE(k) ATTN_TRACE_AT((p.trace && threadIdx.x == 0) ? p.trace + static_cast<size_t>(blockIdx.x) * 8 : nullptr, k)
@@ -37,64 +36,6 @@ constexpr int kLoadsInFlight = 6;
     do {          \
     } while (0)
 #endif
-
-// Where the partials of output row `row` are: n of them, partial i at po + i * o_stride (head_dim floats) with its
-// LSE at pl + i * l_stride. For the decode split pass these are the consecutive slots the pass wrote for the row's
-// segment; with ragged lengths the tile prefix is read, which that pass writes: the wait for it happens in here.
-__device__ __forceinline__ void locate_partials(const MergeParams& p, uint32_t row, const float*& po, const float*& pl,
-                                                uint64_t& o_stride, uint64_t& l_stride, uint32_t& n) {
-    if (p.split_grid) {
-        const uint32_t b = row / p.n_heads;
-        const uint32_t h = row - b * p.n_heads;
-        const uint32_t kvh = h / p.group;
-        const uint32_t g = h - kvh * p.group;
-        const uint32_t hg = kvh / p.hpc;
-        const uint32_t hh = kvh - hg * p.hpc;
-        const uint32_t nseg = p.batch * p.head_groups;
-        const uint32_t seg = b * p.head_groups + hg;
-        uint64_t nt, tile0, tile_end;
-        if (p.kv_len) {
-            grid_dep_wait();  // the tile prefix is written by the split pass
-            nt = p.seg_prefix[nseg];
-            tile0 = p.seg_prefix[seg];
-            tile_end = p.seg_prefix[seg + 1];
-        } else {
-            const uint64_t tu = (clamped_len(p.kv_len_uniform, p.kv_capacity) + p.tile_rows - 1) / p.tile_rows;
-            nt = tu * nseg;
-            tile0 = tu * seg;
-            tile_end = tile0 + tu;
-        }
-        if (tile_end == tile0) {
-            n = 0;
-            po = nullptr;
-            pl = nullptr;
-            o_stride = l_stride = 0;
-        } else {
-            const uint32_t a = active_ctas(p.split_grid, p.max_ctas, p.min_tiles_per_cta, nt);
-            const uint32_t c_first = cta_of_tile(tile0, nt, a);
-            const uint32_t c_last = cta_of_tile(tile_end - 1, nt, a);
-            n = (c_last - c_first + 1) * p.ts;
-            const uint64_t first_slot = (static_cast<uint64_t>(c_first) + seg) * p.ts;
-            const uint64_t row0 = (first_slot * p.hpc + hh) * p.group + g;
-            l_stride = static_cast<uint64_t>(p.hpc) * p.group;
-            o_stride = l_stride * p.head_dim;
-            po = p.part_o + row0 * p.head_dim;
-            pl = p.part_lse + row0;
-#ifdef ATTN_BOUNDS_CHECK
-            if (row0 + static_cast<uint64_t>(n - 1) * l_stride >= p.part_rows) {  // would read past the partials
-                if (p.status) atomicOr(p.status, ATTN_STATUS_BAD_INDEX);
-                n = 0;
-            }
-#endif
-        }
-    } else {
-        n = p.n_parts;
-        o_stride = p.o_part_stride;
-        l_stride = p.lse_part_stride;
-        po = p.part_o + static_cast<uint64_t>(row) * p.head_dim;
-        pl = p.part_lse + row;
-    }
-}
 
 // Many output rows with few partials each (batched decode: a row's segment is shared by a handful of split-pass
 // CTAs): two WARPS per row (even and odd partials), lanes over head_dim, the loads of up to six partials per warp in
@@ -209,15 +150,9 @@ __global__ void __launch_bounds__(kMergeThreads, 4) merge_rows_kernel(const __gr
 template <int SLICE, bool XCHG>
 __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_constant__ MergeParams p) {
     constexpr int LP = SLICE / 4;             // lanes that share one partial (a float4 each)
-    constexpr int P = kMergeThreads / LP;     // partials in flight per round of one load each
-    __shared__ float s_m[kMergeWarps];
-    __shared__ float s_z[kMergeWarps];
-    __shared__ __align__(16) float s_acc[kMergeWarps][SLICE];
+    __shared__ MergeScratch<SLICE> s_scratch;
     __shared__ float s_out[SLICE + 1];
     const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
-    const int pg = tid / LP;  // which partials: pg, pg + P, ...
     const int dl = tid % LP;  // which four floats of the slice
     const uint32_t nslices = p.head_dim / SLICE;
     const uint32_t row = blockIdx.x / nslices;
@@ -226,7 +161,6 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
     // Let the next kernel of the stream be scheduled (a weight GEMV starts prefetching), then wait for the grid that
     // produced the partials (no-op without a programmatic dependency).
     grid_dep_launch_dependents();
-
     const float* po;
     const float* pl;
     uint64_t o_stride, l_stride;
@@ -235,85 +169,21 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
     if (po) po += slice * SLICE + dl * 4;
     grid_dep_wait();
     MTRACE(1);
-
-    // ---- one sweep over this thread's partials (L2-only loads: the producer grid may still have been running when
-    //      this CTA started) ----
-    float m_t = -INFINITY, z_t = 0.f;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (uint32_t i0 = pg; i0 < n; i0 += P * kLoadsInFlight) {
-        float lw[kLoadsInFlight];
-        float4 x[kLoadsInFlight];
-#pragma unroll
-        for (int b = 0; b < kLoadsInFlight; ++b) {
-            const uint32_t i = i0 + b * P;
-            const bool valid = i < n;
-            lw[b] = -INFINITY;
-            x[b] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (valid) {  // no load for the padding of the last round
-                lw[b] = __ldcg(pl + i * l_stride);
-                x[b] = __ldcg(reinterpret_cast<const float4*>(po + i * o_stride));
-            }
-        }
-        float bm = lw[0];
-#pragma unroll
-        for (int b = 1; b < kLoadsInFlight; ++b) bm = fmaxf(bm, lw[b]);
-        if (bm > m_t) {
-            const float s = __expf(m_t - bm);  // 0 when nothing was folded yet (m_t = -inf)
-            z_t *= s;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[e] *= s;
-            m_t = bm;
-        }
-        if (m_t != -INFINITY) {
-#pragma unroll
-            for (int b = 0; b < kLoadsInFlight; ++b) {
-                const float w = __expf(lw[b] - m_t);  // 0 for empty partials and for the padding of the last round
-                z_t += w;
-                acc[0] = fmaf(w, x[b].x, acc[0]);
-                acc[1] = fmaf(w, x[b].y, acc[1]);
-                acc[2] = fmaf(w, x[b].z, acc[2]);
-                acc[3] = fmaf(w, x[b].w, acc[3]);
-            }
-        }
+    // The exchange's step number (step 0 in the arguments = count steps on the device, which keeps the launch
+    // arguments constant, e.g. for graph replay) is fetched here, together with the partials, not when it is needed.
+    // Not earlier: this grid may be resident while the previous exchange launch, which advances the counter with its
+    // last cell, is still running; the wait above orders the two (this pass waits for its split pass, which waited
+    // for that launch).
+    uint32_t step_early = 0;
+    if (XCHG && tid == 0 && p.xchg_world) {
+        const unsigned long long* ctl0 =
+            p.xchg_peers[p.xchg_rank] + 2ull * p.xchg_world * exchange_rank_words(p.rows, p.head_dim, SLICE);
+        step_early = p.xchg_step ? p.xchg_step : static_cast<uint32_t>(*reinterpret_cast<const volatile unsigned long long*>(ctl0)) + 1u;
     }
+
+    float x_out, lse_local;
+    merge_cell<SLICE>(po, pl, o_stride, l_stride, n, tid, s_scratch, [] { __syncthreads(); }, x_out, lse_local);
     MTRACE(2);
-
-    // ---- warp: common maximum, then sums over the partial groups of the warp ----
-    float m_w = m_t;
-#pragma unroll
-    for (int off = 16; off; off >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xffffffffu, m_w, off));
-    const float sc = m_t == -INFINITY ? 0.f : __expf(m_t - m_w);
-    float z_w = dl == 0 ? z_t * sc : 0.f;  // z_t is replicated over the LP lanes of a partial group
-#pragma unroll
-    for (int e = 0; e < 4; ++e) acc[e] *= sc;
-#pragma unroll
-    for (int off = 16; off; off >>= 1) z_w += __shfl_xor_sync(0xffffffffu, z_w, off);
-#pragma unroll
-    for (int off = LP; off < 32; off <<= 1) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
-    }
-    if (lane < LP) *reinterpret_cast<float4*>(&s_acc[warp][lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    if (lane == 0) {
-        s_m[warp] = m_w;
-        s_z[warp] = z_w;
-    }
-    __syncthreads();
-
-    // ---- CTA: the eight warp states merged by every thread that owns an output element ----
-    float mx = s_m[0];
-#pragma unroll
-    for (int w = 1; w < kMergeWarps; ++w) mx = fmaxf(mx, s_m[w]);
-    float z = 0.f, x_out = 0.f;
-#pragma unroll
-    for (int w = 0; w < kMergeWarps; ++w) {
-        const float e = s_m[w] == -INFINITY ? 0.f : __expf(s_m[w] - mx);
-        z = fmaf(s_z[w], e, z);
-        if (tid < SLICE) x_out = fmaf(s_acc[w][tid], e, x_out);
-    }
-    const float inv_z = z > 0.f ? 1.f / z : 0.f;
-    x_out *= inv_z;
-    const float lse_local = z > 0.f ? mx + logf(z) : -INFINITY;
     const size_t out_idx = static_cast<size_t>(row) * p.head_dim + slice * SLICE + tid;
     if (!XCHG || p.xchg_world == 0) {
         if (tid < SLICE) store_out(p.o, p.o_dtype, out_idx, x_out);
@@ -341,8 +211,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(const __grid_const
     unsigned long long* ctl = p.xchg_peers[me] + 2ull * world * rank_words;
     if (tid == 0) {
         s_fail = 0;
-        // step 0 in the arguments = count steps on the device (keeps the launch arguments constant, e.g. for graph replay)
-        s_step = p.xchg_step ? p.xchg_step : static_cast<uint32_t>(*reinterpret_cast<volatile unsigned long long*>(ctl)) + 1u;
+        s_step = step_early;
     }
     if (tid < SLICE) s_out[tid] = x_out;
     if (tid == 0) s_out[SLICE] = lse_local;

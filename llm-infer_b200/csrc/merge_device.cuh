@@ -84,4 +84,168 @@ __device__ __forceinline__ void warp_merge_row(const float* po, const float* pl,
     if (lse_out && lane == 0) lse_out[row] = z > 0.f ? mx + logf(z) : -INFINITY;
 }
 
+
+// Where the partials of output row `row` are: n of them, partial i at po + i * o_stride (head_dim floats) with its
+// LSE at pl + i * l_stride. For the decode split pass these are the consecutive slots the pass wrote for the row's
+// segment; with ragged lengths the tile prefix is read, which that pass writes: the wait for it happens in here.
+__device__ __forceinline__ void locate_partials(const MergeParams& p, uint32_t row, const float*& po, const float*& pl,
+                                                uint64_t& o_stride, uint64_t& l_stride, uint32_t& n) {
+    if (p.split_grid) {
+        const uint32_t b = row / p.n_heads;
+        const uint32_t h = row - b * p.n_heads;
+        const uint32_t kvh = h / p.group;
+        const uint32_t g = h - kvh * p.group;
+        const uint32_t hg = kvh / p.hpc;
+        const uint32_t hh = kvh - hg * p.hpc;
+        const uint32_t nseg = p.batch * p.head_groups;
+        const uint32_t seg = b * p.head_groups + hg;
+        uint64_t nt, tile0, tile_end;
+        if (p.kv_len) {
+            grid_dep_wait();  // the tile prefix is written by the split pass
+            nt = p.seg_prefix[nseg];
+            tile0 = p.seg_prefix[seg];
+            tile_end = p.seg_prefix[seg + 1];
+        } else {
+            const uint64_t tu = (clamped_len(p.kv_len_uniform, p.kv_capacity) + p.tile_rows - 1) / p.tile_rows;
+            nt = tu * nseg;
+            tile0 = tu * seg;
+            tile_end = tile0 + tu;
+        }
+        if (tile_end == tile0) {
+            n = 0;
+            po = nullptr;
+            pl = nullptr;
+            o_stride = l_stride = 0;
+        } else {
+            const uint32_t a = active_ctas(p.split_grid, p.max_ctas, p.min_tiles_per_cta, nt);
+            const uint32_t c_first = cta_of_tile(tile0, nt, a);
+            const uint32_t c_last = cta_of_tile(tile_end - 1, nt, a);
+            n = (c_last - c_first + 1) * p.ts;
+            const uint64_t first_slot = (static_cast<uint64_t>(c_first) + seg) * p.ts;
+            const uint64_t row0 = (first_slot * p.hpc + hh) * p.group + g;
+            l_stride = static_cast<uint64_t>(p.hpc) * p.group;
+            o_stride = l_stride * p.head_dim;
+            po = p.part_o + row0 * p.head_dim;
+            pl = p.part_lse + row0;
+#ifdef ATTN_BOUNDS_CHECK
+            if (row0 + static_cast<uint64_t>(n - 1) * l_stride >= p.part_rows) {  // would read past the partials
+                if (p.status) atomicOr(p.status, ATTN_STATUS_BAD_INDEX);
+                n = 0;
+            }
+#endif
+        }
+    } else {
+        n = p.n_parts;
+        o_stride = p.o_part_stride;
+        l_stride = p.lse_part_stride;
+        po = p.part_o + static_cast<uint64_t>(row) * p.head_dim;
+        pl = p.part_lse + row;
+    }
+}
+
+namespace merge_detail {
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kLoadsInFlight = 6;
+}  // namespace merge_detail
+
+// Shared-memory scratch of merge_cell().
+template <int SLICE>
+struct MergeScratch {
+    float m[merge_detail::kWarps];
+    float z[merge_detail::kWarps];
+    alignas(16) float acc[merge_detail::kWarps][SLICE];
+};
+
+// 256 threads merge the n partials of one cell = (output row, SLICE floats of head_dim). Thread tid owns four floats of
+// the slice (tid % (SLICE/4)) and every P-th partial (P = 256 / (SLICE/4)); it folds its partials into a running
+// (m, z, acc) state exactly as the reference folds tiles (src/attention.cu:41-65), with the loads of up to six
+// partials (LSE and O together, L2-only: the grid that wrote them may still have been running when this CTA started)
+// in flight before the first is used. Warps reduce with shuffles, the eight warps through `s` with one barrier
+// (`sync` is that barrier over exactly these 256 threads). po already points at this thread's four floats of partial
+// 0. On return x_out holds the merged, normalised value of element tid of the slice (threads tid < SLICE) and lse
+// the row's log-sum-exp (every thread); an all-empty row gives zeros and -inf.
+template <int SLICE, typename Sync>
+__device__ __forceinline__ void merge_cell(const float* po, const float* pl, uint64_t o_stride, uint64_t l_stride,
+                                           uint32_t n, int tid, MergeScratch<SLICE>& s, Sync sync, float& x_out,
+                                           float& lse) {
+    using namespace merge_detail;
+    constexpr int LP = SLICE / 4;
+    constexpr int P = kThreads / LP;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int pg = tid / LP, dl = tid % LP;
+    float m_t = -INFINITY, z_t = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (uint32_t i0 = pg; i0 < n; i0 += P * kLoadsInFlight) {
+        float lw[kLoadsInFlight];
+        float4 x[kLoadsInFlight];
+#pragma unroll
+        for (int b = 0; b < kLoadsInFlight; ++b) {
+            const uint32_t i = i0 + b * P;
+            lw[b] = -INFINITY;
+            x[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < n) {  // no load for the padding of the last round
+                lw[b] = __ldcg(pl + i * l_stride);
+                x[b] = __ldcg(reinterpret_cast<const float4*>(po + i * o_stride));
+            }
+        }
+        float bm = lw[0];
+#pragma unroll
+        for (int b = 1; b < kLoadsInFlight; ++b) bm = fmaxf(bm, lw[b]);
+        if (bm > m_t) {
+            const float sc = __expf(m_t - bm);  // 0 when nothing was folded yet (m_t = -inf)
+            z_t *= sc;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] *= sc;
+            m_t = bm;
+        }
+        if (m_t != -INFINITY) {
+#pragma unroll
+            for (int b = 0; b < kLoadsInFlight; ++b) {
+                const float w = __expf(lw[b] - m_t);  // 0 for empty partials and for the padding of the last round
+                z_t += w;
+                acc[0] = fmaf(w, x[b].x, acc[0]);
+                acc[1] = fmaf(w, x[b].y, acc[1]);
+                acc[2] = fmaf(w, x[b].z, acc[2]);
+                acc[3] = fmaf(w, x[b].w, acc[3]);
+            }
+        }
+    }
+    // warp: common maximum, then sums over the partial groups of the warp
+    float m_w = m_t;
+#pragma unroll
+    for (int off = 16; off; off >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xffffffffu, m_w, off));
+    const float sc = m_t == -INFINITY ? 0.f : __expf(m_t - m_w);
+    float z_w = dl == 0 ? z_t * sc : 0.f;  // z_t is replicated over the LP lanes of a partial group
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] *= sc;
+#pragma unroll
+    for (int off = 16; off; off >>= 1) z_w += __shfl_xor_sync(0xffffffffu, z_w, off);
+#pragma unroll
+    for (int off = LP; off < 32; off <<= 1) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+    }
+    if (lane < LP) *reinterpret_cast<float4*>(&s.acc[warp][lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    if (lane == 0) {
+        s.m[warp] = m_w;
+        s.z[warp] = z_w;
+    }
+    sync();
+    // CTA: the eight warp states merged by every thread that owns an output element
+    float mx = s.m[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, s.m[w]);
+    float z = 0.f;
+    x_out = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const float e = s.m[w] == -INFINITY ? 0.f : __expf(s.m[w] - mx);
+        z = fmaf(s.z[w], e, z);
+        if (tid < SLICE) x_out = fmaf(s.acc[w][tid], e, x_out);
+    }
+    x_out *= z > 0.f ? 1.f / z : 0.f;
+    lse = z > 0.f ? mx + logf(z) : -INFINITY;
+}
+
 }  // namespace b200

@@ -131,6 +131,34 @@ def test_q8_0_against_cpu_matmul(attention, port, pkg, n, d, batch, clip):
         assert (np.abs(got[b] - want) <= 4e-6 * mag[b] + 1e-7).all(), (n, d, b, np.abs(got[b] - want).max())
 
 
+@pytest.mark.parametrize("batch", [1, 8])
+def test_q8_0_pinned_on_the_engine_matmul_with_fp16_exact_blocks(attention, checker, batch):
+    """The engine has no Q8_0 code, so the GPU kernel is pinned on its F16 matmul() (include/kernels_cpu.hpp:69-80)
+    directly: blocks whose scale is a power of two dequantise to numbers that are exact in fp16 (|q| <= 127 needs 7
+    bits), so the SAME weights can be handed to the engine as an fp16 matrix and to the GPU as Q8_0 blocks, and the
+    two products must agree at the F16 tolerance - no restated CPU code in between."""
+    import torch
+    rng = np.random.default_rng(55 + batch)
+    d, n = 512, 1024
+    q = rng.integers(-127, 128, size=(d, n // 32, 32), dtype=np.int64).astype(np.int8)
+    exp = rng.integers(-9, -4, size=(d, n // 32, 1))
+    scale = (2.0 ** exp).astype(np.float16)
+    blocks = np.empty((d, n // 32, 34), dtype=np.uint8)
+    blocks[..., :2] = scale.view(np.uint8).reshape(d, n // 32, 2)
+    blocks[..., 2:] = q.view(np.uint8)
+    blocks = blocks.reshape(d, -1)
+    w16 = (scale.astype(np.float32) * q.astype(np.float32)).reshape(d, n).astype(np.float16)
+    assert np.array_equal(w16.astype(np.float32), (scale.astype(np.float32) * q).reshape(d, n))  # exact in fp16
+    x = rng.standard_normal((batch, n), dtype=np.float32)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = attention.gemv_q8_0(torch.from_numpy(x).cuda(), torch.from_numpy(blocks).cuda(), status=status).cpu().numpy()
+    assert status.item() == 0
+    mag = np.abs(x) @ np.abs(w16.astype(np.float32)).T
+    for b in range(batch):
+        want = checker.matmul_clip(x[b], w16, 0.0)
+        assert (np.abs(got[b] - want) <= 4e-6 * mag[b] + 1e-7).all(), np.abs(got[b] - want).max()
+
+
 def test_q8_0_roundtrip_and_reference_f16_path(port, checker, pkg):
     """The writer against the dequantiser (|w - dq| <= d/2 per block, plus the fp16 rounding of d itself) and the Q8_0 sum against the engine's F16 matmul
     fed the values rounded once to fp16 (2^-11 per weight: 1e-3 of the magnitude)."""
