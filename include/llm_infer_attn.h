@@ -222,6 +222,25 @@ int attn_gemv_f16(const AttnGemvArgs* args, void* stream);
  * computes it (src/model/config.cpp:11-17,26-34), so there is no reference kernel this one replaces. */
 int attn_gemv_q8_0(const AttnGemvArgs* args, void* stream);
 
+/* The same product from a tiled copy of the Q8_0 weights, made once when the model is loaded: same bytes (34 per 32
+ * weights), same arithmetic in the same order (results are bit-identical to attn_gemv_q8_0), but every group of
+ * 16 rows x 8 blocks is one contiguous 4352-byte tile whose values already sit in the order the kernel's lanes feed
+ * the tensor cores, so a pipeline stage is one plain bulk copy and a lane reads its sixteen values of a block with
+ * one 16-byte shared-memory load. Layout of tile (row group rg, chunk c) at ((rg * n/256) + c) * 4352: 8 blocks of 544
+ * bytes; in a block, lane L = 4 g + t (g < 8, t < 4) owns the 16 bytes at 16 L = four little-endian words
+ * {row g, k-step 0}, {row g+8, k-step 0}, {row g, k-step 1}, {row g+8, k-step 1}, a word holding the row's elements
+ * 32 blk + 16 s + 4 t + (0, 2, 1, 3) as bytes q + 128; then at 512 + 4 g the fp16 scales of rows g and g + 8. Rows
+ * past d in the last group are zeros. With swiglu, d must be a multiple of 16 (the up rows start a row group).
+ * `args->w` points at the tiled copy; everything else as attn_gemv_q8_0. */
+int attn_gemv_q8_0_tiled(const AttnGemvArgs* args, void* stream);
+
+/* Bytes of the tiled copy of a [d][n] Q8_0 matrix: ceil(d / 16) * (n / 32) * 544. */
+size_t attn_q8_0_tiled_bytes(uint32_t d, uint32_t n);
+
+/* dst (16-byte aligned, attn_q8_0_tiled_bytes(d, n) bytes) = the tiled copy of the GGML Q8_0 blocks at src
+ * ([d][n/32] blocks, n a multiple of 256). One launch, to be run once per matrix at load time. */
+int attn_repack_q8_0_tiled(void* dst, const void* src, uint32_t d, uint32_t n, void* stream);
+
 /* The per-token steps between the GEMVs and attention, for a batch of sequences per launch. They restate on the device
  * the CPU steps of the engine's forward pass, which its CUDA backend does not have yet (the CUDA block ends after
  * attention, src/model/block.cu:235-239; the CUDA model has no final norm or classifier, src/model/model.cu:67-87). */

@@ -293,10 +293,11 @@ class HostDecodeStep:
         return self.out_host
 
 
-def _gemv(entry: str, x, w, n: int, out, out2, out3, out_dtype, clip, accumulate, swiglu, k_split, status, stream):
+def _gemv(entry: str, x, w, n: int, out, out2, out3, out_dtype, clip, accumulate, swiglu, k_split, status, stream,
+          rows=None):
     """Common part of gemv_f16 / gemv_q8_0: output shapes, the argument structure, the call."""
     B = x.shape[0]
-    rows = w.shape[0]
+    rows = w.shape[0] if rows is None else rows
     if swiglu and (rows % 2 or out2 is not None or out3 is not None):
         raise ValueError("swiglu needs an even number of rows (gate rows, then up rows) and a single output")
     if out3 is not None and out2 is None:
@@ -359,17 +360,50 @@ def gemv_f16(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=None
 
 def gemv_q8_0(x: torch.Tensor, w: torch.Tensor, *, out=None, out2=None, out3=None, out_dtype=torch.float32,
               clip: float = 0.0, accumulate: bool = False, swiglu: bool = False, k_split: int = 1, status=None,
-              stream=None) -> torch.Tensor:
+              stream=None, rows=None) -> torch.Tensor:
     """The same over Q8_0 weights: w uint8 [rows, n/32*34] (GGML blocks: fp16 scale + 32 signed bytes). Same
     conventions and fused forms as gemv_f16. x and out may also be int32 tensors, which stand for prepared activations
     (one word per element: fp16 value and fp16 residual, written by rmsnorm(out=int32), attn_decode(out=int32) or
-    this function itself): the kernel then copies x into shared memory as it is instead of converting it in every CTA."""
+    this function itself): the kernel then copies x into shared memory as it is instead of converting it in every CTA.
+    w may also be the tiled copy made by repack_q8_0 (uint8 [ceil(rows/16), n/32, 544]): same result, bit for bit,
+    from a layout the kernel streams and unpacks faster; ``rows`` then gives the row count when it is not a multiple
+    of 16."""
     _require_cuda(x, w)
     B, n = x.shape
-    if w.dim() != 2 or w.dtype != torch.uint8 or w.shape[1] != n // 32 * 34 or n % 32 or \
-            x.dtype not in (torch.float32, torch.int32):
-        raise ValueError("x must be fp32 (or int32 = prepared activations) [B, n] and w uint8 [rows, n/32*34]")
+    if x.dtype not in (torch.float32, torch.int32) or w.dtype != torch.uint8 or n % 32:
+        raise ValueError("x must be fp32 (or int32 = prepared activations) [B, n] and w uint8")
+    if w.dim() == 3:
+        if w.shape[1] != n // 32 or w.shape[2] != Q8_TILE_BLOCK_BYTES:
+            raise ValueError("a tiled Q8_0 matrix is uint8 [ceil(rows/16), n/32, 544]")
+        rows = w.shape[0] * 16 if rows is None else rows
+        if not 0 < rows <= w.shape[0] * 16:
+            raise ValueError("rows does not fit the tiled matrix")
+        return _gemv("attn_gemv_q8_0_tiled", x, w, n, out, out2, out3, out_dtype, clip, accumulate, swiglu, k_split,
+                     status, stream, rows=rows)
+    if w.dim() != 2 or w.shape[1] != n // 32 * 34:
+        raise ValueError("w must be uint8 [rows, n/32*34]")
     return _gemv("attn_gemv_q8_0", x, w, n, out, out2, out3, out_dtype, clip, accumulate, swiglu, k_split, status, stream)
+
+
+Q8_TILE_BLOCK_BYTES = 16 * 34  # one 32-element block of 16 rows in the tiled layout
+
+
+def repack_q8_0(w: torch.Tensor, *, stream=None) -> torch.Tensor:
+    """GGML Q8_0 blocks uint8 [rows, n/32*34] -> the tiled copy uint8 [ceil(rows/16), n/32, 544] that gemv_q8_0 also
+    accepts (attn_repack_q8_0_tiled; one launch, meant to run once per matrix when a model is loaded)."""
+    _require_cuda(w)
+    if w.dim() != 2 or w.dtype != torch.uint8 or w.shape[1] % 34:
+        raise ValueError("w must be uint8 [rows, n/32*34]")
+    w = _dense(w, stream, "w")
+    rows, n = w.shape[0], w.shape[1] // 34 * 32
+    out = torch.empty(((rows + 15) // 16, n // 32, Q8_TILE_BLOCK_BYTES), dtype=torch.uint8, device=w.device)
+    lib = _b.load()
+    if lib.attn_q8_0_tiled_bytes(rows, n) != out.numel():
+        raise RuntimeError("tiled size mismatch")
+    with torch.cuda.device(w.device):
+        _b.check(lib.attn_repack_q8_0_tiled(out.data_ptr(), w.data_ptr(), rows, n, _stream_ptr(stream)),
+                 "attn_repack_q8_0_tiled")
+    return out
 
 
 def embed_f16(table: torch.Tensor, tokens: torch.Tensor, *, out=None, status=None, stream=None) -> torch.Tensor:

@@ -40,6 +40,9 @@ EXPORTED_SYMBOLS = (
     "attn_gather_rows",
     "attn_gemv_f16",
     "attn_gemv_q8_0",
+    "attn_gemv_q8_0_tiled",
+    "attn_q8_0_tiled_bytes",
+    "attn_repack_q8_0_tiled",
     "attn_embed_f16",
     "attn_embed_q8_0",
     "attn_rmsnorm",
@@ -287,6 +290,12 @@ def load() -> C.CDLL:
     lib.attn_gemv_f16.argtypes = [C.POINTER(AttnGemvArgs), C.c_void_p]
     lib.attn_gemv_q8_0.restype = C.c_int
     lib.attn_gemv_q8_0.argtypes = [C.POINTER(AttnGemvArgs), C.c_void_p]
+    lib.attn_gemv_q8_0_tiled.restype = C.c_int
+    lib.attn_gemv_q8_0_tiled.argtypes = [C.POINTER(AttnGemvArgs), C.c_void_p]
+    lib.attn_q8_0_tiled_bytes.restype = C.c_size_t
+    lib.attn_q8_0_tiled_bytes.argtypes = [C.c_uint32, C.c_uint32]
+    lib.attn_repack_q8_0_tiled.restype = C.c_int
+    lib.attn_repack_q8_0_tiled.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
     lib.attn_embed_f16.restype = C.c_int
     lib.attn_embed_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                    C.c_void_p]

@@ -1,7 +1,7 @@
 // The engine's own kernel symbol, include/kernels.cuh:26, defined for sm_100a:
 // fp32 q/o, fp16 K/V, one sequence, all model dimensions taken from device
 // constant memory (set by attention_configure). One launch = split-KV pass +
-// merge by the last-arriving CTA, so it fits a single CUDA-graph kernel node
+// merge by the last-arriving CTAs (in two levels), so it fits a single CUDA-graph kernel node
 // whose grid is frozen (include/model/device.hpp:219-237): the grid is always
 // one CTA per SM and CTAs without rows exit at once.
 #include "../../include/kernels_b200.cuh"
@@ -24,6 +24,9 @@ struct AttentionSymbolConfig {
     float* part_o;
     float* part_lse;
     uint32_t* counters;
+    uint32_t* group_counters;
+    float* group_o;
+    float* group_lse;
     uint32_t* status;     // one word of the workspace: ATTN_STATUS_* bits
     uint32_t smem_bytes;  // dynamic shared memory the node must be launched with
 };
@@ -39,7 +42,7 @@ struct HostCfg {
 HostCfg g_host_cfg[64];
 
 template <int D, int HPC>
-__device__ __forceinline__ void run(const DecodeParams& p, unsigned char* smem) {
+__device__ __noinline__ void run(const DecodeParams& p, unsigned char* smem) {
     decode_detail::decode_split_body<D, HPC, /*QSPLIT=*/true, /*BF16=*/false, /*FUSED=*/true>(p, smem);
 }
 
@@ -95,6 +98,9 @@ attention(float* o, const float* q, const half* k, const half* v, uint32_t kv_to
     p.lse = nullptr;
     p.o_dtype = ATTN_DTYPE_F32;
     p.counters = c.counters;
+    p.group_counters = c.group_counters;
+    p.group_o = c.group_o;
+    p.group_lse = c.group_lse;
     if (c.head_dim == 128) {
         switch (c.hpc) {
             case 8: run<128, 8>(p, smem); break;
@@ -115,9 +121,8 @@ attention(float* o, const float* q, const half* k, const half* v, uint32_t kv_to
 using namespace b200;
 
 namespace {
-// Rows per CTA below which a further CTA is not worth its merge cost in the single-launch kernel,
-// where the last CTA alone merges every partial.
-constexpr uint32_t kSymbolMinRowsPerCta = 128;
+// Rows per CTA below which a further CTA is not worth its share of the merge in the single-launch kernel.
+constexpr uint32_t kSymbolMinRowsPerCta = 64;
 
 int plan_for(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, DecodePlan* plan) {
     DeviceInfo dev{};
@@ -132,7 +137,7 @@ extern "C" {
 size_t attention_workspace_bytes(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim) {
     DecodePlan plan{};
     if (plan_for(n_heads, n_kv_heads, head_dim, &plan) != ATTN_OK) return 0;
-    return plan.workspace_bytes;
+    return plan.symbol_workspace_bytes;
 }
 
 int attention_configure(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, float scale, void* workspace,
@@ -165,9 +170,13 @@ int attention_configure(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim
     c.part_lse = ws + plan.part_o_floats;
     c.counters = reinterpret_cast<uint32_t*>(ws + plan.part_o_floats + plan.part_lse_floats) + plan.prefix_words;
     c.status = c.counters + ((static_cast<size_t>(plan.nseg) + 3) & ~3ull);
+    c.group_o = ws + plan.group_base_words;
+    c.group_lse = c.group_o + plan.group_o_floats;
+    c.group_counters = reinterpret_cast<uint32_t*>(c.group_lse + plan.group_lse_floats);
     c.smem_bytes = static_cast<uint32_t>(plan.smem_bytes);
-    // counters (rounded up to four words) and the status word behind them start at zero
+    // counters (rounded up to four words), the status word behind them and the group counters start at zero
     B200_CUDA_TRY(cudaMemsetAsync(c.counters, 0, (((static_cast<size_t>(plan.nseg) + 3) & ~3ull) + 4) * 4, stream));
+    B200_CUDA_TRY(cudaMemsetAsync(c.group_counters, 0, plan.group_counter_words * 4, stream));
     B200_CUDA_TRY(cudaMemcpyToSymbolAsync(g_cfg, &c, sizeof(c), 0, cudaMemcpyHostToDevice, stream));
     B200_CUDA_TRY(cudaStreamSynchronize(stream));  // c lives on this stack frame
     B200_CUDA_TRY(cudaFuncSetAttribute(attention, cudaFuncAttributeMaxDynamicSharedMemorySize,

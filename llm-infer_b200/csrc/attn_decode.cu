@@ -98,6 +98,13 @@ int make_decode_plan(uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint
     pl.prefix_words = (static_cast<size_t>(pl.nseg) + 1 + 3) & ~3ull;
     pl.workspace_bytes =
         (pl.part_o_floats + pl.part_lse_floats + pl.prefix_words + ((static_cast<size_t>(pl.nseg) + 3) & ~3ull) + 4) * 4;
+    // the engine's single-launch kernel symbol also keeps first-level group records behind that
+    pl.group_base_words = pl.workspace_bytes / 4;
+    const size_t group_rows = slots * pl.hpc * pl.group;
+    pl.group_o_floats = group_rows * head_dim;
+    pl.group_lse_floats = (group_rows + 3) & ~static_cast<size_t>(3);
+    pl.group_counter_words = (slots + 3) & ~static_cast<size_t>(3);
+    pl.symbol_workspace_bytes = (pl.group_base_words + pl.group_o_floats + pl.group_lse_floats + pl.group_counter_words) * 4;
     *plan = pl;
     return ATTN_OK;
 }

@@ -83,12 +83,35 @@ __device__ __forceinline__ void load_a(uint32_t (&r)[4], uint32_t seg_addr, uint
     r[3] = bytes_to_half2<2>(v1);
 }
 
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// Tiled layout (attn_repack_q8_0_tiled): one word = the four values of one row that a lane feeds to one k-step, stored
+// as bytes q + 128 in the order (e0, e2, e1, e3). The even bytes are then the half2 (e0, e1) after one AND/OR
+// (0x6400 | u = 1024 + u) and the odd bytes the half2 (e2, e3) after one byte-permute; 1024 + u - 1152 = q exactly.
+__device__ __forceinline__ void word_to_fragments(uint32_t w, uint32_t& first, uint32_t& second) {
+    const uint32_t even = (w & 0x00ff00ffu) | 0x64006400u;
+    const uint32_t odd = __byte_perm(w, 0x64646464u, 0x4341);
+    const __half2 bias = __half2half2(__ushort_as_half(0x6480));
+    const __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&even), bias);
+    const __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&odd), bias);
+    first = *reinterpret_cast<const uint32_t*>(&a);
+    second = *reinterpret_cast<const uint32_t*>(&b);
+}
+
 // NW warps per CTA. REGX: the inner dimension is exactly NW chunks, so a warp always multiplies by the same CB blocks
 // of the activations and keeps them in registers as MMA B fragments (64 registers for CB = 8) for the whole launch:
 // no shared memory for the activations (which at batch 8 x 4096 would take 128 KB and leave room for 8 warps only), no
 // shared-memory loads for them in the inner loop, and twice the warps per SM to hide the latency of the
 // byte -> fp16 operand construction.
-template <uint32_t CB, int NW, bool REGX>
+// TILED: the weights are in the tiled layout (one contiguous 4352-byte tile per 16 rows x 8 blocks, values already in
+// MMA fragment order, see attn_repack_q8_0_tiled): a stage is filled by one plain bulk copy, and a lane gets its
+// sixteen values of a block with one 16-byte shared-memory load and the two scales with one 4-byte load, in place of
+// four to eight 4-byte loads, two alignment permutes, two XORs and two 2-byte loads.
+template <uint32_t CB, int NW, bool REGX, bool TILED>
 __global__ void __launch_bounds__(NW * 32, 1) gemv_q8_0_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                  const __grid_constant__ Params p) {
     constexpr uint32_t kWarps = NW, kThreads = NW * 32;
@@ -139,6 +162,12 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_q8_0_kernel(const __grid_cons
         const uint32_t bar = bar0 + 8 * stage;
         if (lane == 0) {
             mbar_arrive_expect_tx(bar, kStageBytes);
+            if constexpr (TILED) {
+                const uint8_t* src =
+                    p.w_tiles + (static_cast<size_t>(part * groups + rg) * p.row_chunks + chunk) * kStageBytes;
+                bulk_g2s(ring0 + stage * kStageBytes, src, kStageBytes, bar, policy);
+                return;
+            }
             // x in 32-bit elements (a multiple of 4: 16-byte rule), y = first row of the group (rows past the
             // tensor read as zeros)
             tma_load_rows(ring0 + stage * kStageBytes, &tm_w, bar, static_cast<int>(chunk * (kSegBytes / 4)),
@@ -221,7 +250,19 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_q8_0_kernel(const __grid_cons
 #pragma unroll
                     for (uint32_t bi = 0; bi < kChunkBlocks; ++bi) {
                         uint32_t alo[4], ahi[4];
-                        if (bi & 1) {
+                        float s_lo, s_hi;
+                        if constexpr (TILED) {
+                            const uint32_t blk = ring0 + stage * kStageBytes + bi * (kRows * kBlockBytes);
+                            const uint4 w = lds128(blk + lane * 16);
+                            word_to_fragments(w.x, alo[0], alo[1]);  // row g, k-step 0
+                            word_to_fragments(w.y, ahi[0], ahi[1]);  // row g + 8, k-step 0
+                            word_to_fragments(w.z, alo[2], alo[3]);  // row g, k-step 1
+                            word_to_fragments(w.w, ahi[2], ahi[3]);  // row g + 8, k-step 1
+                            const uint32_t sc = lds32(blk + kRows * 32 + g * 4);
+                            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sc));
+                            s_lo = sf.x;
+                            s_hi = sf.y;
+                        } else if (bi & 1) {
                             load_a<false>(alo, seg_lo, bi, t);
                             load_a<false>(ahi, seg_hi, bi, t);
                         } else {
@@ -241,7 +282,10 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_q8_0_kernel(const __grid_cons
                         mma_f16(acc, alo[2], ahi[2], alo[3], ahi[3], x1.z, x1.w);        // k-step 1, residual
                         mma_f16(acc, alo[0], ahi[0], alo[1], ahi[1], x0.x, x0.y);        // k-step 0, value
                         mma_f16(acc, alo[2], ahi[2], alo[3], ahi[3], x1.x, x1.y);        // k-step 1, value
-                        const float s_lo = lds_scale(seg_lo + kBlockBytes * bi), s_hi = lds_scale(seg_hi + kBlockBytes * bi);
+                        if constexpr (!TILED) {
+                            s_lo = lds_scale(seg_lo + kBlockBytes * bi);
+                            s_hi = lds_scale(seg_hi + kBlockBytes * bi);
+                        }
                         tot[0] = fmaf(s_lo, acc[0], tot[0]);
                         tot[1] = fmaf(s_lo, acc[1], tot[1]);
                         tot[2] = fmaf(s_hi, acc[2], tot[2]);
@@ -266,9 +310,42 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_q8_0_kernel(const __grid_cons
 }  // namespace
 }  // namespace b200
 
-using namespace b200;
+namespace b200 {
+namespace {
 
-extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
+
+// One 16-byte unit of the tiled layout per thread: tile (row group rg, chunk c of 8 blocks), block bi, lane (g, t) ->
+// the words {row g k-step 0, row g+8 k-step 0, row g k-step 1, row g+8 k-step 1}, each the row's elements
+// 32 blk + 16 s + 4 t + (0, 2, 1, 3) as bytes q + 128; lanes 0-7 also write the block's scale pair (rows g, g + 8).
+__global__ void repack_q8_0_tiled_kernel(uint8_t* dst, const uint8_t* src, uint32_t d, uint32_t n_blocks, uint64_t units) {
+    const uint64_t u = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (u >= units) return;
+    const uint32_t lane = static_cast<uint32_t>(u & 31), g = lane >> 2, t = lane & 3;
+    const uint64_t blk_id = u >> 5;                       // (rg * n_blocks + blk): tiles of a row group are consecutive
+    const uint32_t blk = static_cast<uint32_t>(blk_id % n_blocks);
+    const uint32_t rg = static_cast<uint32_t>(blk_id / n_blocks);
+    uint8_t* out_blk = dst + blk_id * (kRows * kBlockBytes);
+    uint32_t words[4];
+    uint16_t scales[2];
+#pragma unroll
+    for (uint32_t half = 0; half < 2; ++half) {
+        const uint32_t row = rg * kRows + g + 8 * half;
+        const uint8_t* b = src + (static_cast<uint64_t>(row) * n_blocks + blk) * kBlockBytes;
+        const bool live = row < d;
+        scales[half] = live ? static_cast<uint16_t>(b[0] | (b[1] << 8)) : 0;
+#pragma unroll
+        for (uint32_t s = 0; s < 2; ++s) {
+            const uint8_t* q = b + 2 + 16 * s + 4 * t;
+            const uint32_t e0 = live ? q[0] : 0u, e1 = live ? q[1] : 0u, e2 = live ? q[2] : 0u, e3 = live ? q[3] : 0u;
+            words[2 * s + half] = (e0 | (e2 << 8) | (e1 << 16) | (e3 << 24)) ^ 0x80808080u;
+        }
+    }
+    *reinterpret_cast<uint4*>(out_blk + lane * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+    // the scale pair of rows (g, g + 8) is the same for the four lanes of a row: the t == 0 lane writes it
+    if (t == 0) *reinterpret_cast<uint32_t*>(out_blk + kRows * 32 + g * 4) = scales[0] | (static_cast<uint32_t>(scales[1]) << 16);
+}
+
+int gemv_q8_0_launch(const AttnGemvArgs* a, void* stream_v, bool tiled) {
     if (!a || !a->out || !a->x || !a->w || a->n == 0 || a->d == 0 || a->batch == 0) return ATTN_ERR_INVALID_ARG;
     if (a->out_dtype != ATTN_DTYPE_F32 && a->out_dtype != ATTN_DTYPE_F16 && a->out_dtype != ATTN_DTYPE_SPLIT16)
         return ATTN_ERR_INVALID_ARG;
@@ -321,11 +398,12 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     Plan plan{};
     Plan wide{};
     if (!make_plan(8, &plan)) return ATTN_ERR_UNSUPPORTED;  // (the slices must be equal and one must fit next to the ring)
-    if (k_split == 1 && make_plan(16, &wide) && wide.slices == 1) plan = wide;
+    if (!tiled && k_split == 1 && make_plan(16, &wide) && wide.slices == 1) plan = wide;
     // Inner dimension of exactly 16 chunks of 8 blocks (n = 4096, the model width of the 8B shape): 16 warps, each
     // with its chunk of the activations in registers, two stages per warp, nothing else staged.
     constexpr uint32_t kRegxWarps = 16;
-    const bool regx = k_split == 1 && n_blocks == kRegxWarps * 8;
+    // (a single sequence of fp32 activations is faster on the 8-warp form: measured 16.1 vs 18.5 us at 14336 x 4096)
+    const bool regx = k_split == 1 && n_blocks == kRegxWarps * 8 && (a->batch >= 2 || a->x_format == ATTN_DTYPE_SPLIT16);
     if (regx) {
         plan = Plan{8, 1, 2,
                     2 * 2 * kRegxWarps * 128 * sizeof(float) + (kRegxWarps * kMaxStages + 2) * sizeof(uint64_t) + 128 +
@@ -337,8 +415,8 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     // W as a 2-D tensor of 32-bit elements [rows][row_bytes / 4]; one box = 16 rows x 272 bytes, no swizzle.
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return ATTN_ERR_CUDA;
-    CUtensorMap tm_w;
-    {
+    CUtensorMap tm_w{};
+    if (!tiled) {
         const cuuint64_t row_bytes = static_cast<cuuint64_t>(n_blocks) * kBlockBytes;
         const cuuint64_t dims[2] = {row_bytes / 4, static_cast<cuuint64_t>(a->d) * (a->swiglu ? 2 : 1)};
         const cuuint64_t strides[1] = {row_bytes};
@@ -360,11 +438,42 @@ extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) {
     p.x_col_pitch = slice_blocks * 32 + 16;
     p.acc_groups = (slices > 1 && k_split == 1) ? groups_per_cta : 0;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    auto kernel = regx ? gemv_q8_0_kernel<8, kRegxWarps, true>
-                       : plan.cb == 16 ? gemv_q8_0_kernel<16, kWarps, false> : gemv_q8_0_kernel<8, kWarps, false>;
+    p.w_tiles = static_cast<const uint8_t*>(a->w);
+    p.row_chunks = n_blocks / 8;
+    auto kernel = tiled ? (regx ? gemv_q8_0_kernel<8, kRegxWarps, true, true> : gemv_q8_0_kernel<8, kWarps, false, true>)
+                  : regx ? gemv_q8_0_kernel<8, kRegxWarps, true, false>
+                  : plan.cb == 16 ? gemv_q8_0_kernel<16, kWarps, false, false> : gemv_q8_0_kernel<8, kWarps, false, false>;
     const uint32_t threads = regx ? kRegxWarps * 32 : kThreads;
     B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     B200_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(threads), smem, stream, tm_w, p));
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return ATTN_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int attn_gemv_q8_0(const AttnGemvArgs* a, void* stream_v) { return gemv_q8_0_launch(a, stream_v, false); }
+
+extern "C" int attn_gemv_q8_0_tiled(const AttnGemvArgs* a, void* stream_v) { return gemv_q8_0_launch(a, stream_v, true); }
+
+extern "C" size_t attn_q8_0_tiled_bytes(uint32_t d, uint32_t n) {
+    return static_cast<size_t>((d + kRows - 1) / kRows) * (n / 32) * (kRows * kBlockBytes);
+}
+
+extern "C" int attn_repack_q8_0_tiled(void* dst, const void* src, uint32_t d, uint32_t n, void* stream_v) {
+    if (!dst || !src || d == 0 || n == 0) return ATTN_ERR_INVALID_ARG;
+    if (n % 256 != 0) return ATTN_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(dst) & 15u) return ATTN_ERR_ALIGNMENT;
+    const uint32_t n_blocks = n / 32;
+    const uint64_t units = static_cast<uint64_t>((d + kRows - 1) / kRows) * n_blocks * 32;
+    const uint64_t grid = (units + 255) / 256;
+    if (grid > 0x7fffffffull) return ATTN_ERR_UNSUPPORTED;
+    repack_q8_0_tiled_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream_v)>>>(
+        static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), d, n_blocks, units);
+    B200_CUDA_TRY(cudaGetLastError());
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return ATTN_OK;
 }

@@ -57,6 +57,11 @@ struct DecodeParams {
     float* lse;
     int32_t o_dtype;
     uint32_t* counters;  // [nseg], zero before the first launch; the kernel leaves them zero
+    // two-level merge of the single-launch mode (segments shared by many CTAs): first-level groups of CTAs merge
+    // their partials into group records, the last group to finish merges the records. nullptr = one level only.
+    uint32_t* group_counters;  // [grid + nseg], zero before the first launch; the kernel leaves them zero
+    float* group_o;            // [(grid + nseg) * hpc * group][head_dim]
+    float* group_lse;          // [(grid + nseg) * hpc * group]
 #ifdef ATTN_TRACE
     unsigned long long* trace;  // [grid][8] time stamps, or null
 #endif
@@ -215,7 +220,13 @@ struct DecodePlan {
     size_t part_o_floats;
     size_t part_lse_floats;
     size_t prefix_words;
-    size_t workspace_bytes;
+    // behind the status words: first-level records of the single-launch mode's two-level merge
+    size_t group_base_words;     // offset of group_o from the start of the workspace, in 32-bit words
+    size_t group_o_floats;
+    size_t group_lse_floats;
+    size_t group_counter_words;
+    size_t workspace_bytes;         // what attn_decode needs
+    size_t symbol_workspace_bytes;  // what the kernel symbol needs (workspace_bytes + the group records)
 };
 int make_decode_plan(uint32_t batch, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, const DeviceInfo& dev,
                      DecodePlan* plan);

@@ -198,8 +198,13 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     // launched and that the only cache row it writes is each sequence's last valid one: the wait then moves behind the
     // tile prefix, and the producer warp starts the tiles that cannot hold that row before it waits (below), so the
     // first K/V bytes are already on their way while the previous kernel finishes.
+    // With uniform lengths (no length array to wait for) the wait moves in the same way, and the producer warp spends
+    // it asking L2 for its first tiles (a hint, not a load: it may run ahead of the kernel that writes the newest row).
+    // In a chain of decode steps the next step's first tiles then cross HBM while this step's slowest CTAs and its
+    // merge pass are still at work.
     const bool early = p.kv_early != 0;
-    if (!early) grid_dep_wait();
+    const bool deferred = early || p.kv_len == nullptr;
+    if (!deferred) grid_dep_wait();
     if (tid == 0) DTRACE(1);
 
     // ---- tile prefix over segments (ragged lengths only) --------------------
@@ -318,6 +323,20 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
             }
             grid_dep_wait();
             if (i > 0 && !issue_q()) return;  // the running segment's query rows, which that kernel produced
+        } else if (deferred) {
+            SegInfo ps = seg;
+            for (uint32_t k = 0; k < n_my && k < nst; ++k) {
+                const uint32_t gt = t_begin + k;
+                while (gt >= ps.tile_end) ps = table.load(ps.seg + 1);
+                const uint32_t tok0 = (gt - ps.tile0) * TT;
+                const size_t seq_off = static_cast<size_t>(ps.b) * p.kv_batch_stride + static_cast<size_t>(ps.hg) * (HPC * D);
+                for (uint32_t j = lane; j < TT && tok0 + j < ps.len; j += 32) {
+                    const size_t off = seq_off + static_cast<size_t>(tok0 + j) * p.kv_row_stride;
+                    bulk_prefetch_l2(p.k + off, ROWB);
+                    bulk_prefetch_l2(p.v + off, ROWB);
+                }
+            }
+            grid_dep_wait();
         }
         for (; i < n_my; ++i) {
             const uint32_t gt = t_begin + i;
@@ -340,7 +359,7 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     }
 
     // ===================== consumer warps =====================
-    if (early) grid_dep_wait();      // before the first partial is written and the query rows are used
+    if (deferred) grid_dep_wait();   // before the first partial is written and the query rows are used
     const int hh = warp / TS;        // kv head within the head group
     const int ts = warp - hh * TS;   // row sub-tile
     const int gq = lane >> 2;        // MMA row owned by this lane (and gq + 8)
@@ -432,46 +451,98 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         }
     };
 
-    // Fused (single-launch) mode: the CTA that delivers the last partial of a segment merges it.
-    // No CTA ever waits for another: each one adds 1 to the segment's counter after its partials are
-    // visible, and whoever sees the final count does the merge and puts the counter back to zero.
+    // Single-launch mode: the CTAs that deliver the last partials merge. No CTA ever waits for another: each one adds
+    // 1 to a counter after its partials are visible, and whoever sees the final count does the merging and puts the
+    // counter back to zero. A segment shared by few CTAs has one counter and one merge. A segment shared by many (one
+    // long sequence: a single CTA would take tens of microseconds to read every partial) is merged in two levels:
+    // consecutive CTAs form groups of gs ~ sqrt(CTAs / TS), the last CTA of a group to arrive merges the group's
+    // gs * TS partials into one group record, then counts itself on the segment's counter, and the last group merges
+    // the records - two short rounds of loads on different SMs in place of one long one.
     // A consumer warp whose bounded wait ran out does not leave: it marks the CTA as aborted, stops computing and keeps
     // walking the tile list so that it still meets the other warps at the named barriers below. An aborted CTA
-    // raises the status bit BEFORE it takes its ticket, and the CTA that takes a segment's last ticket reads the
-    // status word AFTER: the merge is skipped (output untouched, counters back to zero) whenever a partial is missing.
+    // raises the status bit BEFORE it takes its ticket, and a CTA that takes a last ticket reads the status word
+    // AFTER: every merge is skipped (output untouched, counters back to zero) whenever a partial is missing.
     auto fused_merge = [&]() {
         if constexpr (FUSED) {
+            constexpr uint32_t kOneLevelMax = 32;  // partials that one merge reads in two rounds of loads
             __threadfence();
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (tid == 0) {
-                if (*s_abort) {
-                    if (p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
-                    __threadfence();
-                }
-                *s_ticket = atomicAdd(p.counters + seg.seg, 1u);
-            }
             asm volatile("bar.sync 1, 256;" ::: "memory");
             const uint32_t c_first = cta_of_tile(seg.tile0, nt, active);
             const uint32_t c_last = cta_of_tile(seg.tile_end - 1, nt, active);
-            if (*s_ticket == c_last - c_first) {
-                __threadfence();
-                const bool poisoned =
-                    *s_abort || (p.status && (*reinterpret_cast<volatile uint32_t*>(p.status) & ATTN_STATUS_WAIT_TIMEOUT));
-                if (poisoned) {
-                    if (tid == 0) p.counters[seg.seg] = 0u;
-                    return;
-                }
-                const uint64_t first_slot = (static_cast<uint64_t>(c_first) + seg.seg) * TS;
-                const uint64_t l_stride = static_cast<uint64_t>(HPC) * G;
-                const uint32_t n = (c_last - c_first + 1) * TS;
-                for (uint32_t r = warp; r < HPC * G; r += kConsumerWarps) {
-                    const uint64_t row0 = first_slot * l_stride + r;  // r = hh * G + g
-                    const size_t out_row = static_cast<size_t>(seg.b) * p.n_heads + static_cast<size_t>(seg.hg) * HPC * G + r;
-                    warp_merge_row<D / 32, 1>(p.part_o + row0 * D, p.part_lse + row0, l_stride * D, l_stride, n, p.o,
-                                              p.o_dtype, p.lse, out_row, lane);
-                }
-                if (tid == 0) p.counters[seg.seg] = 0u;
+            const uint32_t nc = c_last - c_first + 1;  // CTAs that share the segment
+            const uint32_t R = HPC * G;                // output rows of the segment = rows of one partial record
+            const bool two_level = p.group_counters != nullptr && nc * TS > kOneLevelMax;
+            uint32_t gs = nc, gi = 0, ng = 1;
+            if (two_level) {
+                gs = static_cast<uint32_t>(sqrtf(static_cast<float>(nc) / TS) + 0.5f);
+                gs = gs < 2 ? 2 : gs;
+                gi = (cta - c_first) / gs;
+                ng = (nc + gs - 1) / gs;
             }
+            const uint32_t gsz = nc - gi * gs < gs ? nc - gi * gs : gs;  // CTAs in this CTA's group
+            // groups are disjoint CTA ranges and a CTA is shared by at most two consecutive segments, so (first CTA of
+            // the group + segment) numbers the groups of the whole launch without collisions, below grid + nseg
+            const size_t group_slot = static_cast<size_t>(c_first) + gi * gs + seg.seg;
+            uint32_t* counter = two_level ? p.group_counters + group_slot : p.counters + seg.seg;
+            auto take_ticket = [&](uint32_t* c) {
+                if (tid == 0) {
+                    if (*s_abort) {
+                        if (p.status) atomicOr(p.status, ATTN_STATUS_WAIT_TIMEOUT);
+                        __threadfence();
+                    }
+                    *s_ticket = atomicAdd(c, 1u);
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                return *s_ticket;
+            };
+            auto poisoned = [&]() {
+                __threadfence();
+                return *s_abort ||
+                       (p.status && (*reinterpret_cast<volatile uint32_t*>(p.status) & ATTN_STATUS_WAIT_TIMEOUT));
+            };
+            const size_t out_row0 = static_cast<size_t>(seg.b) * p.n_heads + static_cast<size_t>(seg.hg) * R;
+            auto store_final = [&](uint32_t r, uint32_t f, float4 v, float lse) {
+                const size_t idx = (out_row0 + r) * D + f * 4;
+                if (p.o_dtype == ATTN_DTYPE_F32) {
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.o) + idx) = v;
+                } else {
+                    store_out(p.o, p.o_dtype, idx, v.x);
+                    store_out(p.o, p.o_dtype, idx + 1, v.y);
+                    store_out(p.o, p.o_dtype, idx + 2, v.z);
+                    store_out(p.o, p.o_dtype, idx + 3, v.w);
+                }
+                if (p.lse && f == 0) p.lse[out_row0 + r] = lse;
+            };
+            if (take_ticket(counter) != gsz - 1) return;
+            // this CTA delivered the last partial of its group (one level: of the segment)
+            const size_t first_slot = (static_cast<size_t>(c_first) + gi * gs + seg.seg) * TS;
+            const float* src_o = p.part_o + first_slot * R * D;
+            const float* src_l = p.part_lse + first_slot * R;
+            if (!two_level) {
+                if (!poisoned()) cta_merge_rows<D>(src_o, src_l, static_cast<uint64_t>(R) * D, R, nc * TS, R, tid, store_final);
+                if (tid == 0) *counter = 0u;
+                return;
+            }
+            if (!poisoned()) {
+                float* rec_o = p.group_o + group_slot * R * D;
+                float* rec_l = p.group_lse + group_slot * R;
+                cta_merge_rows<D>(src_o, src_l, static_cast<uint64_t>(R) * D, R, gsz * TS, R, tid,
+                                  [&](uint32_t r, uint32_t f, float4 v, float lse) {
+                                      *reinterpret_cast<float4*>(rec_o + static_cast<size_t>(r) * D + f * 4) = v;
+                                      if (f == 0) rec_l[r] = lse;
+                                  });
+            }
+            if (tid == 0) *counter = 0u;
+            __threadfence();
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // every thread's record stores before the ticket
+            if (take_ticket(p.counters + seg.seg) != ng - 1) return;
+            // this group's record was the segment's last: records of group k at slot (c_first + seg) + k * gs
+            if (!poisoned()) {
+                const size_t rec0 = static_cast<size_t>(c_first) + seg.seg;
+                cta_merge_rows<D>(p.group_o + rec0 * R * D, p.group_lse + rec0 * R, static_cast<uint64_t>(gs) * R * D,
+                                  static_cast<uint64_t>(gs) * R, ng, R, tid, store_final);
+            }
+            if (tid == 0) p.counters[seg.seg] = 0u;
         }
     };
 

@@ -41,6 +41,8 @@ struct Params {
     int32_t out_dtype;
     int32_t accumulate;
     int32_t x_split;          // x holds prepared activations (ATTN_DTYPE_SPLIT16 words) instead of fp32
+    const uint8_t* w_tiles;   // Q8_0 weights in the tiled layout (attn_repack_q8_0_tiled), else unused
+    uint32_t row_chunks;      // tiles per row group in that layout (n / 256)
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,

@@ -1,5 +1,4 @@
-// Device routine shared by the stand-alone merge kernel and the fused
-// (single-launch) decode kernel: one warp merges n partials of one output row.
+// Device routines shared by the stand-alone merge kernels and the single-launch decode kernel.
 #pragma once
 
 #include "attn_internal.cuh"
@@ -140,6 +139,64 @@ __device__ __forceinline__ void locate_partials(const MergeParams& p, uint32_t r
         l_stride = p.lse_part_stride;
         po = p.part_o + static_cast<uint64_t>(row) * p.head_dim;
         pl = p.part_lse + row;
+    }
+}
+
+// 256 threads merge n partial records of `rows` consecutive output rows each: partial i of row r at
+// po + i * o_stride + r * D (D floats) with its LSE at pl + i * l_stride + r. A thread owns four floats of one row over
+// all partials and folds them into a running (m, z, acc) state as the reference folds tiles
+// (src/attention.cu:41-65), sixteen partials' loads (LSE and values, L2-only) in flight at a time; no thread needs
+// another's result. store(r, f, value, lse) receives the normalised float4 number f of row r and the row's
+// log-sum-exp (zeros and -inf for an all-empty row). Not inlined: it runs once or twice per segment, and as a call it
+// does not add to the register pressure of the streaming loop it is called from.
+template <int D, typename Store>
+__device__ __noinline__ void cta_merge_rows(const float* po, const float* pl, uint64_t o_stride, uint64_t l_stride,
+                                               uint32_t n, uint32_t rows, int tid, Store store) {
+    constexpr int F4 = D / 4;
+    constexpr int kInFlight = 16;
+    for (uint32_t it = tid; it < rows * F4; it += 256) {
+        const uint32_t r = it / F4, f = it - r * F4;
+        const float* o0 = po + static_cast<size_t>(r) * D + f * 4;
+        const float* l0 = pl + r;
+        float m = -INFINITY, z = 0.f;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (uint32_t i0 = 0; i0 < n; i0 += kInFlight) {
+            float lw[kInFlight];
+            float4 x[kInFlight];
+#pragma unroll
+            for (int b = 0; b < kInFlight; ++b) {
+                const uint32_t i = i0 + b;
+                lw[b] = -INFINITY;
+                x[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < n) {
+                    lw[b] = __ldcg(l0 + i * l_stride);
+                    x[b] = __ldcg(reinterpret_cast<const float4*>(o0 + i * o_stride));
+                }
+            }
+            float bm = lw[0];
+#pragma unroll
+            for (int b = 1; b < kInFlight; ++b) bm = fmaxf(bm, lw[b]);
+            if (bm > m) {
+                const float sc = __expf(m - bm);  // 0 when nothing was folded yet
+                z *= sc;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[e] *= sc;
+                m = bm;
+            }
+            if (m != -INFINITY) {
+#pragma unroll
+                for (int b = 0; b < kInFlight; ++b) {
+                    const float w = __expf(lw[b] - m);  // 0 for empty partials and for the padding of the last round
+                    z += w;
+                    acc[0] = fmaf(w, x[b].x, acc[0]);
+                    acc[1] = fmaf(w, x[b].y, acc[1]);
+                    acc[2] = fmaf(w, x[b].z, acc[2]);
+                    acc[3] = fmaf(w, x[b].w, acc[3]);
+                }
+            }
+        }
+        const float inv = z > 0.f ? 1.f / z : 0.f;
+        store(r, f, make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv), z > 0.f ? m + logf(z) : -INFINITY);
     }
 }
 

@@ -114,6 +114,16 @@ class Llama:
         # followed by up (w3) rows with the SwiGLU product as its epilogue. Only the stacks are kept.
         self.w["wqkv"] = torch.cat([self.w.pop("wq"), self.w.pop("wk"), self.w.pop("wv")], dim=1).contiguous()
         self.w["w13"] = torch.cat([self.w.pop("w1"), self.w.pop("w3")], dim=1).contiguous()
+        # Weights as the decode step's GEMVs read them. Q8_0: a tiled copy of every matrix, made once here (same bytes,
+        # same products bit for bit, streamed and unpacked faster: attn_repack_q8_0_tiled); the GGML blocks stay for the
+        # embedding rows and for the whole-prompt path, which expands them to fp16.
+        self.wg, self._rows = self.w, {}
+        if q8 and c.hidden_dim % 16 == 0:
+            self.wg = dict(self.w)
+            self._rows = {name: self.w[name].shape[-2] for name in ("wqkv", "wo", "w13", "w2", "wcls")}
+            for name in ("wqkv", "wo", "w13", "w2"):
+                self.wg[name] = torch.stack([A.repack_q8_0(self.w[name][l]) for l in range(c.n_layers)])
+            self.wg["wcls"] = A.repack_q8_0(self.w["wcls"])
         B, f32 = batch, torch.float32
         q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
         z = lambda *s, dtype=f32: torch.zeros(*s, dtype=dtype, device=dev)  # noqa: E731
@@ -177,33 +187,38 @@ class Llama:
     def _launch_step(self, kv_sink: int, want_logits: bool) -> None:
         """Every launch of one step, reading self.tokens / pos / kv_pos / kv_len. With logits the step ends with the
         greedy pick (self.next_token) and feeds it back into self.tokens for the next step."""
-        c, w, B = self.cfg, self.w, self.batch
-        gemv = self._gemv
+        c, w, B = self.cfg, self.wg, self.batch
+
+        def gemv(x, name, l=None, **kw):
+            if name in self._rows:  # a tiled copy: its last row group may be padded
+                kw["rows"] = self._rows[name]
+            return self._gemv(x, w[name] if l is None else w[name][l], **kw)
+
         self._embed(w["embed"], self.tokens, out=self.x, status=self.status)
         att_flat = self.att.view(B, self._q_dim)
         pending = None  # partial products of the previous layer's down projection, still to be added into x
         for l in range(c.n_layers):
             A.rmsnorm(self.x, w["rms_att"][l], c.norm_eps, out=self.xb, partials=pending)
             pending = None
-            gemv(self.xb, w["wqkv"][l], out=self.q.view(B, self._q_dim), out2=self.k.view(B, self._kv_dim),
+            gemv(self.xb, "wqkv", l, out=self.q.view(B, self._q_dim), out2=self.k.view(B, self._kv_dim),
                  out3=self.v.view(B, self._kv_dim), clip=c.qkv_clip)
             A.rope_kv_insert(self.q, self.k, self.v, self.k_cache[l], self.v_cache[l], self.pos, self.kv_pos,
                              theta=c.rope_theta, rotary_dim=c.rotary_dim, kv_sink=kv_sink, q_out=self.q,
                              pos_early=True)   # positions are copied in before the step's first kernel
             A.attn_decode(self.q, self.k_cache[l], self.v_cache[l], self.kv_len, out=self.att,
                           workspace=self.workspace)
-            gemv(att_flat, w["wo"][l], out=self.x, accumulate=True)       # x += Wo att
+            gemv(att_flat, "wo", l, out=self.x, accumulate=True)           # x += Wo att
             A.rmsnorm(self.x, w["rms_ffn"][l], c.norm_eps, out=self.xb)
-            gemv(self.xb, w["w13"][l], out=self.hb, swiglu=True)          # hb = silu(W1 xb) * (W3 xb)
+            gemv(self.xb, "w13", l, out=self.hb, swiglu=True)              # hb = silu(W1 xb) * (W3 xb)
             if self._k_split > 1:
-                gemv(self.hb, w["w2"][l], out=self.partials, k_split=self._k_split)
+                gemv(self.hb, "w2", l, out=self.partials, k_split=self._k_split)
                 pending = self.partials                                    # x += W2 hb, added by the next norm
             else:
-                gemv(self.hb, w["w2"][l], out=self.x, accumulate=True)    # x += W2 (silu(W1 xb) * W3 xb)
+                gemv(self.hb, "w2", l, out=self.x, accumulate=True)        # x += W2 (silu(W1 xb) * W3 xb)
         if not want_logits:
             return  # prefill mode: no final norm, no classifier (src/model/model.cpp:74-76); x is not read again
         A.rmsnorm(self.x, w["rms_final"], c.norm_eps, out=self.xb, partials=pending)
-        gemv(self.xb, w["wcls"], out=self.logits)
+        gemv(self.xb, "wcls", out=self.logits)
         A.argmax(self.logits, out=self.next_token)
         self.tokens.copy_(self.next_token)
 
@@ -287,7 +302,7 @@ class Llama:
         # the last token of every prompt: final norm, classifier, greedy pick (the decode step's own kernels)
         A.gather_rows(x, last_rows, out=self.x)
         A.rmsnorm(self.x, w["rms_final"], c.norm_eps, out=self.xb)
-        self._gemv(self.xb, w["wcls"], out=self.logits)
+        self._gemv(self.xb, self.wg["wcls"], out=self.logits, **({"rows": self._rows["wcls"]} if self._rows else {}))
         A.argmax(self.logits, out=self.next_token)
         self.tokens.copy_(self.next_token)
 

@@ -37,6 +37,29 @@ def dequantize_q8_0(blocks: np.ndarray) -> np.ndarray:
     return (d * q).reshape(*blocks.shape[:-1], -1)
 
 
+def repack_q8_0_tiled(blocks: np.ndarray) -> np.ndarray:
+    """uint8 [rows, n/32*34] -> the tiled layout of attn_repack_q8_0_tiled, uint8 [ceil(rows/16), n/32, 544]: per
+    group of 16 rows and per block, lane L = 4 g + t owns 16 bytes = the words {row g, k-step 0}, {row g+8, k-step 0},
+    {row g, k-step 1}, {row g+8, k-step 1}, a word = the row's elements 16 s + 4 t + (0, 2, 1, 3) of the block as
+    bytes q + 128; the fp16 scales of rows (g, g+8) follow at 512 + 4 g. Rows past the end are zeros (bytes 0x80)."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8)
+    rows, nb = b.shape[0], b.shape[1] // BLOCK_BYTES
+    groups = (rows + 15) // 16
+    padded = np.zeros((groups * 16, nb, BLOCK_BYTES), dtype=np.uint8)
+    padded[:, :, 2:] = 0  # q = 0
+    padded[:rows] = b.reshape(rows, nb, BLOCK_BYTES)
+    q = padded[:, :, 2:] ^ np.uint8(0x80)               # [R, nb, 32] biased bytes
+    q[rows:] = 0x80
+    q = q.reshape(groups, 2, 8, nb, 2, 4, 4)            # [rg, half, g, blk, s, t, e]
+    q = q[..., [0, 2, 1, 3]]                            # byte order inside a word
+    q = q.transpose(0, 3, 2, 5, 4, 1, 6)                # [rg, blk, g, t, s, half, e]
+    out = np.empty((groups, nb, 16 * BLOCK_BYTES), dtype=np.uint8)
+    out[:, :, :512] = q.reshape(groups, nb, 512)
+    sc = padded[:, :, :2].reshape(groups, 2, 8, nb, 2)  # [rg, half, g, blk, byte]
+    out[:, :, 512:] = sc.transpose(0, 3, 2, 1, 4).reshape(groups, nb, 32)
+    return out
+
+
 def quantize_q8_0_torch(w):
     """The same writer on torch tensors of any device: [..., n] float -> uint8 [..., n/32*34]."""
     import torch

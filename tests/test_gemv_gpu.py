@@ -191,6 +191,64 @@ def test_q8_0_streams_weights_near_hbm_rate(attention, pkg):
     assert gbs > 3000
 
 
+def test_tiled_q8_0_copy_and_bit_identical_products(attention, pkg):
+    """attn_repack_q8_0_tiled writes exactly the layout quant.repack_q8_0_tiled states, and the GEMV over the tiled copy
+    returns what the GEMV over the GGML blocks returns - the same per-block arithmetic; the same bits wherever both run
+    with the same split of the inner dimension over the warps, else equal up to the order of the fp32 sum over the
+    warps: plain (batch 1 and 8, a row count that is not a multiple of 16), clamp, stacked Q/K/V segments, SwiGLU
+    rows, split-k partials, prepared activations in and out."""
+    import torch
+    from llm_infer_b200 import quant
+    rng = np.random.default_rng(123)
+
+    def make(d, n):
+        blocks = quant.quantize_q8_0(rng.standard_normal((d, n), dtype=np.float32) * 0.05)
+        dev = torch.from_numpy(blocks).cuda()
+        tiled = attention.repack_q8_0(dev)
+        assert (tiled.cpu().numpy() == quant.repack_q8_0_tiled(blocks)).all()
+        return dev, tiled
+
+    def same(a, b, exact=False):
+        torch.cuda.synchronize()
+        if a.dtype == torch.int32:  # prepared activations: compare the numbers they stand for (value + residual)
+            a, b = (t.view(torch.float16).float().view(*t.shape[:-1], -1, 2, 2, 2).sum(dim=-3) for t in (a, b))
+        if exact:
+            assert torch.equal(a, b)
+        scale = float(b.float().abs().max())
+        assert float((a.float() - b.float()).abs().max()) <= 1e-5 * scale
+
+    for d, n, B in ((4096, 4096, 1), (4096, 4096, 8), (777, 2048, 3), (1024, 14336, 1), (48, 256, 2)):
+        w, wt = make(d, n)
+        x = torch.randn(B, n, device="cuda")
+        same(attention.gemv_q8_0(x, w), attention.gemv_q8_0(x, wt, rows=d), exact=(n == 4096 and B == 8))
+        clip = 0.5 * float(attention.gemv_q8_0(x, w).abs().max())
+        same(attention.gemv_q8_0(x, w, clip=clip), attention.gemv_q8_0(x, wt, clip=clip, rows=d))
+    # stacked projections, one fp16 output
+    n, B = 4096, 8
+    w, wt = make(4096 + 1024 + 1024, n)
+    x = torch.randn(B, n, device="cuda")
+    outs = []
+    for m in (w, wt):
+        q, k = torch.empty(B, 4096, device="cuda"), torch.empty(B, 1024, device="cuda")
+        v = torch.empty(B, 1024, device="cuda")
+        attention.gemv_q8_0(x, m, out=q, out2=k, out3=v)
+        outs.append((q, k, v))
+    for a, b in zip(*outs):
+        same(a, b)
+    # SwiGLU rows, prepared activations in and out
+    hidden = 1040
+    w, wt = make(2 * hidden, n)
+    xs = attention.rmsnorm(x, torch.ones(n, device="cuda"), 1e-5, out=torch.empty(B, n, dtype=torch.int32, device="cuda"))
+    same(attention.gemv_q8_0(xs, w, swiglu=True, out_dtype=torch.int32),
+         attention.gemv_q8_0(xs, wt, swiglu=True, out_dtype=torch.int32))
+    # split-k partials of a batch whose activations do not fit at once
+    n2 = 14336
+    w, wt = make(1024, n2)
+    x2 = torch.randn(B, n2, device="cuda")
+    same(attention.gemv_q8_0(x2, w, k_split=4), attention.gemv_q8_0(x2, wt, k_split=4))
+    same(attention.gemv_q8_0(x2, w), attention.gemv_q8_0(x2, wt))
+
+
 def _weights(kind, w32, port, checker):
     """(device tensor, gemv wrapper name, per-sequence CPU product, fp32 view of the stored weights)."""
     import torch

@@ -111,3 +111,32 @@ def test_engine_parser_rejects_a_file_without_required_keys(M, tmp_path):
     s = RefGgufSummary()
     rc = C.CDLL(REF_GGUF_SO).ref_gguf_open(path.encode(), C.byref(s))
     assert rc == -1 and b"quantization_version" in s.error
+
+
+def test_tiled_q8_0_layout_element_by_element(pkg):
+    """The tiled Q8_0 layout (what attn_repack_q8_0_tiled writes) stated one byte at a time, against the vectorised
+    writer; 21 rows, so the second row group has padding rows."""
+    from llm_infer_b200 import quant
+    rng = np.random.default_rng(5)
+    rows, n = 21, 512
+    blocks = quant.quantize_q8_0(rng.standard_normal((rows, n), dtype=np.float32))
+    tiled = quant.repack_q8_0_tiled(blocks)
+    nb = n // 32
+    assert tiled.shape == ((rows + 15) // 16, nb, 544)
+    src = blocks.reshape(rows, nb, 34)
+    for rg in range(tiled.shape[0]):
+        for blk in range(nb):
+            t544 = tiled[rg, blk]
+            for lane in range(32):
+                g, t = lane >> 2, lane & 3
+                for word in range(4):
+                    s, half = word >> 1, word & 1
+                    row = rg * 16 + g + 8 * half
+                    for byte, e in enumerate((0, 2, 1, 3)):
+                        want = (src[row, blk, 2 + 16 * s + 4 * t + e] ^ 0x80) if row < rows else 0x80
+                        assert t544[16 * lane + 4 * word + byte] == want
+            for g in range(8):
+                for half in range(2):
+                    row = rg * 16 + g + 8 * half
+                    want = src[row, blk, :2] if row < rows else np.zeros(2, np.uint8)
+                    assert (t544[512 + 4 * g + 2 * half: 512 + 4 * g + 2 * half + 2] == want).all()
