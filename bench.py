@@ -303,9 +303,10 @@ def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, pro
     return res
 
 
-def gemv_measure(torch, steps: int, warmup: int, hbm_peak: float, peak_kind: str):
+def gemv_measure(torch, steps: int, warmup: int, hbm_peak: float, peak_kind: str, kinds=None):
     """The weight GEMVs of one Llama-3-8B-shaped layer alone (eager launches, rotated weight copies > L2, CUDA events):
-    fp16 and Q8_0, batch 1 and 8. Used for profiler captures and the GEMV roofline figures."""
+    fp16 and Q8_0, batch 1 and 8. Used for profiler captures and the GEMV roofline figures. ``kinds`` restricts the
+    run to some of "q8_0", "q8_0_tiled", "f16" (profiler captures of one kernel)."""
     import numpy as np
     from llm_infer_b200 import attention as A, quant
     rng = np.random.default_rng(0)
@@ -314,10 +315,17 @@ def gemv_measure(torch, steps: int, warmup: int, hbm_peak: float, peak_kind: str
     base = rng.standard_normal((2048, n), dtype=np.float32)
     wq8 = torch.from_numpy(quant.quantize_q8_0(base)).cuda().repeat(d // 2048, 1).contiguous()
     wf16 = torch.from_numpy(base.astype(np.float16)).cuda().repeat(d // 2048, 1).contiguous()
-    for kind, w, fn in (("q8_0", wq8, A.gemv_q8_0), ("f16", wf16, A.gemv_f16)):
+    for kind, w, fn in (("q8_0", wq8, A.gemv_q8_0), ("q8_0_tiled", wq8, A.gemv_q8_0), ("f16", wf16, A.gemv_f16)):
+        if kinds and kind not in kinds:
+            continue
         copies = [w.clone() for _ in range(int(400e6 // (w.numel() * w.element_size())) + 2)]
+        if kind == "q8_0_tiled":  # the tiled copy of the same blocks, and activations in the prepared form
+            copies = [A.repack_q8_0(c) for c in copies]
         for batch in (1, 8):
             x = torch.randn(batch, n, device="cuda")
+            if kind == "q8_0_tiled":
+                x = A.rmsnorm(x, torch.ones(n, device="cuda"), 1e-5,
+                              out=torch.empty(batch, n, dtype=torch.int32, device="cuda"))
             out = torch.empty(batch, d, device="cuda")
             for i in range(max(3, warmup)):
                 fn(x, copies[i % len(copies)], out=out)
@@ -332,9 +340,30 @@ def gemv_measure(torch, steps: int, warmup: int, hbm_peak: float, peak_kind: str
             alg = w.numel() * w.element_size() + batch * (n * 4 + d * 4)
             res[f"{kind}_b{batch}"] = {"us": round(us, 2), "gbs": round(alg / us / 1e3, 1),
                                        "frac": round(alg / us / 1e3 / hbm_peak, 3), "algorithmic_bytes": alg}
+            if kind == "q8_0_tiled":
+                # the same calls replayed from one CUDA graph: the host's launch cost is out of the figure and
+                # consecutive launches overlap through programmatic dependent launch, as they do in a model step
+                g = torch.cuda.CUDAGraph()
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side), torch.cuda.graph(g):
+                    for c in copies:
+                        fn(x, c, out=out)
+                torch.cuda.current_stream().wait_stream(side)
+                g.replay()
+                torch.cuda.synchronize()
+                t0.record()
+                for _ in range(10):
+                    g.replay()
+                t1.record()
+                torch.cuda.synchronize()
+                us = t0.elapsed_time(t1) * 1e3 / (10 * len(copies))
+                res[f"{kind}_b{batch}"]["graph_replay"] = {"us": round(us, 2), "gbs": round(alg / us / 1e3, 1),
+                                                           "frac": round(alg / us / 1e3 / hbm_peak, 3)}
         del copies
     res["note"] = (f"{d}x{n} matrix, eager back-to-back launches (host launch cost included when the kernel is "
-                   f"shorter), frac of {peak_kind} HBM peak {hbm_peak:.1f} GB/s")
+                   f"shorter), frac of {peak_kind} HBM peak {hbm_peak:.1f} GB/s; q8_0_tiled = the tiled copy of the "
+                   "blocks with prepared activations (what a model step runs), also replayed from one CUDA graph")
     return res
 
 
@@ -516,7 +545,7 @@ def attention_symbol_measure(torch, hbm_peak: float):
         rt.cudaGraphDestroy(graph)
         del ks, vs
     res["note"] = ("one graph launch per token with the node's arguments refreshed first, back to back; single-launch "
-                   "mode (the CTA that delivers a segment's last partial merges it)")
+                   "mode (the CTAs that deliver the last partials merge them, in two levels for long sequences)")
     return res
 
 
@@ -998,6 +1027,8 @@ def main():
                     help="time only the causal-prefill workload (used for profiler captures)")
     ap.add_argument("--gemv-only", action="store_true",
                     help="time only the weight GEMVs of one layer (fp16 and Q8_0; used for profiler captures)")
+    ap.add_argument("--gemv-kinds", default="",
+                    help="with --gemv-only: comma-separated subset of q8_0,q8_0_tiled,f16")
     ap.add_argument("--generate-only", action="store_true",
                     help="run only the end-to-end greedy generation workload (Q8_0 8B-shaped model) and print it")
     ap.add_argument("--generate-eager", action="store_true",
@@ -1033,7 +1064,9 @@ def main():
         import torch
         load_package()
         hbm_peak, _, peak_kind = measured_peaks()
-        print(json.dumps({"gemv_layer": gemv_measure(torch, args.steps, args.warmup, hbm_peak, peak_kind)}), flush=True)
+        print(json.dumps({"gemv_layer": gemv_measure(torch, args.steps, args.warmup, hbm_peak, peak_kind,
+                                                     args.gemv_kinds.split(",") if args.gemv_kinds else None)}),
+              flush=True)
         return
     if args.generate_only:
         import torch

@@ -42,7 +42,7 @@ struct HostCfg {
 HostCfg g_host_cfg[64];
 
 template <int D, int HPC>
-__device__ __noinline__ void run(const DecodeParams& p, unsigned char* smem) {
+__device__ __forceinline__ void run(const DecodeParams& p, unsigned char* smem) {
     decode_detail::decode_split_body<D, HPC, /*QSPLIT=*/true, /*BF16=*/false, /*FUSED=*/true>(p, smem);
 }
 

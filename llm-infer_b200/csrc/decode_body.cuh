@@ -198,10 +198,10 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     // launched and that the only cache row it writes is each sequence's last valid one: the wait then moves behind the
     // tile prefix, and the producer warp starts the tiles that cannot hold that row before it waits (below), so the
     // first K/V bytes are already on their way while the previous kernel finishes.
-    // With uniform lengths (no length array to wait for) the wait moves in the same way, and the producer warp spends
-    // it asking L2 for its first tiles (a hint, not a load: it may run ahead of the kernel that writes the newest row).
-    // In a chain of decode steps the next step's first tiles then cross HBM while this step's slowest CTAs and its
-    // merge pass are still at work.
+    // With uniform lengths (no length array to wait for) the wait moves behind the tile arithmetic in the same way.
+    // (Tried there and dropped: asking L2 for the CTA's first tiles with bulk prefetches before the wait. In a chain of
+    // decode steps it made the step 3 us slower, 48.0 -> 51.0 us at batch 16 x 4096 rows: the hints compete for HBM
+    // with the previous step's slowest CTAs instead of filling a gap.)
     const bool early = p.kv_early != 0;
     const bool deferred = early || p.kv_len == nullptr;
     if (!deferred) grid_dep_wait();
@@ -324,18 +324,6 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
             grid_dep_wait();
             if (i > 0 && !issue_q()) return;  // the running segment's query rows, which that kernel produced
         } else if (deferred) {
-            SegInfo ps = seg;
-            for (uint32_t k = 0; k < n_my && k < nst; ++k) {
-                const uint32_t gt = t_begin + k;
-                while (gt >= ps.tile_end) ps = table.load(ps.seg + 1);
-                const uint32_t tok0 = (gt - ps.tile0) * TT;
-                const size_t seq_off = static_cast<size_t>(ps.b) * p.kv_batch_stride + static_cast<size_t>(ps.hg) * (HPC * D);
-                for (uint32_t j = lane; j < TT && tok0 + j < ps.len; j += 32) {
-                    const size_t off = seq_off + static_cast<size_t>(tok0 + j) * p.kv_row_stride;
-                    bulk_prefetch_l2(p.k + off, ROWB);
-                    bulk_prefetch_l2(p.v + off, ROWB);
-                }
-            }
             grid_dep_wait();
         }
         for (; i < n_my; ++i) {
@@ -359,6 +347,9 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     }
 
     // ===================== consumer warps =====================
+    // (No setmaxnreg here: with nine warps, warps 0, 4 and 8 share one of the SM's four register files of 512
+    // registers per lane, 3 x 168 of which are taken at launch; an increase for the consumer warpgroups can never be
+    // granted and the instruction would wait for ever.)
     if (deferred) grid_dep_wait();   // before the first partial is written and the query rows are used
     const int hh = warp / TS;        // kv head within the head group
     const int ts = warp - hh * TS;   // row sub-tile
@@ -464,7 +455,7 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     // AFTER: every merge is skipped (output untouched, counters back to zero) whenever a partial is missing.
     auto fused_merge = [&]() {
         if constexpr (FUSED) {
-            constexpr uint32_t kOneLevelMax = 32;  // partials that one merge reads in two rounds of loads
+            constexpr uint32_t kOneLevelMax = 32;  // partials that one merge reads in four rounds of loads
             __threadfence();
             asm volatile("bar.sync 1, 256;" ::: "memory");
             const uint32_t c_first = cta_of_tile(seg.tile0, nt, active);

@@ -145,15 +145,15 @@ __device__ __forceinline__ void locate_partials(const MergeParams& p, uint32_t r
 // 256 threads merge n partial records of `rows` consecutive output rows each: partial i of row r at
 // po + i * o_stride + r * D (D floats) with its LSE at pl + i * l_stride + r. A thread owns four floats of one row over
 // all partials and folds them into a running (m, z, acc) state as the reference folds tiles
-// (src/attention.cu:41-65), sixteen partials' loads (LSE and values, L2-only) in flight at a time; no thread needs
+// (src/attention.cu:41-65), eight partials' loads (LSE and values, L2-only) in flight at a time; no thread needs
 // another's result. store(r, f, value, lse) receives the normalised float4 number f of row r and the row's
-// log-sum-exp (zeros and -inf for an all-empty row). Not inlined: it runs once or twice per segment, and as a call it
-// does not add to the register pressure of the streaming loop it is called from.
+// log-sum-exp (zeros and -inf for an all-empty row). (Inlined on purpose: as a call, the variables that `store`
+// captures by reference had to live in local memory for the whole calling kernel, which slowed its streaming loop.)
 template <int D, typename Store>
-__device__ __noinline__ void cta_merge_rows(const float* po, const float* pl, uint64_t o_stride, uint64_t l_stride,
+__device__ __forceinline__ void cta_merge_rows(const float* po, const float* pl, uint64_t o_stride, uint64_t l_stride,
                                                uint32_t n, uint32_t rows, int tid, Store store) {
     constexpr int F4 = D / 4;
-    constexpr int kInFlight = 16;
+    constexpr int kInFlight = 8;
     for (uint32_t it = tid; it < rows * F4; it += 256) {
         const uint32_t r = it / F4, f = it - r * F4;
         const float* o0 = po + static_cast<size_t>(r) * D + f * 4;
