@@ -304,8 +304,8 @@ def generate_measure(torch, batch: int = 8, n_new: int = 128, seed: int = 5, pro
 
 
 def gemv_measure(torch, steps: int, warmup: int, hbm_peak: float, peak_kind: str, kinds=None):
-    """The weight GEMVs of one Llama-3-8B-shaped layer alone (eager launches, rotated weight copies > L2, CUDA events):
-    fp16 and Q8_0, batch 1 and 8. Used for profiler captures and the GEMV roofline figures. ``kinds`` restricts the
+    """The weight GEMVs of one Llama-3-8B-shaped layer alone (rotated weight copies > L2, CUDA events; replayed from a
+    CUDA graph and launched one by one): fp16 and Q8_0, batch 1 and 8. Used for profiler captures and the GEMV roofline figures. ``kinds`` restricts the
     run to some of "q8_0", "q8_0_tiled", "f16" (profiler captures of one kernel)."""
     import numpy as np
     from llm_infer_b200 import attention as A, quant
@@ -336,34 +336,34 @@ def gemv_measure(torch, steps: int, warmup: int, hbm_peak: float, peak_kind: str
                 fn(x, copies[i % len(copies)], out=out)
             t1.record()
             torch.cuda.synchronize()
-            us = t0.elapsed_time(t1) * 1e3 / steps
+            eager_us = t0.elapsed_time(t1) * 1e3 / steps
             alg = w.numel() * w.element_size() + batch * (n * 4 + d * 4)
-            res[f"{kind}_b{batch}"] = {"us": round(us, 2), "gbs": round(alg / us / 1e3, 1),
-                                       "frac": round(alg / us / 1e3 / hbm_peak, 3), "algorithmic_bytes": alg}
-            if kind == "q8_0_tiled":
-                # the same calls replayed from one CUDA graph: the host's launch cost is out of the figure and
-                # consecutive launches overlap through programmatic dependent launch, as they do in a model step
-                g = torch.cuda.CUDAGraph()
-                side = torch.cuda.Stream()
-                side.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(side), torch.cuda.graph(g):
-                    for c in copies:
-                        fn(x, c, out=out)
-                torch.cuda.current_stream().wait_stream(side)
+            # The figure of the row: the same calls replayed from one CUDA graph. The host's launch cost (which exceeds
+            # the kernel's time when launches come from Python one by one) is out of it, and consecutive launches
+            # overlap through programmatic dependent launch, as they do in a model step.
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side), torch.cuda.graph(g):
+                for c in copies:
+                    fn(x, c, out=out)
+            torch.cuda.current_stream().wait_stream(side)
+            g.replay()
+            torch.cuda.synchronize()
+            t0.record()
+            for _ in range(10):
                 g.replay()
-                torch.cuda.synchronize()
-                t0.record()
-                for _ in range(10):
-                    g.replay()
-                t1.record()
-                torch.cuda.synchronize()
-                us = t0.elapsed_time(t1) * 1e3 / (10 * len(copies))
-                res[f"{kind}_b{batch}"]["graph_replay"] = {"us": round(us, 2), "gbs": round(alg / us / 1e3, 1),
-                                                           "frac": round(alg / us / 1e3 / hbm_peak, 3)}
+            t1.record()
+            torch.cuda.synchronize()
+            us = t0.elapsed_time(t1) * 1e3 / (10 * len(copies))
+            res[f"{kind}_b{batch}"] = {"us": round(us, 2), "gbs": round(alg / us / 1e3, 1),
+                                       "frac": round(alg / us / 1e3 / hbm_peak, 3), "algorithmic_bytes": alg,
+                                       "eager_us": round(eager_us, 2)}
         del copies
-    res["note"] = (f"{d}x{n} matrix, eager back-to-back launches (host launch cost included when the kernel is "
-                   f"shorter), frac of {peak_kind} HBM peak {hbm_peak:.1f} GB/s; q8_0_tiled = the tiled copy of the "
-                   "blocks with prepared activations (what a model step runs), also replayed from one CUDA graph")
+    res["note"] = (f"{d}x{n} matrix, rotated weight copies > L2; us / gbs / frac = CUDA-graph replay of the calls "
+                   f"(device time), eager_us = launched one by one from Python (host launch cost included); frac of "
+                   f"{peak_kind} HBM peak {hbm_peak:.1f} GB/s; q8_0 = GGML blocks with fp32 activations, q8_0_tiled = "
+                   "the tiled copy of the same blocks with prepared activations (what a model step runs)")
     return res
 
 

@@ -21,8 +21,8 @@
  * the split-KV partials) is set once per device with attention_configure(); the
  * launch geometry that the graph node must use comes from attention_launch_dims().
  * One launch does both passes: every CTA writes partial (O, LSE) results for its
- * share of the rows, and the CTA that delivers the last partial merges them
- * (no CTA waits for another).
+ * share of the rows, and the CTAs that deliver the last partials merge them - in
+ * two levels when a sequence is long (no CTA waits for another).
  */
 #ifndef LLM_INFER_KERNELS_B200_CUH
 #define LLM_INFER_KERNELS_B200_CUH
