@@ -139,6 +139,10 @@ class Llama:
         self.next_token = z(B, dtype=torch.int32)
         self.tokens = z(B, dtype=torch.int32)   # the step's input tokens; a decode step writes its picks back here
         self._graphs = None
+        # The lengths are copied in before a step's first kernel and the kernel in front of the attention (rotary +
+        # insert) writes only each sequence's newest row: the attention may start streaming the older rows early
+        # (measured: 3.03 -> 3.00 ms per step of the 8B-shaped Q8_0 model at batch 8).
+        self.kv_early = True
         self.pos, self.kv_pos, self.kv_len = (z(B, dtype=torch.int32) for _ in range(3))
         self.status = z(1, dtype=torch.int32)
         # one cache per layer and sequence, the engine's layout
@@ -206,7 +210,7 @@ class Llama:
                              theta=c.rope_theta, rotary_dim=c.rotary_dim, kv_sink=kv_sink, q_out=self.q,
                              pos_early=True)   # positions are copied in before the step's first kernel
             A.attn_decode(self.q, self.k_cache[l], self.v_cache[l], self.kv_len, out=self.att,
-                          workspace=self.workspace)
+                          workspace=self.workspace, kv_early=self.kv_early)
             gemv(att_flat, "wo", l, out=self.x, accumulate=True)           # x += Wo att
             A.rmsnorm(self.x, w["rms_ffn"][l], c.norm_eps, out=self.xb)
             gemv(self.xb, "w13", l, out=self.hb, swiglu=True)              # hb = silu(W1 xb) * (W3 xb)
