@@ -1035,6 +1035,8 @@ def main():
                     help="time only the causal-prefill workload (used for profiler captures)")
     ap.add_argument("--gemv-only", action="store_true",
                     help="time only the weight GEMVs of one layer (fp16 and Q8_0; used for profiler captures)")
+    ap.add_argument("--symbol-only", action="store_true",
+                    help="time only the engine's attention kernel symbol (used for profiler captures)")
     ap.add_argument("--gemv-kinds", default="",
                     help="with --gemv-only: comma-separated subset of q8_0,q8_0_tiled,f16")
     ap.add_argument("--generate-only", action="store_true",
@@ -1067,6 +1069,12 @@ def main():
         _, tflops_peak, peak_kind = measured_peaks()
         print(json.dumps({"prompt_gemm": gemm_measure(torch, args.steps, args.warmup, tflops_peak, peak_kind,
                                                       small=args.steps <= 5)}), flush=True)
+        return
+    if args.symbol_only:
+        import torch
+        load_package()
+        hbm_peak, _, _ = measured_peaks()
+        print(json.dumps({"attention_symbol": attention_symbol_measure(torch, hbm_peak)}), flush=True)
         return
     if args.gemv_only:
         import torch
