@@ -41,9 +41,15 @@ struct HostCfg {
 };
 HostCfg g_host_cfg[64];
 
+// Two forms per shape: up to eight query heads per kv head (rows 8-15 of the MMAs dropped: no spills in the
+// 168 registers of this nine-warp CTA), and the general one.
 template <int D, int HPC>
 __device__ __forceinline__ void run(const DecodeParams& p, unsigned char* smem) {
-    decode_detail::decode_split_body<D, HPC, /*QSPLIT=*/true, /*BF16=*/false, /*FUSED=*/true>(p, smem);
+    if (p.group <= 8) {
+        decode_detail::decode_split_body<D, HPC, /*QSPLIT=*/true, /*BF16=*/false, /*FUSED=*/true, /*LOW8=*/true>(p, smem);
+    } else {
+        decode_detail::decode_split_body<D, HPC, /*QSPLIT=*/true, /*BF16=*/false, /*FUSED=*/true, /*LOW8=*/false>(p, smem);
+    }
 }
 
 }  // namespace

@@ -133,7 +133,10 @@ __device__ __forceinline__ void load_q_fragments(const T* q_head0, int D, int G,
     }
 }
 
-template <int D, int HPC, bool QSPLIT, bool BF16, bool FUSED>
+// LOW8: the caller guarantees at most eight query heads per kv head. Rows 8-15 of every MMA are then empty, and the
+// query fragments, score and output accumulators of those rows (half of each: 64 registers with value + residual
+// queries and head_dim 128) are not kept at all.
+template <int D, int HPC, bool QSPLIT, bool BF16, bool FUSED, bool LOW8 = false>
 __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigned char* smem) {
     constexpr int TS = kConsumerWarps / HPC;     // row sub-tiles per kv head
     constexpr int TT = 16 * TS;                  // rows per tile
@@ -356,7 +359,7 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
     const int gq = lane >> 2;        // MMA row owned by this lane (and gq + 8)
     const int cq = lane & 3;
     const uint32_t G = p.group;
-    const bool ghi = G > 8;          // rows 8..15 of the MMA hold real heads
+    const bool ghi = !LOW8 && G > 8;  // rows 8..15 of the MMA hold real heads
 
     // per-lane ldmatrix row addresses inside a tile (stage base added per tile)
     const uint32_t k_lane_off = (ts * 16 + ((lane >> 4) << 3) + (lane & 7)) * PITCH + hh * (D * 2) + (((lane >> 3) & 1) << 4);
@@ -574,11 +577,20 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         for (int kc = 0; kc < KC; ++kc) {
             uint32_t b0, b1, b2, b3;
             ldmatrix_x4(b0, b1, b2, b3, kbase + k_lane_off + kc * 32);
-            mma_16816<BF16>(s[0], qhi[kc], b0, b1);
-            mma_16816<BF16>(s[1], qhi[kc], b2, b3);
-            if constexpr (QSPLIT) {
-                mma_16816<BF16>(s[0], qlo[kc], b0, b1);
-                mma_16816<BF16>(s[1], qlo[kc], b2, b3);
+            if constexpr (LOW8) {
+                mma_16816_low8<BF16>(s[0][0], s[0][1], qhi[kc][0], qhi[kc][2], b0, b1);
+                mma_16816_low8<BF16>(s[1][0], s[1][1], qhi[kc][0], qhi[kc][2], b2, b3);
+                if constexpr (QSPLIT) {
+                    mma_16816_low8<BF16>(s[0][0], s[0][1], qlo[kc][0], qlo[kc][2], b0, b1);
+                    mma_16816_low8<BF16>(s[1][0], s[1][1], qlo[kc][0], qlo[kc][2], b2, b3);
+                }
+            } else {
+                mma_16816<BF16>(s[0], qhi[kc], b0, b1);
+                mma_16816<BF16>(s[1], qhi[kc], b2, b3);
+                if constexpr (QSPLIT) {
+                    mma_16816<BF16>(s[0], qlo[kc], b0, b1);
+                    mma_16816<BF16>(s[1], qlo[kc], b2, b3);
+                }
             }
         }
 
@@ -587,7 +599,7 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < (LOW8 ? 2 : 4); ++e) {
                 const uint32_t r = tok + n * 8 + (e & 1);
                 s[n][e] = r < seg.len ? s[n][e] * p.scale_log2 : -INFINITY;
             }
@@ -641,8 +653,10 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
             for (int dn = 0; dn < DN; ++dn) {
                 o[dn][0] *= sc0;
                 o[dn][1] *= sc0;
-                o[dn][2] *= sc1;
-                o[dn][3] *= sc1;
+                if constexpr (!LOW8) {
+                    o[dn][2] *= sc1;
+                    o[dn][3] *= sc1;
+                }
             }
         }
 
@@ -656,10 +670,17 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
         for (int d2 = 0; d2 < DN / 2; ++d2) {
             uint32_t b0, b1, b2, b3;
             ldmatrix_x4_trans(b0, b1, b2, b3, vbase + v_lane_off + d2 * 32);
-            mma_16816<BF16>(o[2 * d2], pa, b0, b1);
-            mma_16816<BF16>(o[2 * d2 + 1], pa, b2, b3);
-            mma_16816<BF16>(o[2 * d2], pb, b0, b1);
-            mma_16816<BF16>(o[2 * d2 + 1], pb, b2, b3);
+            if constexpr (LOW8) {
+                mma_16816_low8<BF16>(o[2 * d2][0], o[2 * d2][1], pa[0], pa[2], b0, b1);
+                mma_16816_low8<BF16>(o[2 * d2 + 1][0], o[2 * d2 + 1][1], pa[0], pa[2], b2, b3);
+                mma_16816_low8<BF16>(o[2 * d2][0], o[2 * d2][1], pb[0], pb[2], b0, b1);
+                mma_16816_low8<BF16>(o[2 * d2 + 1][0], o[2 * d2 + 1][1], pb[0], pb[2], b2, b3);
+            } else {
+                mma_16816<BF16>(o[2 * d2], pa, b0, b1);
+                mma_16816<BF16>(o[2 * d2 + 1], pa, b2, b3);
+                mma_16816<BF16>(o[2 * d2], pb, b0, b1);
+                mma_16816<BF16>(o[2 * d2 + 1], pb, b2, b3);
+            }
         }
 
         __syncwarp();

@@ -114,6 +114,26 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
     }
 }
 
+// The same product when rows 8-15 of A are known to be zero (at most eight query heads per kv head): only rows 0-7
+// are fed (a0: columns k, a2: columns k+8) and kept (c0, c1); the zero half of A, the zero accumulator half and the
+// discarded outputs are temporaries of the instruction, so they occupy no register of the caller between MMAs.
+template <bool BF16>
+__device__ __forceinline__ void mma_16816_low8(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    if constexpr (BF16) {
+        asm volatile(
+            "{\n\t.reg .b32 z;\n\t.reg .f32 zf, j0, j1;\n\tmov.b32 z, 0;\n\tmov.f32 zf, 0f00000000;\n\t"
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,j0,j1}, {%2,z,%3,z}, {%4,%5}, {%0,%1,zf,zf};\n\t}"
+            : "+f"(c0), "+f"(c1)
+            : "r"(a0), "r"(a2), "r"(b0), "r"(b1));
+    } else {
+        asm volatile(
+            "{\n\t.reg .b32 z;\n\t.reg .f32 zf, j0, j1;\n\tmov.b32 z, 0;\n\tmov.f32 zf, 0f00000000;\n\t"
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,j0,j1}, {%2,z,%3,z}, {%4,%5}, {%0,%1,zf,zf};\n\t}"
+            : "+f"(c0), "+f"(c1)
+            : "r"(a0), "r"(a2), "r"(b0), "r"(b1));
+    }
+}
+
 // Two floats -> packed 16-bit pair (low half = first argument), round to nearest even.
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
