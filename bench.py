@@ -883,7 +883,7 @@ def run_multi(args, world: int, rank: int, local_rank: int):
     #      replayed from CUDA graphs (one per input copy) the way the engine replays its decode graph
     step, launch_mode, graphs = None, "nccl-allgather, eager", None
     try:
-        fused = FusedShardedDecode(1, H, Hkv, D, device=dev)
+        fused = FusedShardedDecode(1, H, Hkv, D, device=dev, kv_early=not args.no_sharded_kv_early)
         ok = True
     except Exception as e:  # no peer-mapped memory on this box: stay on path A
         fused, ok = None, False
@@ -1024,6 +1024,7 @@ def run_multi(args, world: int, rank: int, local_rank: int):
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
             "config": workload_config(shape, world),
             "exchange": launch_mode,
+            "kv_early": not args.no_sharded_kv_early,
             "l2": f"{rows * Hkv * D * 4 >> 20} MiB of KV per GPU per step, {n_sets} copies rotated",
             "tok_per_s": 1.0 / (ms_per_step * 1e-3),
             "parity": parity,
@@ -1060,6 +1061,10 @@ def main():
                     help="time only the causal-prefill workload (used for profiler captures)")
     ap.add_argument("--gemv-only", action="store_true",
                     help="time only the weight GEMVs of one layer (fp16 and Q8_0; used for profiler captures)")
+    ap.add_argument("--no-sharded-kv-early", action="store_true",
+                    help="with --gpus N > 1: do not let the local pass stream K/V rows ahead of the previous kernel "
+                         "(by default it does: between the steps of this workload no cache row changes, and in the "
+                         "engine only each sequence's newest row would)")
     ap.add_argument("--symbol-only", action="store_true",
                     help="time only the engine's attention kernel symbol (used for profiler captures)")
     ap.add_argument("--gemv-kinds", default="",

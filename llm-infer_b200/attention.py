@@ -135,11 +135,14 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, k
 
 def attn_decode_sharded(q, k_shard, v_shard, kv_len_local=None, *, peer_buffers, world_size: int, rank: int,
                         step: int = 0, poll_limit: int = 0, out=None, lse=None, out_dtype=torch.float32,
-                        scale: float = 0.0, workspace: DecodeWorkspace | None = None, stream=None) -> torch.Tensor:
+                        scale: float = 0.0, workspace: DecodeWorkspace | None = None, kv_early: bool = False,
+                        stream=None) -> torch.Tensor:
     """Decode over this rank's KV rows with the cross-GPU exchange fused into the merge pass (C ABI
     ``attn_decode_sharded``). ``peer_buffers`` holds one device pointer per rank (as int) to that rank's exchange
-    buffer, valid on this GPU; ``step = 0`` lets the kernel count steps itself. Returns the final out [B, H, D]."""
-    a, out, _, _q = _decode_args(q, k_shard, v_shard, kv_len_local, out, lse, out_dtype, scale, workspace, 0, stream)
+    buffer, valid on this GPU; ``step = 0`` lets the kernel count steps itself; ``kv_early`` as in attn_decode.
+    Returns the final out [B, H, D]."""
+    a, out, _, _q = _decode_args(q, k_shard, v_shard, kv_len_local, out, lse, out_dtype, scale, workspace, 0, stream,
+                                 kv_early)
     s = _b.AttnDecodeShardedArgs()
     s.decode = a
     s.world_size, s.rank, s.step, s.poll_limit = world_size, rank, step, poll_limit

@@ -137,12 +137,17 @@ class FusedShardedDecode:
     """The same sharded decode with the collective carried by the merge kernel itself instead of NCCL.
 
     Every rank owns an exchange buffer in symmetric (peer-mapped) memory. The merge pass of ``attn_decode_sharded``
-    stores each merged row straight into all ranks' buffers over NVLink, raises a per-row flag there, waits (bounded)
-    for the other ranks' flags of that row and finishes the row: two launches per step, no separate collective and
-    no third kernel. ``torch.distributed`` is only used to allocate and exchange the buffer handles.
+    stores each merged cell (a row's 32-float slice and its LSE) straight into all ranks' buffers over NVLink as 64-bit
+    words that carry the step number, waits (bounded) until the other ranks' words of that cell show the step and
+    finishes the cell: two launches per step, no separate collective and no third kernel. ``torch.distributed`` is
+    only used to allocate and exchange the buffer handles. ``kv_early``: the caller vouches that between steps only
+    each sequence's newest row is written (by the kernel in front of the step), so the local pass may start streaming
+    the older rows before that kernel has finished.
     """
 
-    def __init__(self, batch: int, n_heads: int, n_kv_heads: int, head_dim: int, *, device, group=None):
+    def __init__(self, batch: int, n_heads: int, n_kv_heads: int, head_dim: int, *, device, group=None,
+                 kv_early: bool = False):
+        self.kv_early = bool(kv_early)
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import attention
@@ -163,7 +168,7 @@ class FusedShardedDecode:
         """q [B,H,D] (replicated); k_shard, v_shard [B,T_local,Hkv,D] (this rank's rows) -> out [B,H,D]."""
         return self._attention.attn_decode_sharded(
             q, k_shard, v_shard, kv_len_local, peer_buffers=self.peer_buffers, world_size=self.world, rank=self.rank,
-            step=0, out=out, lse=lse, out_dtype=out_dtype, workspace=self.workspace)
+            step=0, out=out, lse=lse, out_dtype=out_dtype, workspace=self.workspace, kv_early=self.kv_early)
 
     def capture(self, q, k_shard, v_shard, out, kv_len_local=None):
         """One step as a CUDA graph (the kernel counts steps on the device, so the arguments never change)."""
