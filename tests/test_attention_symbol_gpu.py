@@ -26,7 +26,8 @@ def _configure(lib, torch, H, Hkv, D):
 
 
 @pytest.mark.parametrize("H,Hkv,D,T", [(32, 8, 128, 4096), (32, 4, 64, 512), (32, 8, 128, 37), (8, 1, 128, 300),
-                                       (32, 8, 128, 20011), (16, 2, 64, 9001)])  # the long ones: two-level merge
+                                       (32, 8, 128, 20011), (16, 2, 64, 9001),  # the long ones: two-level merge
+                                       (32, 2, 128, 777)])  # 16 query heads per kv head: the general form of the body
 def test_plain_launch_matches_cpu_attn(env, checker, H, Hkv, D, T):
     from gpu_util import check_close
     lib, wl, torch = env
