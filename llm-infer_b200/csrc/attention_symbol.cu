@@ -29,6 +29,10 @@ struct AttentionSymbolConfig {
     float* group_lse;
     uint32_t* status;     // one word of the workspace: ATTN_STATUS_* bits
     uint32_t smem_bytes;  // dynamic shared memory the node must be launched with
+#ifdef ATTN_BOUNDS_CHECK
+    uint64_t part_rows;    // what the checking build compares its workspace indices with
+    uint64_t group_slots;
+#endif
 };
 
 __constant__ AttentionSymbolConfig g_cfg;
@@ -107,6 +111,10 @@ attention(float* o, const float* q, const half* k, const half* v, uint32_t kv_to
     p.group_counters = c.group_counters;
     p.group_o = c.group_o;
     p.group_lse = c.group_lse;
+#ifdef ATTN_BOUNDS_CHECK
+    p.part_rows = c.part_rows;
+    p.group_slots = c.group_slots;
+#endif
     if (c.head_dim == 128) {
         switch (c.hpc) {
             case 8: run<128, 8>(p, smem); break;
@@ -180,6 +188,10 @@ int attention_configure(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim
     c.group_lse = c.group_o + plan.group_o_floats;
     c.group_counters = reinterpret_cast<uint32_t*>(c.group_lse + plan.group_lse_floats);
     c.smem_bytes = static_cast<uint32_t>(plan.smem_bytes);
+#ifdef ATTN_BOUNDS_CHECK
+    c.part_rows = plan.part_o_floats / head_dim;
+    c.group_slots = static_cast<uint64_t>(plan.grid) + plan.nseg;
+#endif
     // counters (rounded up to four words), the status word behind them and the group counters start at zero
     B200_CUDA_TRY(cudaMemsetAsync(c.counters, 0, (((static_cast<size_t>(plan.nseg) + 3) & ~3ull) + 4) * 4, stream));
     B200_CUDA_TRY(cudaMemsetAsync(c.group_counters, 0, plan.group_counter_words * 4, stream));

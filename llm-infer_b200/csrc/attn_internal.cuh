@@ -50,6 +50,7 @@ struct DecodeParams {
     uint32_t kv_capacity;  // rows a sequence's caches hold, 0 = not stated (lengths beyond it are clamped and reported)
 #ifdef ATTN_BOUNDS_CHECK
     uint64_t part_rows;    // rows of part_o / entries of part_lse that exist
+    uint64_t group_slots;  // group records / group counters that exist (single-launch mode)
 #endif
     uint32_t* status;
     // single-launch (fused merge) mode only: final output and per-segment arrival counters

@@ -477,6 +477,12 @@ __device__ __forceinline__ void decode_split_body(const DecodeParams& p, unsigne
             // groups are disjoint CTA ranges and a CTA is shared by at most two consecutive segments, so (first CTA of
             // the group + segment) numbers the groups of the whole launch without collisions, below grid + nseg
             const size_t group_slot = static_cast<size_t>(c_first) + gi * gs + seg.seg;
+#ifdef ATTN_BOUNDS_CHECK
+            if (two_level && group_slot >= p.group_slots) {  // the group arithmetic left the workspace: record, do nothing
+                if (tid == 0 && p.status) atomicOr(p.status, ATTN_STATUS_BAD_INDEX);
+                return;
+            }
+#endif
             uint32_t* counter = two_level ? p.group_counters + group_slot : p.counters + seg.seg;
             auto take_ticket = [&](uint32_t* c) {
                 if (tid == 0) {

@@ -202,7 +202,7 @@ def test_length_beyond_the_cache_is_clamped_and_reported(attention, wl, checker)
 def test_checking_build_runs_clean(pkg, wl, checker, tmp_path):
     """The -DATTN_BOUNDS_CHECK build (the decode passes verify their workspace indices and report ATTN_STATUS_BAD_INDEX
     instead of accessing) gives the same results with no status bit on uniform, ragged and single-long-sequence
-    shapes. Runs in a child process because the library is chosen when the binding is first loaded."""
+    shapes, through attn_decode and through the engine's single-launch kernel symbol. Runs in a child process because the library is chosen when the binding is first loaded."""
     import subprocess
     import sys
     from conftest import ROOT
@@ -225,6 +225,22 @@ for (B, T, lens) in ((3, 700, [700, 1, 333]), (1, 20000, None), (16, 512, None))
     assert int(ws.status.item()) == 0, ws.status.item()
     want = oracle.best().attn_decode(q, k, v, None if lens is None else np.array(lens, np.uint32))
     a, r = wl.error_metrics(out.cpu().numpy(), want)
+    assert a <= wl.ABS_TOL and r <= wl.REL_TOL, (a, r)
+# the engine's kernel symbol (single launch; two-level merge on the long sequence)
+import ctypes as C
+lib = binding.load()
+n = lib.attention_workspace_bytes(32, 8, 128)
+wsb = torch.zeros(n, dtype=torch.uint8, device='cuda')
+stream = torch.cuda.current_stream().cuda_stream
+assert lib.attention_configure(32, 8, 128, 0.0, wsb.data_ptr(), n, stream) == 0
+for T in (300, 20000):
+    q, k, v = wl.decode_inputs(wl.DecodeShape('s', 6, 1, 32, 8, 128, T, 'f32', 'f16'))
+    qd, kd, vd = (torch.from_numpy(x[0]).cuda() for x in (q, k, v))
+    o = torch.empty(32, 128, device='cuda')
+    assert lib.attention_launch(o.data_ptr(), qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), T, stream) == 0
+    bits = C.c_uint32(7)
+    assert lib.attention_status(C.byref(bits), 0, stream) == 0 and bits.value == 0, bits.value
+    a, r = wl.error_metrics(o.cpu().numpy(), oracle.best().attn_decode(q, k, v)[0])
     assert a <= wl.ABS_TOL and r <= wl.REL_TOL, (a, r)
 print('ok')
 """
