@@ -102,7 +102,7 @@ __device__ __forceinline__ void word_to_fragments(uint32_t w, uint32_t& first, u
     second = *reinterpret_cast<const uint32_t*>(&b);
 }
 
-// NW warps per CTA. REGX: the inner dimension is exactly NW chunks, so a warp always multiplies by the same CB blocks
+// NW warps per CTA. REGX: the inner dimension (or, with split-k, the CTA's slice of it) is exactly NW chunks, so a warp always multiplies by the same CB blocks
 // of the activations and keeps them in registers as MMA B fragments (64 registers for CB = 8) for the whole launch:
 // no shared memory for the activations (which at batch 8 x 4096 would take 128 KB and leave room for 8 warps only), no
 // shared-memory loads for them in the inner loop, and twice the warps per SM to hide the latency of the
@@ -194,7 +194,9 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_q8_0_kernel(const __grid_cons
             for (uint32_t s2 = 0; s2 < 2; ++s2) {
                 xr[bi][s2] = make_uint4(0, 0, 0, 0);
                 if (has_col) {
-                    const size_t e = static_cast<size_t>(g) * p.x_batch_stride + 32 * (warp * CB + bi) + 16 * s2 + 4 * t;
+                    // (with split-k this CTA's slice starts slice_begin * NW chunks into the row)
+                    const size_t e = static_cast<size_t>(g) * p.x_batch_stride + 32 * ((slice_begin * NW + warp) * CB + bi) +
+                                     16 * s2 + 4 * t;
                     if (p.x_split) {
                         xr[bi][s2] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(p.x) + e);
                     } else {
@@ -403,11 +405,17 @@ int gemv_q8_0_launch(const AttnGemvArgs* a, void* stream_v, bool tiled) {
     // with its chunk of the activations in registers, two stages per warp, nothing else staged.
     constexpr uint32_t kRegxWarps = 16;
     // (a single sequence of fp32 activations is faster on the 8-warp form: measured 16.1 vs 18.5 us at 14336 x 4096)
-    const bool regx = k_split == 1 && n_blocks == kRegxWarps * 8 && (a->batch >= 2 || a->x_format == ATTN_DTYPE_SPLIT16);
-    if (regx) {
-        plan = Plan{8, 1, 2,
-                    2 * 2 * kRegxWarps * 128 * sizeof(float) + (kRegxWarps * kMaxStages + 2) * sizeof(uint64_t) + 128 +
-                        static_cast<size_t>(2) * kRegxWarps * stage_bytes(8)};
+    const bool regx_x = a->batch >= 2 || a->x_format == ATTN_DTYPE_SPLIT16;
+    const bool regx = k_split == 1 && n_blocks == kRegxWarps * 8 && regx_x;
+    // The same with 14 warps for split-k slices of 14 chunks (the 14336-wide down projection cut in four), tiled copy
+    // only.
+    constexpr uint32_t kRegxSliceWarps = 14;
+    const bool regx_slice = tiled && k_split > 1 && n_blocks == k_split * kRegxSliceWarps * 8 && regx_x;
+    if (regx || regx_slice) {
+        const uint32_t w = regx ? kRegxWarps : kRegxSliceWarps;
+        plan = Plan{8, k_split, 2,
+                    2 * 2 * w * 128 * sizeof(float) + (w * kMaxStages + 2) * sizeof(uint64_t) + 128 +
+                        static_cast<size_t>(2) * w * stage_bytes(8)};
     }
     const uint32_t slices = plan.slices, stages = plan.stages, slice_blocks = n_blocks / slices;
     const size_t smem = plan.smem;
@@ -440,10 +448,11 @@ int gemv_q8_0_launch(const AttnGemvArgs* a, void* stream_v, bool tiled) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     p.w_tiles = static_cast<const uint8_t*>(a->w);
     p.row_chunks = n_blocks / 8;
-    auto kernel = tiled ? (regx ? gemv_q8_0_kernel<8, kRegxWarps, true, true> : gemv_q8_0_kernel<8, kWarps, false, true>)
-                  : regx ? gemv_q8_0_kernel<8, kRegxWarps, true, false>
+    auto kernel = regx_slice ? gemv_q8_0_kernel<8, kRegxSliceWarps, true, true>
+                  : tiled    ? (regx ? gemv_q8_0_kernel<8, kRegxWarps, true, true> : gemv_q8_0_kernel<8, kWarps, false, true>)
+                  : regx     ? gemv_q8_0_kernel<8, kRegxWarps, true, false>
                   : plan.cb == 16 ? gemv_q8_0_kernel<16, kWarps, false, false> : gemv_q8_0_kernel<8, kWarps, false, false>;
-    const uint32_t threads = regx ? kRegxWarps * 32 : kThreads;
+    const uint32_t threads = regx_slice ? kRegxSliceWarps * 32 : regx ? kRegxWarps * 32 : kThreads;
     B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     B200_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(threads), smem, stream, tm_w, p));
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
